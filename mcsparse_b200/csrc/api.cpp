@@ -1,0 +1,859 @@
+// Host side of libmcsparse.so: handle, descriptors, argument validation, dtype routing.
+//
+// Internally every function reports an mcspStatus-like code and the exported wrapper maps
+// it to the public status exactly as the reference does
+// (mcsparse/src/wrapper/mcsp_interface_wrapper.cpp:5-42):
+//   invalid handle            -> MCSPARSE_STATUS_NOT_INITIALIZED
+//   invalid pointer/size/value-> MCSPARSE_STATUS_INVALID_VALUE
+//   not implemented           -> MCSPARSE_STATUS_NOT_SUPPORTED
+//   launch failure            -> MCSPARSE_STATUS_EXECUTION_FAILED
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+
+using namespace mcsp_b200;
+
+namespace {
+
+enum St {
+    OK = 0,
+    BAD_HANDLE,
+    BAD_POINTER,
+    BAD_SIZE,
+    BAD_VALUE,
+    NOT_IMPL,
+    INTERNAL,
+    EXEC_FAILED,
+    ALLOC_FAILED,
+};
+
+mcsparseStatus_t pub(St s) {
+    switch (s) {
+        case OK: return MCSPARSE_STATUS_SUCCESS;
+        case BAD_HANDLE: return MCSPARSE_STATUS_NOT_INITIALIZED;
+        case BAD_POINTER:
+        case BAD_SIZE:
+        case BAD_VALUE: return MCSPARSE_STATUS_INVALID_VALUE;
+        case NOT_IMPL: return MCSPARSE_STATUS_NOT_SUPPORTED;
+        case EXEC_FAILED: return MCSPARSE_STATUS_EXECUTION_FAILED;
+        case ALLOC_FAILED: return MCSPARSE_STATUS_ALLOC_FAILED;
+        default: return MCSPARSE_STATUS_INTERNAL_ERROR;
+    }
+}
+
+St from_cuda(cudaError_t e) {
+    if (e == cudaSuccess) return OK;
+    if (e == cudaErrorMemoryAllocation) return ALLOC_FAILED;
+    return EXEC_FAILED;
+}
+
+// Warnings go to stderr unless SPARSE_LOG_ENABLE=0, the switch the reference's logger reads
+// (mcsparse/src/utils/mcsp_logger.cpp:29-61).
+void log_error(const char* msg) {
+    static const bool enabled = [] {
+        const char* v = std::getenv("SPARSE_LOG_ENABLE");
+        return !(v && v[0] == '0');
+    }();
+    if (enabled) std::fprintf(stderr, "[mcsparse] %s\n", msg);
+}
+
+bool value_type_known(macaDataType t) {
+    switch (t) {
+        case MACA_R_32F: case MACA_R_64F: case MACA_C_32F: case MACA_C_64F: case MACA_R_16F:
+        case MACA_R_16BF: case MACA_C_16F: case MACA_C_16BF: case MACA_R_8I:
+            return true;
+        default:
+            return false;
+    }
+}
+
+bool is_real_fp(macaDataType t) { return t == MACA_R_32F || t == MACA_R_64F; }
+size_t value_size(macaDataType t) { return t == MACA_R_64F ? 8 : 4; }
+bool too_big(int64_t v) { return (v >> 31) != 0; }  // int32 indices: every extent must fit
+
+bool descr_general(const mcsparseMatDescr* d) {
+    return d->type == MCSPARSE_MATRIX_TYPE_GENERAL && d->fill_mode == MCSPARSE_FILL_MODE_FULL &&
+           d->diag_type == MCSPARSE_DIAG_TYPE_NON_UNIT;
+}
+
+template <typename T>
+ScalarArg<T> scalar_arg(const mcsparseContext* h, const void* p) {
+    ScalarArg<T> a;
+    if (h->ptr_mode == MCSPARSE_POINTER_MODE_HOST) {
+        a.host = *static_cast<const T*>(p);
+        a.dev = nullptr;
+    } else {
+        a.host = T(0);
+        a.dev = static_cast<const T*>(p);
+    }
+    return a;
+}
+
+// Makes the handle's device current for the duration of a call.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+// ----------------------------------------------------------------------------- SpMV
+
+// Checks shared by bufferSize / preprocess / compute, in the reference's order
+// (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:690-720 and :309-336).
+St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
+              mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
+              bool need_buffer, const void* buffer, bool need_size_out, const void* size_out) {
+    if (h == nullptr) return BAD_HANDLE;
+    if (alpha == nullptr || beta == nullptr || A == nullptr || X == nullptr || Y == nullptr) return BAD_POINTER;
+    if (need_size_out && size_out == nullptr) return BAD_POINTER;
+    if (!(A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I)) return NOT_IMPL;
+    if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(X->size) || too_big(Y->size) ||
+        too_big(A->row_num + A->nnz))
+        return NOT_IMPL;
+    if (need_buffer && buffer == nullptr) return BAD_POINTER;
+    if (A->format != MCSPARSE_FORMAT_CSR) return NOT_IMPL;
+    const bool n_op = opA == MCSPARSE_OPERATION_NON_TRANSPOSE;
+    if (!((n_op && X->size == A->col_num && Y->size == A->row_num) ||
+          (!n_op && X->size == A->row_num && Y->size == A->col_num)))
+        return BAD_SIZE;
+    if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
+    if (!n_op) return NOT_IMPL;
+    if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType)) return NOT_IMPL;
+    if (!is_real_fp(computeType)) return NOT_IMPL;
+    return OK;
+}
+
+template <typename T>
+St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
+            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute) {
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T));
+    void* buf = align_up_256(buffer);
+    const int base = A->mat_descr->base;
+    const int32_t* rows = static_cast<const int32_t*>(A->rows);
+    if (analyse) {
+        cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
+        if (e != cudaSuccess) return from_cuda(e);
+    }
+    if (!compute) return OK;
+    cudaError_t e = spmv_tiled<T>(h->stream, A->row_num, A->nnz, base, rows, static_cast<const int32_t*>(A->cols),
+                                  static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
+                                  static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
+                                  buf);
+    return from_cuda(e);
+}
+
+St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
+              mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
+              void* buffer, bool preprocess_only) {
+    St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr);
+    if (st != OK) return st;
+    // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
+    if (A->rows == nullptr || A->cols == nullptr || A->vals == nullptr || X->values == nullptr ||
+        Y->values == nullptr || A->mat_descr == nullptr)
+        return BAD_POINTER;
+    if (!descr_general(A->mat_descr)) return NOT_IMPL;
+    DeviceGuard guard(h->device);
+    const int ipt = computeType == MACA_R_64F ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    bool analyse = true;
+    {
+        std::lock_guard<std::mutex> g(A->lock);
+        if (preprocess_only) {
+            A->analysed_buffer = buffer;
+            A->analysed_rows = A->rows;
+            A->analysed_items_per_tile = ipt;
+        } else if (A->analysed_buffer == buffer && A->analysed_rows == A->rows &&
+                   A->analysed_items_per_tile == ipt) {
+            analyse = false;
+        }
+    }
+    if (computeType == MACA_R_64F)
+        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only);
+    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only);
+}
+
+// Legacy csrmv family: raw arrays plus a matrix descriptor
+// (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:203-259 is the shared template).
+template <typename T>
+St csrmv_entry(mcsparseHandle_t h, mcsparseOperation_t transA, int m, int n, int nnz, const T* alpha,
+               const mcsparseMatDescr_t descr, const T* vals, const int* rows, const int* cols, const T* x,
+               const T* beta, T* y, void* buffer, bool has_buffer) {
+    if (h == nullptr) return BAD_HANDLE;
+    if (nnz < 0 || m < 0 || n < 0) return BAD_SIZE;
+    if (alpha == nullptr || beta == nullptr || rows == nullptr || cols == nullptr || vals == nullptr ||
+        x == nullptr || y == nullptr || descr == nullptr)
+        return BAD_POINTER;
+    if (!descr_general(descr)) return NOT_IMPL;
+    if (transA != MCSPARSE_OPERATION_NON_TRANSPOSE) return NOT_IMPL;
+    if (too_big(int64_t(m) + nnz)) return NOT_IMPL;
+    DeviceGuard guard(h->device);
+    const ScalarArg<T> a = scalar_arg<T>(h, alpha), b = scalar_arg<T>(h, beta);
+    if (has_buffer) {
+        if (buffer == nullptr) return BAD_POINTER;
+        const SpmvWorkspace ws = spmv_workspace(m, nnz, sizeof(T));
+        void* buf = align_up_256(buffer);
+        cudaError_t e = spmv_analysis(h->stream, m, nnz, descr->base, rows, ws, buf);
+        if (e != cudaSuccess) return from_cuda(e);
+        return from_cuda(spmv_tiled<T>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b, ws, buf));
+    }
+    return from_cuda(spmv_rowgroup<T>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b));
+}
+
+// ----------------------------------------------------------------------------- SpMM
+
+// mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:789-807 (compute) and :314-331 (bufferSize).
+St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t opB, const void* alpha,
+              mcsparseSpMatDescr_t A, mcsparseDnMatDescr_t B, const void* beta, mcsparseDnMatDescr_t C,
+              macaDataType computeType, bool need_buffer, const void* buffer) {
+    if (h == nullptr) return BAD_HANDLE;
+    if (A == nullptr || B == nullptr || C == nullptr || alpha == nullptr || beta == nullptr) return BAD_POINTER;
+    if (need_buffer && buffer == nullptr) return BAD_POINTER;
+    if (!(A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I)) return NOT_IMPL;
+    if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(B->row_num) ||
+        too_big(B->col_num) || too_big(B->ld) || too_big(C->row_num) || too_big(C->col_num) || too_big(C->ld))
+        return NOT_IMPL;
+    if (A->format != MCSPARSE_FORMAT_CSR) return NOT_IMPL;
+    if (!(computeType == A->valueType && computeType == C->valueType && computeType == B->valueType)) return NOT_IMPL;
+    if (!is_real_fp(computeType)) return NOT_IMPL;
+    if (opA != MCSPARSE_OPERATION_NON_TRANSPOSE) return NOT_IMPL;  // :105
+    if (opB == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
+    // Shapes: op(B) is A.cols x C.cols, C is A.rows x C.cols. The reference trusts the caller
+    // here; an inconsistent set would read out of bounds, so it is rejected instead.
+    const bool tB = opB == MCSPARSE_OPERATION_TRANSPOSE;
+    const int64_t opb_rows = tB ? B->col_num : B->row_num, opb_cols = tB ? B->row_num : B->col_num;
+    if (opb_rows != A->col_num || opb_cols != C->col_num || C->row_num != A->row_num) return BAD_SIZE;
+    if (B->ld < (B->order == MCSPARSE_ORDER_ROW ? B->col_num : B->row_num)) return BAD_SIZE;
+    if (C->ld < (C->order == MCSPARSE_ORDER_ROW ? C->col_num : C->row_num)) return BAD_SIZE;
+    return OK;
+}
+
+template <typename T>
+St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, mcsparseDnMatDescr* B,
+            mcsparseDnMatDescr* C, const void* alpha, const void* beta) {
+    int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
+    if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
+    const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
+    return from_cuda(spmm<T>(h->stream, A->row_num, C->col_num, A->mat_descr->base,
+                             static_cast<const int32_t*>(A->rows), static_cast<const int32_t*>(A->cols),
+                             static_cast<const T*>(A->vals), static_cast<const T*>(B->values), b_rs, b_cs,
+                             static_cast<T*>(C->values), c_rs, c_cs, scalar_arg<T>(h, alpha),
+                             scalar_arg<T>(h, beta)));
+}
+
+// Legacy csrmm / csrmm2: column-major B and C (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:19-80).
+template <typename T>
+St csrmm_entry(mcsparseHandle_t h, mcsparseOperation_t transA, mcsparseOperation_t transB, int m, int n, int k,
+               int nnz, const T* alpha, const mcsparseMatDescr_t descr, const T* vals, const int* rows,
+               const int* cols, const T* B, int ldb, const T* beta, T* C, int ldc) {
+    if (h == nullptr) return BAD_HANDLE;
+    if (m < 0 || n < 0 || k < 0 || nnz < 0) return BAD_SIZE;
+    if (alpha == nullptr || beta == nullptr || vals == nullptr || rows == nullptr || cols == nullptr ||
+        B == nullptr || C == nullptr || descr == nullptr)
+        return BAD_POINTER;
+    if (transA != MCSPARSE_OPERATION_NON_TRANSPOSE || !descr_general(descr)) return NOT_IMPL;
+    if (transB == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
+    DeviceGuard guard(h->device);
+    int64_t b_rs = 1, b_cs = ldb;
+    if (transB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
+    return from_cuda(spmm<T>(h->stream, m, n, descr->base, rows, cols, vals, B, b_rs, b_cs, C, 1, ldc,
+                             scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
+}
+
+}  // namespace
+
+extern "C" {
+
+// ----------------------------------------------------------------------------- handle
+
+mcsparseStatus_t mcsparseCreate(mcsparseHandle_t* handle) {
+    if (handle == nullptr) return pub(BAD_POINTER);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return MCSPARSE_STATUS_NOT_INITIALIZED;
+    mcsparseContext* ctx = new (std::nothrow) mcsparseContext();
+    if (ctx == nullptr) return MCSPARSE_STATUS_ALLOC_FAILED;
+    ctx->device = dev;
+    cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, dev);
+    *handle = ctx;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDestroy(mcsparseHandle_t handle) {
+    delete handle;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseGetVersion(mcsparseHandle_t handle, int* version) {
+    if (version == nullptr) return pub(BAD_POINTER);
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    *version = 1 * 1000000 + 0 * 1000 + 0;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseGetProperty(libraryPropertyType type, int* value) {
+    if (value == nullptr) return pub(BAD_POINTER);
+    switch (type) {
+        case MAJOR_VERSION: *value = 1; break;
+        case MINOR_VERSION: *value = 0; break;
+        case PATCH_LEVEL: *value = 0; break;
+        default: return pub(BAD_VALUE);
+    }
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+const char* mcsparseGetErrorName(mcsparseStatus_t status) {
+    switch (status) {
+        case MCSPARSE_STATUS_SUCCESS: return "MCSPARSE_STATUS_SUCCESS";
+        case MCSPARSE_STATUS_NOT_INITIALIZED: return "MCSPARSE_STATUS_NOT_INITIALIZED";
+        case MCSPARSE_STATUS_ALLOC_FAILED: return "MCSPARSE_STATUS_ALLOC_FAILED";
+        case MCSPARSE_STATUS_INVALID_VALUE: return "MCSPARSE_STATUS_INVALID_VALUE";
+        case MCSPARSE_STATUS_ARCH_MISMATCH: return "MCSPARSE_STATUS_ARCH_MISMATCH";
+        case MCSPARSE_STATUS_MAPPING_ERROR: return "MCSPARSE_STATUS_MAPPING_ERROR";
+        case MCSPARSE_STATUS_EXECUTION_FAILED: return "MCSPARSE_STATUS_EXECUTION_FAILED";
+        case MCSPARSE_STATUS_INTERNAL_ERROR: return "MCSPARSE_STATUS_INTERNAL_ERROR";
+        case MCSPARSE_STATUS_MATRIX_TYPE_NOT_SUPPORTED: return "MCSPARSE_STATUS_MATRIX_TYPE_NOT_SUPPORTED";
+        case MCSPARSE_STATUS_ZERO_PIVOT: return "MCSPARSE_STATUS_ZERO_PIVOT";
+        case MCSPARSE_STATUS_NOT_SUPPORTED: return "MCSPARSE_STATUS_NOT_SUPPORTED";
+        case MCSPARSE_STATUS_INSUFFICIENT_RESOURCES: return "MCSPARSE_STATUS_INSUFFICIENT_RESOURCES";
+        default: return "unrecognized error code";
+    }
+}
+
+const char* mcsparseGetErrorString(mcsparseStatus_t status) {
+    switch (status) {
+        case MCSPARSE_STATUS_SUCCESS: return "success";
+        case MCSPARSE_STATUS_NOT_INITIALIZED: return "initialization error";
+        case MCSPARSE_STATUS_ALLOC_FAILED: return "out of memory";
+        case MCSPARSE_STATUS_INVALID_VALUE: return "invalid value";
+        case MCSPARSE_STATUS_ARCH_MISMATCH: return "architecture mismatch";
+        case MCSPARSE_STATUS_MAPPING_ERROR: return "texture memory mapping error";
+        case MCSPARSE_STATUS_EXECUTION_FAILED: return "kernel launch failure";
+        case MCSPARSE_STATUS_INTERNAL_ERROR: return "internal error";
+        case MCSPARSE_STATUS_MATRIX_TYPE_NOT_SUPPORTED: return "matrix type not supported";
+        case MCSPARSE_STATUS_ZERO_PIVOT: return "zero pivot";
+        case MCSPARSE_STATUS_NOT_SUPPORTED: return "operation not supported";
+        case MCSPARSE_STATUS_INSUFFICIENT_RESOURCES: return "insufficient resources";
+        default: return "unrecognized error code";
+    }
+}
+
+mcsparseStatus_t mcsparseSetStream(mcsparseHandle_t handle, mcStream_t sid) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    handle->stream = sid;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseGetStream(const mcsparseHandle_t handle, mcStream_t* sid) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (sid == nullptr) return pub(BAD_POINTER);
+    *sid = handle->stream;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSetPointerMode(mcsparseHandle_t handle, mcsparsePointerMode_t pointer_mode) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    handle->ptr_mode = pointer_mode;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseGetPointerMode(const mcsparseHandle_t handle, mcsparsePointerMode_t* pointer_mode) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (pointer_mode == nullptr) return pub(BAD_POINTER);
+    *pointer_mode = handle->ptr_mode;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- legacy matrix descriptor
+
+mcsparseStatus_t mcsparseCreateMatDescr(mcsparseMatDescr_t* descr) {
+    if (descr == nullptr) return pub(BAD_POINTER);
+    *descr = new (std::nothrow) mcsparseMatDescr();
+    return *descr ? MCSPARSE_STATUS_SUCCESS : MCSPARSE_STATUS_INTERNAL_ERROR;
+}
+
+mcsparseStatus_t mcsparseDestroyMatDescr(mcsparseMatDescr_t descr) {
+    delete descr;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSetMatIndexBase(mcsparseMatDescr_t descr, mcsparseIndexBase_t index_base) {
+    if (descr == nullptr) return pub(BAD_POINTER);
+    if (index_base != MCSPARSE_INDEX_BASE_ZERO && index_base != MCSPARSE_INDEX_BASE_ONE) return pub(BAD_VALUE);
+    descr->base = index_base;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+mcsparseIndexBase_t mcsparseGetMatIndexBase(const mcsparseMatDescr_t descr) {
+    return descr ? descr->base : (mcsparseIndexBase_t)-1;
+}
+
+mcsparseStatus_t mcsparseSetMatType(mcsparseMatDescr_t descr, mcsparseMatrixType_t matrix_type) {
+    if (descr == nullptr) return pub(BAD_POINTER);
+    if ((int)matrix_type < 0 || (int)matrix_type > 3) return pub(BAD_VALUE);
+    descr->type = matrix_type;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+mcsparseMatrixType_t mcsparseGetMatType(const mcsparseMatDescr_t descr) {
+    return descr ? descr->type : (mcsparseMatrixType_t)-1;
+}
+
+mcsparseStatus_t mcsparseSetMatFillMode(mcsparseMatDescr_t descr, mcsparseFillMode_t mode) {
+    if (descr == nullptr) return pub(BAD_POINTER);
+    if ((int)mode < 0 || (int)mode > 2) return pub(BAD_VALUE);
+    descr->fill_mode = mode;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+mcsparseFillMode_t mcsparseGetMatFillMode(const mcsparseMatDescr_t descr) {
+    return descr ? descr->fill_mode : (mcsparseFillMode_t)-1;
+}
+
+mcsparseStatus_t mcsparseSetMatDiagType(mcsparseMatDescr_t descr, mcsparseDiagType_t diag_type) {
+    if (descr == nullptr) return pub(BAD_POINTER);
+    if ((int)diag_type < 0 || (int)diag_type > 1) return pub(BAD_VALUE);
+    descr->diag_type = diag_type;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+mcsparseDiagType_t mcsparseGetMatDiagType(const mcsparseMatDescr_t descr) {
+    return descr ? descr->diag_type : (mcsparseDiagType_t)-1;
+}
+
+// ----------------------------------------------------------------------------- dense vector
+
+mcsparseStatus_t mcsparseCreateDnVec(mcsparseDnVecDescr_t* dnVecDescr, int64_t size, void* values,
+                                     macaDataType valueType) {
+    if (size < 0) {
+        log_error("Wrong input size");
+        return pub(BAD_SIZE);
+    }
+    if (dnVecDescr == nullptr || values == nullptr) return pub(BAD_POINTER);
+    if (!(value_type_known(valueType) || valueType == MACA_R_32I)) return pub(NOT_IMPL);
+    mcsparseDnVecDescr* d = new (std::nothrow) mcsparseDnVecDescr();
+    if (d == nullptr) return MCSPARSE_STATUS_INTERNAL_ERROR;
+    d->size = size;
+    d->values = values;
+    d->valueType = valueType;
+    *dnVecDescr = d;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDestroyDnVec(mcsparseDnVecDescr_t dnVecDescr) {
+    delete dnVecDescr;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnVecGet(mcsparseDnVecDescr_t d, int64_t* size, void** values, macaDataType* valueType) {
+    if (d == nullptr || size == nullptr || values == nullptr || valueType == nullptr) return pub(BAD_POINTER);
+    *size = d->size;
+    *values = d->values;
+    *valueType = d->valueType;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnVecGetValues(mcsparseDnVecDescr_t d, void** values) {
+    if (d == nullptr || values == nullptr) return pub(BAD_POINTER);
+    *values = d->values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnVecSetValues(mcsparseDnVecDescr_t d, void* values) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    d->values = values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- CSR matrix
+
+mcsparseStatus_t mcsparseCreateCsr(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                   void* csrRowOffsets, void* csrColInd, void* csrValues,
+                                   mcsparseIndexType_t csrRowOffsetsType, mcsparseIndexType_t csrColIndType,
+                                   mcsparseIndexBase_t idxBase, macaDataType valueType) {
+    if (rows < 0 || cols < 0 || nnz < 0) {
+        log_error("Wrong input size");
+        return pub(BAD_SIZE);
+    }
+    if (!value_type_known(valueType)) return pub(NOT_IMPL);
+    if (spMatDescr == nullptr) return pub(BAD_POINTER);
+    if (idxBase != MCSPARSE_INDEX_BASE_ZERO && idxBase != MCSPARSE_INDEX_BASE_ONE) return pub(BAD_VALUE);
+    mcsparseSpMatDescr* d = new (std::nothrow) mcsparseSpMatDescr();
+    mcsparseMatDescr* md = new (std::nothrow) mcsparseMatDescr();
+    if (d == nullptr || md == nullptr) {
+        delete d;
+        delete md;
+        return MCSPARSE_STATUS_INTERNAL_ERROR;
+    }
+    d->format = MCSPARSE_FORMAT_CSR;
+    d->row_num = rows;
+    d->col_num = cols;
+    d->nnz = nnz;
+    d->rows = csrRowOffsets;
+    d->cols = csrColInd;
+    d->vals = csrValues;
+    d->rowIdxType = csrRowOffsetsType;
+    d->colIdxType = csrColIndType;
+    d->idxBase = idxBase;
+    d->valueType = valueType;
+    md->base = idxBase;
+    d->mat_descr = md;
+    *spMatDescr = d;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseCsrGet(mcsparseSpMatDescr_t d, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                void** csrRowOffsets, void** csrColInd, void** csrValues,
+                                mcsparseIndexType_t* csrRowOffsetsType, mcsparseIndexType_t* csrColIndType,
+                                mcsparseIndexBase_t* idxBase, macaDataType* valueType) {
+    if (d == nullptr || rows == nullptr || cols == nullptr || nnz == nullptr || csrRowOffsets == nullptr ||
+        csrColInd == nullptr || csrValues == nullptr || csrRowOffsetsType == nullptr || csrColIndType == nullptr ||
+        idxBase == nullptr || valueType == nullptr)
+        return pub(BAD_POINTER);
+    *rows = d->row_num;
+    *cols = d->col_num;
+    *nnz = d->nnz;
+    *csrRowOffsets = d->rows;
+    *csrColInd = d->cols;
+    *csrValues = d->vals;
+    *csrRowOffsetsType = d->rowIdxType;
+    *csrColIndType = d->colIdxType;
+    *idxBase = d->idxBase;
+    *valueType = d->valueType;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffsets, void* csrColInd,
+                                        void* csrValues) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    std::lock_guard<std::mutex> g(d->lock);
+    d->rows = csrRowOffsets;
+    d->cols = csrColInd;
+    d->vals = csrValues;
+    d->analysed_buffer = nullptr;
+    d->analysed_rows = nullptr;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDestroySpMat(mcsparseSpMatDescr_t d) {
+    if (d == nullptr) return MCSPARSE_STATUS_SUCCESS;
+    delete d->mat_descr;
+    delete d;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatGetSize(mcsparseSpMatDescr_t d, int64_t* rows, int64_t* cols, int64_t* nnz) {
+    if (d == nullptr || rows == nullptr || cols == nullptr || nnz == nullptr) return pub(BAD_POINTER);
+    *rows = d->row_num;
+    *cols = d->col_num;
+    *nnz = d->nnz;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatGetFormat(mcsparseSpMatDescr_t d, mcsparseFormat_t* format) {
+    if (d == nullptr || format == nullptr) return pub(BAD_POINTER);
+    *format = d->format;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatGetIndexBase(mcsparseSpMatDescr_t d, mcsparseIndexBase_t* idxBase) {
+    if (d == nullptr || idxBase == nullptr) return pub(BAD_POINTER);
+    *idxBase = d->idxBase;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatGetValues(mcsparseSpMatDescr_t d, void** values) {
+    if (d == nullptr || values == nullptr) return pub(BAD_POINTER);
+    *values = d->vals;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatSetValues(mcsparseSpMatDescr_t d, void* values) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    d->vals = values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatGetAttribute(mcsparseSpMatDescr_t d, mcsparseSpMatAttribute_t attribute, void* data,
+                                           size_t dataSize) {
+    (void)dataSize;
+    if (data == nullptr || d == nullptr || d->mat_descr == nullptr) return pub(BAD_POINTER);
+    if (attribute == MCSPARSE_SPMAT_FILL_MODE)
+        std::memcpy(data, &d->mat_descr->fill_mode, sizeof(d->mat_descr->fill_mode));
+    else if (attribute == MCSPARSE_SPMAT_DIAG_TYPE)
+        std::memcpy(data, &d->mat_descr->diag_type, sizeof(d->mat_descr->diag_type));
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMatSetAttribute(mcsparseSpMatDescr_t d, mcsparseSpMatAttribute_t attribute,
+                                           const void* data, size_t dataSize) {
+    (void)dataSize;
+    if (data == nullptr || d == nullptr || d->mat_descr == nullptr) return pub(BAD_POINTER);
+    if (attribute == MCSPARSE_SPMAT_FILL_MODE)
+        std::memcpy(&d->mat_descr->fill_mode, data, sizeof(d->mat_descr->fill_mode));
+    else if (attribute == MCSPARSE_SPMAT_DIAG_TYPE)
+        std::memcpy(&d->mat_descr->diag_type, data, sizeof(d->mat_descr->diag_type));
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- dense matrix
+
+mcsparseStatus_t mcsparseCreateDnMat(mcsparseDnMatDescr_t* dnMatDescr, int64_t rows, int64_t cols, int64_t ld,
+                                     void* values, macaDataType valueType, mcsparseOrder_t order) {
+    if (rows < 0 || cols < 0 || ld < 0) {
+        log_error("Wrong input size");
+        return pub(BAD_SIZE);
+    }
+    if (!(value_type_known(valueType) || valueType == MACA_R_32I)) {
+        log_error("Dense matrix data type not supported");
+        return pub(NOT_IMPL);
+    }
+    if (dnMatDescr == nullptr || values == nullptr) return pub(BAD_POINTER);
+    if (order != MCSPARSE_ORDER_ROW && order != MCSPARSE_ORDER_COL) return pub(BAD_VALUE);
+    mcsparseDnMatDescr* d = new (std::nothrow) mcsparseDnMatDescr();
+    if (d == nullptr) return MCSPARSE_STATUS_INTERNAL_ERROR;
+    d->row_num = rows;
+    d->col_num = cols;
+    d->ld = ld;
+    d->values = values;
+    d->valueType = valueType;
+    d->order = order;
+    *dnMatDescr = d;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDestroyDnMat(mcsparseDnMatDescr_t d) {
+    delete d;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnMatGet(mcsparseDnMatDescr_t d, int64_t* rows, int64_t* cols, int64_t* ld, void** values,
+                                  macaDataType* type, mcsparseOrder_t* order) {
+    if (d == nullptr || rows == nullptr || cols == nullptr || ld == nullptr || values == nullptr ||
+        type == nullptr || order == nullptr)
+        return pub(BAD_POINTER);
+    *rows = d->row_num;
+    *cols = d->col_num;
+    *ld = d->ld;
+    *values = d->values;
+    *type = d->valueType;
+    *order = d->order;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnMatGetValues(mcsparseDnMatDescr_t d, void** values) {
+    if (d == nullptr || values == nullptr) return pub(BAD_POINTER);
+    *values = d->values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnMatSetValues(mcsparseDnMatDescr_t d, void* values) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    d->values = values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- SpMV
+
+mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                         mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                         mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                         mcsparseSpMVAlg_t alg, size_t* bufferSize) {
+    (void)alg;
+    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize);
+    if (st != OK) return pub(st);
+    // Work partition + carries, plus slack to align the caller's pointer to 256 bytes.
+    *bufferSize = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType)).bytes + 256;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMV_preprocess(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                         mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                         mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                         mcsparseSpMVAlg_t alg, void* externalBuffer) {
+    (void)alg;
+    return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, true));
+}
+
+mcsparseStatus_t mcsparseSpMV(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                              mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                              mcsparseDnVecDescr_t vecY, macaDataType computeType, mcsparseSpMVAlg_t alg,
+                              void* externalBuffer) {
+    (void)alg;
+    return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false));
+}
+
+mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* externalBuffer, int* itemsPerTile,
+                                               int64_t* numTiles, const int32_t** tileStarts) {
+    if (matA == nullptr || externalBuffer == nullptr || itemsPerTile == nullptr || numTiles == nullptr ||
+        tileStarts == nullptr)
+        return pub(BAD_POINTER);
+    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType));
+    *itemsPerTile = ws.items_per_tile;
+    *numTiles = ws.num_tiles;
+    *tileStarts = static_cast<const int32_t*>(align_up_256(externalBuffer));
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- SpMM
+
+mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperation_t opA, mcsparseOperation_t opB,
+                                         const void* alpha, mcsparseSpMatDescr_t matA, mcsparseDnMatDescr_t matB,
+                                         const void* beta, mcsparseDnMatDescr_t matC, macaDataType computeType,
+                                         mcsparseSpMMAlg_t alg, size_t* bufferSize) {
+    (void)alg;
+    St st = spmm_check(handle, opA, opB, alpha, matA, matB, beta, matC, computeType, false, nullptr);
+    if (st != OK) return pub(st);
+    if (bufferSize == nullptr) return pub(BAD_POINTER);
+    *bufferSize = 128;  // MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15)
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperation_t opA, mcsparseOperation_t opB,
+                                         const void* alpha, mcsparseSpMatDescr_t matA, mcsparseDnMatDescr_t matB,
+                                         const void* beta, mcsparseDnMatDescr_t matC, macaDataType computeType,
+                                         mcsparseSpMMAlg_t alg, void* externalBuffer) {
+    // The reference returns success without looking at any argument
+    // (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:965-970); so does this build, which
+    // needs no per-matrix state for SpMM.
+    (void)handle; (void)opA; (void)opB; (void)alpha; (void)matA; (void)matB; (void)beta; (void)matC;
+    (void)computeType; (void)alg; (void)externalBuffer;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, mcsparseOperation_t opB,
+                              const void* alpha, mcsparseSpMatDescr_t matA, mcsparseDnMatDescr_t matB,
+                              const void* beta, mcsparseDnMatDescr_t matC, macaDataType computeType,
+                              mcsparseSpMMAlg_t alg, void* externalBuffer) {
+    (void)alg;
+    St st = spmm_check(handle, opA, opB, alpha, matA, matB, beta, matC, computeType, true, externalBuffer);
+    if (st != OK) return pub(st);
+    if (matA->rows == nullptr || matA->cols == nullptr || matA->vals == nullptr || matB->values == nullptr ||
+        matC->values == nullptr || matA->mat_descr == nullptr)
+        return pub(BAD_POINTER);
+    if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
+    DeviceGuard guard(handle->device);
+    if (computeType == MACA_R_64F) return pub(spmm_run<double>(handle, opB, matA, matB, matC, alpha, beta));
+    return pub(spmm_run<float>(handle, opB, matA, matB, matC, alpha, beta));
+}
+
+// ----------------------------------------------------------------------------- legacy entry points
+
+mcsparseStatus_t mcsparseScsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const float* alpha, const mcsparseMatDescr_t descrA, const float* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const float* x, const float* beta,
+                                float* y) {
+    return pub(csrmv_entry<float>(handle, transA, m, n, nnz, alpha, descrA, csrValA, csrRowPtrA, csrColIndA, x, beta,
+                                  y, nullptr, false));
+}
+
+mcsparseStatus_t mcsparseDcsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const double* alpha, const mcsparseMatDescr_t descrA, const double* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const double* x, const double* beta,
+                                double* y) {
+    return pub(csrmv_entry<double>(handle, transA, m, n, nnz, alpha, descrA, csrValA, csrRowPtrA, csrColIndA, x,
+                                   beta, y, nullptr, false));
+}
+
+static bool csrmvex_types_equal(macaDataType a, macaDataType v, macaDataType x, macaDataType b, macaDataType y,
+                                macaDataType e) {
+    return a == x && v == x && b == x && y == x && e == x;  // mcsp_spmv_gpu.cpp:911-914
+}
+
+mcsparseStatus_t mcsparseCsrmvEx_bufferSize(mcsparseHandle_t handle, mcsparseAlgMode_t alg,
+                                            mcsparseOperation_t transA, int m, int n, int nnz, const void* alpha,
+                                            macaDataType alphatype, const mcsparseMatDescr_t descrA,
+                                            const void* csrValA, macaDataType csrValAtype, const int* csrRowPtrA,
+                                            const int* csrColIndA, const void* x, macaDataType xtype,
+                                            const void* beta, macaDataType betatype, void* y, macaDataType ytype,
+                                            macaDataType executiontype, size_t* bufferSizeInBytes) {
+    (void)alg; (void)transA; (void)n; (void)alpha; (void)descrA; (void)csrValA; (void)csrRowPtrA;
+    (void)csrColIndA; (void)x; (void)beta; (void)y;
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (bufferSizeInBytes == nullptr) return pub(BAD_POINTER);
+    if (m < 0 || nnz < 0) return pub(BAD_SIZE);
+    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_real_fp(xtype))
+        return pub(NOT_IMPL);
+    *bufferSizeInBytes = spmv_workspace(m, nnz, value_size(xtype)).bytes + 256;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseCsrmvEx(mcsparseHandle_t handle, mcsparseAlgMode_t alg, mcsparseOperation_t transA, int m,
+                                 int n, int nnz, const void* alpha, macaDataType alphatype,
+                                 const mcsparseMatDescr_t descrA, const void* csrValA, macaDataType csrValAtype,
+                                 const int* csrRowPtrA, const int* csrColIndA, const void* x, macaDataType xtype,
+                                 const void* beta, macaDataType betatype, void* y, macaDataType ytype,
+                                 macaDataType executiontype, void* buffer) {
+    (void)alg;
+    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_real_fp(xtype))
+        return pub(NOT_IMPL);
+    if (xtype == MACA_R_64F)
+        return pub(csrmv_entry<double>(handle, transA, m, n, nnz, static_cast<const double*>(alpha), descrA,
+                                       static_cast<const double*>(csrValA), csrRowPtrA, csrColIndA,
+                                       static_cast<const double*>(x), static_cast<const double*>(beta),
+                                       static_cast<double*>(y), buffer, true));
+    return pub(csrmv_entry<float>(handle, transA, m, n, nnz, static_cast<const float*>(alpha), descrA,
+                                  static_cast<const float*>(csrValA), csrRowPtrA, csrColIndA,
+                                  static_cast<const float*>(x), static_cast<const float*>(beta),
+                                  static_cast<float*>(y), buffer, true));
+}
+
+mcsparseStatus_t mcsparseScsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const float* alpha, const mcsparseMatDescr_t descrA,
+                                 const float* csrValA, const int* csrRowPtrA, const int* csrColIndA, const float* B,
+                                 int ldb, const float* beta, float* C, int ldc) {
+    return pub(csrmm_entry<float>(handle, transA, transB, m, n, k, nnz, alpha, descrA, csrValA, csrRowPtrA,
+                                  csrColIndA, B, ldb, beta, C, ldc));
+}
+
+mcsparseStatus_t mcsparseDcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const double* alpha,
+                                 const mcsparseMatDescr_t descrA, const double* csrValA, const int* csrRowPtrA,
+                                 const int* csrColIndA, const double* B, int ldb, const double* beta, double* C,
+                                 int ldc) {
+    return pub(csrmm_entry<double>(handle, transA, transB, m, n, k, nnz, alpha, descrA, csrValA, csrRowPtrA,
+                                   csrColIndA, B, ldb, beta, C, ldc));
+}
+
+mcsparseStatus_t mcsparseScsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const float* alpha, const mcsparseMatDescr_t descrA, const float* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const float* B, int ldb,
+                                const float* beta, float* C, int ldc) {
+    return pub(csrmm_entry<float>(handle, transA, MCSPARSE_OPERATION_NON_TRANSPOSE, m, n, k, nnz, alpha, descrA,
+                                  csrValA, csrRowPtrA, csrColIndA, B, ldb, beta, C, ldc));
+}
+
+mcsparseStatus_t mcsparseDcsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const double* alpha, const mcsparseMatDescr_t descrA, const double* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const double* B, int ldb,
+                                const double* beta, double* C, int ldc) {
+    return pub(csrmm_entry<double>(handle, transA, MCSPARSE_OPERATION_NON_TRANSPOSE, m, n, k, nnz, alpha, descrA,
+                                   csrValA, csrRowPtrA, csrColIndA, B, ldb, beta, C, ldc));
+}
+
+// ----------------------------------------------------------------------------- sharding helpers
+
+mcsparseStatus_t mcsparseB200ShardRowBounds(mcsparseHandle_t handle, int64_t rows, int64_t nnz,
+                                            mcsparseIndexBase_t idxBase, const int32_t* rowOffsets, int numShards,
+                                            int64_t* bounds) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (rowOffsets == nullptr || bounds == nullptr) return pub(BAD_POINTER);
+    if (rows < 0 || nnz < 0 || numShards < 1 || too_big(rows) || too_big(nnz)) return pub(BAD_SIZE);
+    DeviceGuard guard(handle->device);
+    return pub(from_cuda(shard_row_bounds(handle->stream, rows, nnz, idxBase, rowOffsets, numShards, bounds)));
+}
+
+mcsparseStatus_t mcsparseB200ShardLocalRowOffsets(mcsparseHandle_t handle, const int32_t* rowOffsets,
+                                                  int64_t firstRow, int64_t numRows, mcsparseIndexBase_t idxBase,
+                                                  int32_t* localOffsets) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (rowOffsets == nullptr || localOffsets == nullptr) return pub(BAD_POINTER);
+    if (firstRow < 0 || numRows < 0) return pub(BAD_SIZE);
+    DeviceGuard guard(handle->device);
+    return pub(from_cuda(
+        shard_local_row_offsets(handle->stream, rowOffsets, firstRow, numRows, idxBase, localOffsets)));
+}
+
+}  // extern "C"

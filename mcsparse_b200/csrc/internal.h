@@ -1,0 +1,107 @@
+// Internal declarations shared by the host API (api.cpp) and the CUDA translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <mutex>
+
+#include "mcsparse.h"
+
+// Descriptor payloads. Field meaning follows the reference's structs
+// (mcsparse/src/include/mcsp_internal_types.h:86-92,127-145,184-223 and
+// mcsparse/src/include/mcsp_handle.h:11-27) minus everything the CSR path never reads.
+struct mcsparseContext {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    mcsparsePointerMode_t ptr_mode = MCSPARSE_POINTER_MODE_HOST;
+};
+
+struct mcsparseMatDescr {
+    mcsparseMatrixType_t type = MCSPARSE_MATRIX_TYPE_GENERAL;
+    mcsparseFillMode_t fill_mode = MCSPARSE_FILL_MODE_FULL;
+    mcsparseDiagType_t diag_type = MCSPARSE_DIAG_TYPE_NON_UNIT;
+    mcsparseStorageMode_t storage_mode = MCSPARSE_STORAGE_MODE_SORTED;
+    mcsparseIndexBase_t base = MCSPARSE_INDEX_BASE_ZERO;
+};
+
+struct mcsparseSpMatDescr {
+    mcsparseFormat_t format = MCSPARSE_FORMAT_CSR;
+    int64_t row_num = 0, col_num = 0, nnz = 0;
+    void* rows = nullptr;  // row offsets (device)
+    void* cols = nullptr;  // column indices (device)
+    void* vals = nullptr;  // values (device)
+    mcsparseIndexType_t rowIdxType = MCSPARSE_INDEX_32I, colIdxType = MCSPARSE_INDEX_32I;
+    mcsparseIndexBase_t idxBase = MCSPARSE_INDEX_BASE_ZERO;
+    macaDataType valueType = MACA_R_32F;
+    mcsparseMatDescr* mat_descr = nullptr;
+    // Analysis recorded by mcsparseSpMV_preprocess: which buffer holds the partition of
+    // which row-offset array. Guarded by `lock`; cleared by mcsparseCsrSetPointers.
+    std::mutex lock;
+    void* analysed_buffer = nullptr;
+    const void* analysed_rows = nullptr;
+    int analysed_items_per_tile = 0;
+};
+
+struct mcsparseDnVecDescr {
+    int64_t size = 0;
+    void* values = nullptr;
+    macaDataType valueType = MACA_R_32F;
+};
+
+struct mcsparseDnMatDescr {
+    int64_t row_num = 0, col_num = 0, ld = 0;
+    void* values = nullptr;
+    macaDataType valueType = MACA_R_32F;
+    mcsparseOrder_t order = MCSPARSE_ORDER_COL;
+};
+
+namespace mcsp_b200 {
+
+// alpha / beta as the kernels receive them: a host value, or a device address to read.
+template <typename T>
+struct ScalarArg {
+    T host;
+    const T* dev;
+#ifdef __CUDACC__
+    __device__ __forceinline__ T get() const { return dev ? *dev : host; }
+#endif
+};
+
+// Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
+//   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles]
+struct SpmvWorkspace {
+    int items_per_tile = 0;
+    int64_t num_tiles = 0;
+    size_t off_carry_row = 0, off_carry_val = 0, bytes = 0;
+};
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size);
+inline void* align_up_256(void* p) {
+    return reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255));
+}
+
+cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                          const SpmvWorkspace& ws, void* buf);
+template <typename T>
+cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                       const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
+                       const SpmvWorkspace& ws, void* buf);
+template <typename T>
+cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                          const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,
+                          ScalarArg<T> beta);
+
+// Dense operand addressed as element(r, c) = ptr[r * row_stride + c * col_stride].
+template <typename T>
+cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
+                 const T* val, const T* B, int64_t b_row_stride, int64_t b_col_stride, T* C, int64_t c_row_stride,
+                 int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta);
+
+cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                             int num_shards, int64_t* bounds_host);
+cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,
+                                    int base, int32_t* local);
+
+}  // namespace mcsp_b200

@@ -1,0 +1,67 @@
+// Row-block sharding helpers for running one CSR matrix on several GPUs.
+// The reference is single-device (mcsparse/src/common/mcsp_handle.cpp:5-8); these kernels
+// have no counterpart there. Their CPU restatement is the bit-exact check.
+#include "internal.h"
+
+namespace mcsp_b200 {
+
+namespace {
+
+// bounds[g] = first row r with row_ptr[r] - base >= floor(g * nnz / G); bounds[0] = 0, bounds[G] = m.
+__global__ void shard_row_bounds_kernel(long long m, long long nnz, int base, const int* __restrict__ row_ptr,
+                                        int num_shards, long long* __restrict__ bounds) {
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    if (g > num_shards) return;
+    if (g == 0) {
+        bounds[0] = 0;
+        return;
+    }
+    if (g == num_shards) {
+        bounds[g] = m;
+        return;
+    }
+    // g * nnz < 2^31 * 2^31: fits in 64 bits.
+    const long long target = (long long)(((unsigned long long)g * (unsigned long long)nnz) / (unsigned)num_shards);
+    long long lo = 0, hi = m;
+    while (lo < hi) {
+        const long long mid = (lo + hi) >> 1;
+        if ((long long)__ldg(row_ptr + mid) - base < target)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    bounds[g] = lo;
+}
+
+__global__ void shard_local_row_offsets_kernel(const int* __restrict__ row_ptr, long long first_row,
+                                               long long num_rows, int base, int* __restrict__ local) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i > num_rows) return;
+    local[i] = __ldg(row_ptr + first_row + i) - __ldg(row_ptr + first_row) + base;
+}
+
+}  // namespace
+
+cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                             int num_shards, int64_t* bounds_host) {
+    long long* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, sizeof(long long) * (num_shards + 1));
+    if (e != cudaSuccess) return e;
+    shard_row_bounds_kernel<<<(num_shards + 1 + 63) / 64, 64, 0, s>>>(m, nnz, base, row_ptr, num_shards, d);
+    e = cudaGetLastError();
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(bounds_host, d, sizeof(long long) * (num_shards + 1), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(d);
+    return e;
+}
+
+cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,
+                                    int base, int32_t* local) {
+    const int threads = 256;
+    shard_local_row_offsets_kernel<<<(unsigned)((num_rows + 1 + threads - 1) / threads), threads, 0, s>>>(
+        row_ptr, first_row, num_rows, base, local);
+    return cudaGetLastError();
+}
+
+}  // namespace mcsp_b200

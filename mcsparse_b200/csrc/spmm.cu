@@ -1,0 +1,192 @@
+// CSR SpMM for sm_100a: C = alpha * A * B + beta * C.
+//
+// Replaces mcspBatchedSpmmCsrNnKernel (mcsparse/src/kernels/level3/spmm/csr_spmm_device.hpp:91-167,
+// launched from mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:82-162). The reference runs one
+// warp per (row, C column), re-reading A's row for every column, and needs B column-major, so a
+// row-major B is first transposed into a temporary allocation. Here a row of A is read once
+// and every nonzero is applied to a whole row of B with 128-bit loads; row-major B and C are
+// used in place. No temporary memory, no stream synchronisation.
+#include "internal.h"
+
+namespace mcsp_b200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+struct VecOf;
+template <>
+struct VecOf<float> {
+    using type = float4;
+    static constexpr int W = 4;
+};
+template <>
+struct VecOf<double> {
+    using type = double2;
+    static constexpr int W = 2;
+};
+
+__device__ __forceinline__ void fma_vec(float4& acc, float a, const float4& b) {
+    acc.x = fmaf(a, b.x, acc.x);
+    acc.y = fmaf(a, b.y, acc.y);
+    acc.z = fmaf(a, b.z, acc.z);
+    acc.w = fmaf(a, b.w, acc.w);
+}
+__device__ __forceinline__ void fma_vec(double2& acc, double a, const double2& b) {
+    acc.x = fma(a, b.x, acc.x);
+    acc.y = fma(a, b.y, acc.y);
+}
+__device__ __forceinline__ float4 axpby(float alpha, const float4& a, float beta, const float4& c) {
+    return make_float4(alpha * a.x + beta * c.x, alpha * a.y + beta * c.y, alpha * a.z + beta * c.z,
+                       alpha * a.w + beta * c.w);
+}
+__device__ __forceinline__ double2 axpby(double alpha, const double2& a, double beta, const double2& c) {
+    return make_double2(alpha * a.x + beta * c.x, alpha * a.y + beta * c.y);
+}
+__device__ __forceinline__ float4 scale(float alpha, const float4& a) {
+    return make_float4(alpha * a.x, alpha * a.y, alpha * a.z, alpha * a.w);
+}
+__device__ __forceinline__ double2 scale(double alpha, const double2& a) {
+    return make_double2(alpha * a.x, alpha * a.y);
+}
+template <typename V>
+__device__ __forceinline__ V zero_vec();
+template <>
+__device__ __forceinline__ float4 zero_vec<float4>() {
+    return make_float4(0.f, 0.f, 0.f, 0.f);
+}
+template <>
+__device__ __forceinline__ double2 zero_vec<double2>() {
+    return make_double2(0.0, 0.0);
+}
+
+// ---------------------------------------------------------------------------------------
+// K3: row-major SpMM. G lanes form a group that owns one row of A and a slab of G * W
+// consecutive columns of C (W = 4 floats or 2 doubles per lane: one 128-bit access). The
+// group loads G (col, val) pairs of the row with one coalesced access, then broadcasts them
+// lane by lane with shuffles; each broadcast nonzero costs one 128-bit load of B per lane
+// and W FMAs. The loop over the G nonzeros is unrolled so several B rows are in flight.
+// B rows are fetched with default caching: B is the operand with reuse (through L2).
+// ---------------------------------------------------------------------------------------
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads)
+    spmm_rowmajor_kernel(int m, int n, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+                         const T* __restrict__ val, const T* __restrict__ B, long long ldb, T* __restrict__ C,
+                         long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
+    using V = typename VecOf<T>::type;
+    constexpr int W = VecOf<T>::W;
+    const int lane = threadIdx.x & (G - 1);
+    const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / G;
+    const int c0 = (blockIdx.y * G + lane) * W;  // first column of this lane
+    const bool row_ok = row < m;                 // uniform within a group
+    const bool col_ok = c0 < n;
+    // Shuffles below use the full-warp mask with width G: all 32 lanes always execute them.
+    int j0 = 0, j1 = 0;
+    if (row_ok) {
+        j0 = __ldg(row_ptr + row) - base;
+        j1 = __ldg(row_ptr + row + 1) - base;
+    }
+    V acc = zero_vec<V>();
+    const T* const Bc = B + c0 - (long long)base * ldb;
+    // Groups of one warp may have different trip counts; width-G shuffles only need the
+    // lanes of the same group to be converged, which the group-uniform bounds guarantee.
+    for (int j = j0; j < j1; j += G) {
+        int cj = 0;
+        T vj = T(0);
+        if (j + lane < j1) {
+            cj = __ldcs(col + j + lane);
+            vj = __ldcs(val + j + lane);
+        }
+        const int cnt = min(G, j1 - j);
+        const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) & ~(G - 1)));
+#pragma unroll 8
+        for (int q = 0; q < cnt; ++q) {
+            const int cq = __shfl_sync(gmask, cj, q, G);
+            const T vq = __shfl_sync(gmask, vj, q, G);
+            if (col_ok) {
+                const V b = *reinterpret_cast<const V*>(Bc + (long long)cq * ldb);
+                fma_vec(acc, vq, b);
+            }
+        }
+    }
+    if (row_ok && col_ok) {
+        const T alpha = alpha_arg.get(), beta = beta_arg.get();
+        V* out = reinterpret_cast<V*>(C + row * ldc + c0);
+        *out = (beta != T(0)) ? axpby(alpha, acc, beta, *out) : scale(alpha, acc);
+    }
+}
+
+// Any layout, any n: one thread per C element, addressed through (row, col) strides.
+// Consecutive threads run along C's contiguous dimension.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    spmm_strided_kernel(long long m, long long n, int base, const int* __restrict__ row_ptr,
+                        const int* __restrict__ col, const T* __restrict__ val, const T* __restrict__ B,
+                        long long b_rs, long long b_cs, T* __restrict__ C, long long c_rs, long long c_cs,
+                        ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
+    const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (idx >= m * n) return;
+    long long r, c;
+    if (c_cs == 1) {
+        r = idx / n;
+        c = idx - r * n;
+    } else {
+        c = idx / m;
+        r = idx - c * m;
+    }
+    const int j0 = __ldg(row_ptr + r) - base, j1 = __ldg(row_ptr + r + 1) - base;
+    T sum = T(0);
+    for (int j = j0; j < j1; ++j) sum += __ldg(val + j) * __ldg(B + (long long)(__ldg(col + j) - base) * b_rs + c * b_cs);
+    const T alpha = alpha_arg.get(), beta = beta_arg.get();
+    T* out = C + r * c_rs + c * c_cs;
+    T v = alpha * sum;
+    if (beta != T(0)) v += beta * *out;
+    *out = v;
+}
+
+template <typename T, int G>
+cudaError_t launch_rowmajor(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr,
+                            const int32_t* col, const T* val, const T* B, int64_t ldb, T* C, int64_t ldc,
+                            ScalarArg<T> alpha, ScalarArg<T> beta) {
+    constexpr int W = VecOf<T>::W;
+    const long long threads_total = m * G;
+    dim3 grid((unsigned)((threads_total + kThreads - 1) / kThreads), (unsigned)((n + G * W - 1) / (G * W)));
+    spmm_rowmajor_kernel<T, G><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C, ldc,
+                                                         alpha, beta);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+template <typename T>
+cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
+                 const T* val, const T* B, int64_t b_rs, int64_t b_cs, T* C, int64_t c_rs, int64_t c_cs,
+                 ScalarArg<T> alpha, ScalarArg<T> beta) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    constexpr int W = VecOf<T>::W;
+    const bool vec_ok = b_cs == 1 && c_cs == 1 && n % W == 0 && b_rs % W == 0 && c_rs % W == 0 &&
+                        ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+    if (vec_ok) {
+        const int64_t lanes = n / W;
+        if (lanes <= 2) return launch_rowmajor<T, 2>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 4) return launch_rowmajor<T, 4>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 8) return launch_rowmajor<T, 8>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 16)
+            return launch_rowmajor<T, 16>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        return launch_rowmajor<T, 32>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+    }
+    const long long total = m * n;
+    spmm_strided_kernel<T><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, s>>>(
+        m, n, base, row_ptr, col, val, B, b_rs, b_cs, C, c_rs, c_cs, alpha, beta);
+    return cudaGetLastError();
+}
+
+template cudaError_t spmm<float>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, const float*,
+                                 const float*, int64_t, int64_t, float*, int64_t, int64_t, ScalarArg<float>,
+                                 ScalarArg<float>);
+template cudaError_t spmm<double>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
+                                  const double*, const double*, int64_t, int64_t, double*, int64_t, int64_t,
+                                  ScalarArg<double>, ScalarArg<double>);
+
+}  // namespace mcsp_b200

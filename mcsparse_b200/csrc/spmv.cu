@@ -1,0 +1,383 @@
+// CSR SpMV for sm_100a: merge-path analysis, tiled kernel, carry fix-up, row-group kernel.
+//
+// Replaces the reference's one-warp-per-row kernel
+// (mcsparse/src/kernels/level2/spmv/csr_vector_device.hpp:22-79, launched from
+// mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:203-259) with the same arithmetic
+// y[r] = beta * y[r] + alpha * sum_j val[j] * x[col[j] - base].
+//
+// The path is HBM-bound: each nonzero moves sizeof(T) + 4 bytes once, so the kernels are
+// organised around wide, coalesced, streaming loads of col/val with many bytes in flight
+// per SM, while x is gathered through L1/L2 with default caching.
+#include <cstdio>
+
+#include "internal.h"
+
+namespace mcsp_b200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+struct TileCfg;
+template <>
+struct TileCfg<float> {
+    static constexpr int kItemsPerThread = MCSPARSE_B200_SPMV_TILE_ITEMS_F32 / kThreads;
+};
+template <>
+struct TileCfg<double> {
+    static constexpr int kItemsPerThread = MCSPARSE_B200_SPMV_TILE_ITEMS_F64 / kThreads;
+};
+
+// ---------------------------------------------------------------------------------------
+// K0: merge-path analysis. Thread t finds where diagonal min(t * items_per_tile, m + nnz)
+// crosses the merge of row ends and nonzero indices. Same search, same tie-break (a row end
+// equal to a nonzero index is taken first) as the CPU partition it is checked against.
+// ---------------------------------------------------------------------------------------
+__global__ void merge_path_partition_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr,
+                                            int items_per_tile, long long num_tiles, int2* __restrict__ starts) {
+    long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t > num_tiles) return;
+    long long items = (long long)m + nnz;
+    long long diag = t * items_per_tile;
+    if (diag > items) diag = items;
+    long long lo = diag > nnz ? diag - nnz : 0;
+    long long hi = diag < m ? diag : m;
+    while (lo < hi) {
+        long long mid = (lo + hi) >> 1;
+        if ((long long)__ldg(row_ptr + mid + 1) - base <= diag - mid - 1)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    starts[t] = make_int2((int)lo, (int)(diag - lo));
+}
+
+// ---------------------------------------------------------------------------------------
+// Streaming 4-element loads of the matrix arrays (evict-first: A is read exactly once and
+// must not push x out of L2).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+struct Quad;
+template <>
+struct Quad<float> {
+    float4 v;
+    __device__ __forceinline__ void load(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ float get(int i) const { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+    __device__ __forceinline__ static void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <>
+struct Quad<double> {
+    double2 lo, hi;
+    __device__ __forceinline__ void load(const double* p) {
+        lo = __ldcs(reinterpret_cast<const double2*>(p));
+        hi = __ldcs(reinterpret_cast<const double2*>(p) + 1);
+    }
+    __device__ __forceinline__ double get(int i) const { return i == 0 ? lo.x : i == 1 ? lo.y : i == 2 ? hi.x : hi.y; }
+    __device__ __forceinline__ static void store(double* p, double a, double b, double c, double d) {
+        reinterpret_cast<double2*>(p)[0] = make_double2(a, b);
+        reinterpret_cast<double2*>(p)[1] = make_double2(c, d);
+    }
+};
+
+// ---------------------------------------------------------------------------------------
+// K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
+// `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
+//   phase 1  128-bit coalesced loads of col/val, gather x, products -> shared memory
+//   phase 2  each thread walks IPT consecutive merge items over the shared products
+//            (sequential sum per row segment, row totals into shared y slots)
+//   phase 3  thread carries (a row open at a thread boundary) are combined with a
+//            warp-shuffle segmented scan, then across the 8 warps in a fixed order
+//   phase 4  coalesced epilogue y = alpha * s + beta * y for the rows that end in the tile;
+//            the sum of the row still open at the tile's end goes to carry_{row,val}[t]
+// No atomics: every addition has a fixed place, so results are reproducible run to run.
+// VEC = false is the same kernel with scalar loads for arrays that are not 16-byte aligned.
+// ---------------------------------------------------------------------------------------
+template <typename T, int THREADS, int IPT, bool VEC>
+__global__ void __launch_bounds__(THREADS)
+    spmv_tile_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+                     const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
+                     ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
+                     T* __restrict__ carry_val) {
+    constexpr int TILE = THREADS * IPT;
+    constexpr int NWARPS = THREADS / 32;
+    constexpr int CPT = IPT / 4;  // 4-element chunks per thread in the unrolled pass
+    static_assert(IPT % 4 == 0, "items per thread must be a multiple of 4");
+
+    __shared__ __align__(32) T s_buf[TILE + 8];  // products, then the row sums behind them
+    __shared__ int s_row_end[TILE + 4];
+    __shared__ int s_warp_row[NWARPS];
+    __shared__ T s_warp_sum[NWARPS];
+
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x;
+    const int2 s0 = tile_starts[t];
+    const int2 s1 = tile_starts[t + 1];
+    const int row_s = s0.x, nz_s = s0.y;
+    const int nrows = s1.x - s0.x;
+    const int nz_e = s1.y;
+    const int nnz_tile = nz_e - nz_s;
+    const int tile_items = nrows + nnz_tile;
+
+    const int a0 = VEC ? (nz_s & ~3) : nz_s;  // products are stored at index (nonzero - a0)
+    const int head = nz_s - a0;
+    T* const s_prod = s_buf + head;             // s_prod[k]: k-th nonzero of the tile
+    T* const s_y = s_buf + head + nnz_tile;     // s_y[i]: row row_s + i, i in [0, nrows]
+
+    // Row ends in tile-local nonzero coordinates; entry nrows is the row left open.
+    for (int i = tid; i <= nrows; i += THREADS) {
+        const int r = row_s + i;
+        int e = (r < m) ? __ldg(row_ptr + r + 1) - base : nz_e;
+        e = min(e, nz_e);
+        s_row_end[i] = e - nz_s;
+        s_y[i] = T(0);
+    }
+
+    // ---- phase 1
+    const int* const colb = col;
+    const T* const xb = x - base;
+    if (VEC) {
+        const int nchunks = (head + nnz_tile + 3) >> 2;
+        int4 cc[CPT];
+        Quad<T> vv[CPT];
+        bool full[CPT];
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            const int c = tid + k * THREADS;
+            const int g = a0 + 4 * c;
+            full[k] = (c < nchunks) && (g >= nz_s) && (g + 4 <= nz_e);
+            if (full[k]) {
+                cc[k] = __ldcs(reinterpret_cast<const int4*>(colb + g));
+                vv[k].load(val + g);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            if (full[k]) {
+                const T x0 = __ldg(xb + cc[k].x), x1 = __ldg(xb + cc[k].y);
+                const T x2 = __ldg(xb + cc[k].z), x3 = __ldg(xb + cc[k].w);
+                Quad<T>::store(s_buf + 4 * (tid + k * THREADS), vv[k].get(0) * x0, vv[k].get(1) * x1,
+                               vv[k].get(2) * x2, vv[k].get(3) * x3);
+            }
+        }
+        // Ragged chunks (the tile's first and last) and the one chunk beyond the unrolled pass.
+        for (int c = tid; c < nchunks; c += THREADS) {
+            const int g = a0 + 4 * c;
+            const bool done = (c < CPT * THREADS) && (g >= nz_s) && (g + 4 <= nz_e);
+            if (!done) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int gi = g + e;
+                    if (gi >= nz_s && gi < nz_e) s_buf[4 * c + e] = __ldcs(val + gi) * __ldg(xb + __ldcs(colb + gi));
+                }
+            }
+        }
+    } else {
+        for (int k = tid; k < nnz_tile; k += THREADS) {
+            const int gi = nz_s + k;
+            s_prod[k] = __ldcs(val + gi) * __ldg(xb + __ldcs(colb + gi));
+        }
+    }
+    __syncthreads();
+
+    // ---- phase 2: merge walk over this thread's IPT items
+    const int d0 = min(tid * IPT, tile_items);
+    const int d1 = min(d0 + IPT, tile_items);
+    int lo = max(d0 - nnz_tile, 0), hi = min(d0, nrows);
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s_row_end[mid] <= d0 - mid - 1)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    int r = lo;       // tile-local row
+    int k = d0 - lo;  // tile-local nonzero
+    int end = s_row_end[r];
+    T sum = T(0);
+#pragma unroll
+    for (int it = 0; it < IPT; ++it) {
+        if (d0 + it < d1) {
+            if (k < end) {
+                sum += s_prod[k];
+                ++k;
+            } else {
+                s_y[r] = sum;
+                sum = T(0);
+                ++r;
+                end = s_row_end[r];
+            }
+        }
+    }
+
+    // ---- phase 3: segmented reduction of the per-thread carries (key = r, value = sum)
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const T up = __shfl_up_sync(0xffffffffu, sum, d);
+        const int ru = __shfl_up_sync(0xffffffffu, r, d);
+        if (lane >= d && ru == r) sum += up;
+    }
+    const int rn = __shfl_down_sync(0xffffffffu, r, 1);
+    __syncthreads();  // all direct row sums are in s_y
+    if (lane == 31) {
+        s_warp_row[warp] = r;
+        s_warp_sum[warp] = sum;
+    } else if (rn != r) {
+        s_y[r] += sum;  // the run of threads holding row r ends inside this warp: single writer
+    }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) s_y[s_warp_row[w]] += s_warp_sum[w];
+    }
+    __syncthreads();
+
+    // ---- phase 4
+    const T alpha = alpha_arg.get();
+    const T beta = beta_arg.get();
+    for (int i = tid; i < nrows; i += THREADS) {
+        T v = alpha * s_y[i];
+        if (beta != T(0)) v += beta * y[row_s + i];
+        y[row_s + i] = v;
+    }
+    if (tid == 0) {
+        carry_row[t] = row_s + nrows;
+        carry_val[t] = s_y[nrows];
+    }
+}
+
+// Adds the carries of rows that cross tile boundaries. The first tile of each run of equal
+// carry rows sums the run in tile order, so the result does not depend on scheduling.
+template <typename T>
+__global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* __restrict__ carry_row,
+                                        const T* __restrict__ carry_val, T* __restrict__ y, ScalarArg<T> alpha_arg) {
+    long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t >= num_tiles) return;
+    const int r = carry_row[t];
+    if (r >= m) return;
+    if (t > 0 && carry_row[t - 1] == r) return;
+    T sum = carry_val[t];
+    for (long long u = t + 1; u < num_tiles && carry_row[u] == r; ++u) sum += carry_val[u];
+    y[r] += alpha_arg.get() * sum;
+}
+
+// ---------------------------------------------------------------------------------------
+// K2: row-group SpMV. G lanes share a row (G chosen from the mean row length), lane-strided
+// loads, xor-shuffle reduction. Needs no analysis and no work buffer: the kernel behind the
+// legacy csrmv calls, which have neither.
+// ---------------------------------------------------------------------------------------
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads)
+    spmv_rowgroup_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+                         const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y,
+                         ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
+    const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / G;
+    const int lane = threadIdx.x & (G - 1);
+    const bool active = gid < m;
+    T sum = T(0);
+    if (active) {
+        const int j0 = __ldg(row_ptr + gid) - base, j1 = __ldg(row_ptr + gid + 1) - base;
+        const T* xb = x - base;
+        for (int j = j0 + lane; j < j1; j += G) sum += __ldcs(val + j) * __ldg(xb + __ldcs(col + j));
+    }
+#pragma unroll
+    for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, G);
+    if (active && lane == 0) {
+        const T alpha = alpha_arg.get(), beta = beta_arg.get();
+        T v = alpha * sum;
+        if (beta != T(0)) v += beta * y[gid];
+        y[gid] = v;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size) {
+    SpmvWorkspace ws;
+    ws.items_per_tile = value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    const int64_t items = m + nnz;
+    ws.num_tiles = (items + ws.items_per_tile - 1) / ws.items_per_tile;
+    auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+    ws.off_carry_row = up(size_t(ws.num_tiles + 1) * 8);
+    ws.off_carry_val = ws.off_carry_row + up(size_t(ws.num_tiles) * 4);
+    ws.bytes = ws.off_carry_val + up(size_t(ws.num_tiles) * value_size);
+    return ws;
+}
+
+cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                          const SpmvWorkspace& ws, void* buf) {
+    const long long n = ws.num_tiles + 1;
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    merge_path_partition_kernel<<<blocks, threads, 0, s>>>((int)m, (int)nnz, base, row_ptr, ws.items_per_tile,
+                                                           ws.num_tiles, reinterpret_cast<int2*>(buf));
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                       const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
+                       const SpmvWorkspace& ws, void* buf) {
+    (void)nnz;
+    if (ws.num_tiles == 0) return cudaSuccess;
+    char* base_ptr = static_cast<char*>(buf);
+    const int2* starts = reinterpret_cast<const int2*>(base_ptr);
+    int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
+    T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
+    constexpr int IPT = TileCfg<T>::kItemsPerThread;
+    const bool aligned =
+        ((reinterpret_cast<uintptr_t>(col) | reinterpret_cast<uintptr_t>(val)) & 15) == 0;
+    const unsigned grid = (unsigned)ws.num_tiles;
+    if (aligned)
+        spmv_tile_kernel<T, kThreads, IPT, true><<<grid, kThreads, 0, s>>>(
+            (int)m, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val);
+    else
+        spmv_tile_kernel<T, kThreads, IPT, false><<<grid, kThreads, 0, s>>>(
+            (int)m, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const int threads = 256;
+    spmv_carry_fixup_kernel<T><<<(unsigned)((ws.num_tiles + threads - 1) / threads), threads, 0, s>>>(
+        (int)m, ws.num_tiles, carry_row, carry_val, y, alpha);
+    return cudaGetLastError();
+}
+
+template <typename T, int G>
+static cudaError_t launch_rowgroup(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
+                                   const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta) {
+    const long long threads_total = m * G;
+    const unsigned grid = (unsigned)((threads_total + kThreads - 1) / kThreads);
+    spmv_rowgroup_kernel<T, G><<<grid, kThreads, 0, s>>>((int)m, base, row_ptr, col, val, x, y, alpha, beta);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
+                          const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,
+                          ScalarArg<T> beta) {
+    if (m == 0) return cudaSuccess;
+    const double mean = double(nnz) / double(m);
+    if (mean <= 3.0) return launch_rowgroup<T, 2>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
+    if (mean <= 6.0) return launch_rowgroup<T, 4>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
+    if (mean <= 12.0) return launch_rowgroup<T, 8>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
+    if (mean <= 24.0) return launch_rowgroup<T, 16>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
+    return launch_rowgroup<T, 32>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
+}
+
+#define INSTANTIATE(T)                                                                                         \
+    template cudaError_t spmv_tiled<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,    \
+                                       const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>,                     \
+                                       const SpmvWorkspace&, void*);                                           \
+    template cudaError_t spmv_rowgroup<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, \
+                                          const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>);
+INSTANTIATE(float)
+INSTANTIATE(double)
+#undef INSTANTIATE
+
+}  // namespace mcsp_b200

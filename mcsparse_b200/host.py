@@ -1,0 +1,148 @@
+"""Host-side objects over the C API: handle and descriptors that keep their torch tensors alive.
+
+Every method is a thin call into ``capi.lib`` (the C ABI). torch is used for device memory
+and streams only; all arithmetic happens in libmcsparse.so.
+"""
+
+import ctypes as C
+
+import torch
+
+from . import capi
+from .capi import check, lib
+
+_DTYPE = {torch.float32: capi.MACA_R_32F, torch.float64: capi.MACA_R_64F}
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _scalar(value, dtype):
+    """A host scalar of the compute type, as the C API expects behind ``const void*``."""
+    return (C.c_double if dtype == torch.float64 else C.c_float)(value)
+
+
+class Handle:
+    """mcsparseHandle_t bound to the current CUDA device and (optionally) a torch stream."""
+
+    def __init__(self, stream=None):
+        h = C.c_void_p()
+        check(lib.mcsparseCreate(C.byref(h)), "mcsparseCreate")
+        self.h = h
+        self.pointer_mode = capi.MCSPARSE_POINTER_MODE_HOST
+        if stream is None:
+            stream = torch.cuda.current_stream()
+        self.set_stream(stream)
+
+    def set_stream(self, stream):
+        self.stream = stream
+        check(lib.mcsparseSetStream(self.h, C.c_void_p(stream.cuda_stream)), "mcsparseSetStream")
+
+    def set_pointer_mode(self, mode):
+        check(lib.mcsparseSetPointerMode(self.h, mode), "mcsparseSetPointerMode")
+        self.pointer_mode = mode
+
+    def close(self):
+        if self.h is not None:
+            lib.mcsparseDestroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
+
+
+class CsrMatrix:
+    """mcsparseSpMatDescr_t over three device tensors (borrowed by the C side, owned here)."""
+
+    def __init__(self, rows, cols, row_offsets, col_ind, values, base=0):
+        assert row_offsets.dtype == torch.int32 and col_ind.dtype == torch.int32
+        self.rows, self.cols, self.base = int(rows), int(cols), int(base)
+        self.nnz = int(col_ind.numel())
+        self.row_offsets, self.col_ind, self.values = row_offsets, col_ind, values
+        d = C.c_void_p()
+        check(lib.mcsparseCreateCsr(C.byref(d), self.rows, self.cols, self.nnz, _ptr(row_offsets), _ptr(col_ind),
+                                    _ptr(values), capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, self.base,
+                                    _DTYPE[values.dtype]), "mcsparseCreateCsr")
+        self.d = d
+
+    @property
+    def dtype(self):
+        return self.values.dtype
+
+    def __del__(self):
+        if getattr(self, "d", None) is not None:
+            lib.mcsparseDestroySpMat(self.d)
+            self.d = None
+
+
+class DnVec:
+    def __init__(self, values):
+        self.values = values
+        d = C.c_void_p()
+        check(lib.mcsparseCreateDnVec(C.byref(d), values.numel(), _ptr(values), _DTYPE[values.dtype]),
+              "mcsparseCreateDnVec")
+        self.d = d
+
+    def __del__(self):
+        if getattr(self, "d", None) is not None:
+            lib.mcsparseDestroyDnVec(self.d)
+            self.d = None
+
+
+class DnMat:
+    """Dense matrix descriptor. ``values`` is the backing tensor; rows/cols/ld/order describe it."""
+
+    def __init__(self, values, rows, cols, ld, order=capi.MCSPARSE_ORDER_ROW):
+        self.values, self.rows, self.cols, self.ld, self.order = values, int(rows), int(cols), int(ld), order
+        d = C.c_void_p()
+        check(lib.mcsparseCreateDnMat(C.byref(d), self.rows, self.cols, self.ld, _ptr(values), _DTYPE[values.dtype],
+                                      order), "mcsparseCreateDnMat")
+        self.d = d
+
+    def __del__(self):
+        if getattr(self, "d", None) is not None:
+            lib.mcsparseDestroyDnMat(self.d)
+            self.d = None
+
+
+def _scalars(handle, alpha, beta, dtype):
+    """alpha/beta as C arguments: host scalars, or device tensors in device pointer mode."""
+    if handle.pointer_mode == capi.MCSPARSE_POINTER_MODE_DEVICE:
+        return _ptr(alpha), _ptr(beta), (alpha, beta)
+    a, b = _scalar(alpha, dtype), _scalar(beta, dtype)
+    return C.cast(C.pointer(a), C.c_void_p), C.cast(C.pointer(b), C.c_void_p), (a, b)
+
+
+def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0):
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    size = C.c_size_t()
+    check(lib.mcsparseSpMV_bufferSize(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d,
+                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, C.byref(size)),
+          "mcsparseSpMV_bufferSize")
+    del keep
+    return size.value
+
+
+def spmv_preprocess(handle, A, x, y, buffer, alpha=1.0, beta=0.0):
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    check(lib.mcsparseSpMV_preprocess(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d,
+                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)),
+          "mcsparseSpMV_preprocess")
+    del keep
+
+
+def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0):
+    """y = alpha * A @ x + beta * y through mcsparseSpMV (asynchronous on the handle's stream)."""
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    check(lib.mcsparseSpMV(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d, _DTYPE[A.dtype],
+                           capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)), "mcsparseSpMV")
+    del keep
+
+
+def spmm(handle, A, B, Cmat, buffer, alpha=1.0, beta=0.0, op_b=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
+    """C = alpha * A @ op(B) + beta * C through mcsparseSpMM."""
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    check(lib.mcsparseSpMM(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, op_b, pa, A.d, B.d, pb, Cmat.d,
+                           _DTYPE[A.dtype], capi.MCSPARSE_SPMM_ALG_DEFAULT, _ptr(buffer)), "mcsparseSpMM")
+    del keep
