@@ -1,0 +1,431 @@
+#!/usr/bin/env python
+"""Benchmark of the CSR SpMV / SpMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C5] [--impl reference]
+
+One JSON line on stdout (rank 0). The headline workload is the 27-point stencil SpMV
+(fp64, 16.8 M rows, 449 M nonzeros): the largest single-GPU configuration and one of the two
+that are sharded over several GPUs, so the same matrix is measured at every N (strong
+scaling: nnz-balanced row blocks, x replicated, y assembled on every GPU). At N = 1 the line
+also carries the other configurations under "configs".
+
+  value     algorithmic bytes / s with all operands resident in HBM (events on the handle's stream)
+  e2e       same metric through the C ABI with x copied from pinned host memory and y copied back
+            inside the timed region of every step (the matrix stays resident, as in a solver loop)
+  roofline  algorithmic bytes / mean device time of one mcsparseSpMV call (tile kernel + carry
+            fix-up kernel, so slightly conservative for the tile kernel alone) against the measured
+            HBM copy bandwidth in MEASURED_PEAKS.json
+  --impl reference   the OpenMP C CSR kernels of oracle/ on the host cores (the mcSparse reference has
+            no CPU implementation and builds only with the MetaX toolchain), on a bounded row block
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+METRIC = "csr_spmv_spmm_algorithmic_hbm_throughput"
+UNIT = "GB/s"
+
+
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Reads (never sets) SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.dev, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nv:
+            self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv:
+            self.thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def visible_device_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+class SpmvJob:
+    """One configuration on one rank: a row block of A resident in HBM, x replicated."""
+
+    def __init__(self, name, device, rank, world, handle, scale=1):
+        import torch
+
+        import mcsparse_b200 as mc
+        from mcsparse_b200 import workloads
+
+        self.torch, self.mc, self.h = torch, mc, handle
+        cfg = workloads.CONFIGS[name] if scale == 1 else workloads.scaled(name, scale)
+        self.cfg, self.world, self.rank = cfg, world, rank
+        self.vsize = 8 if cfg.dtype == torch.float64 else 4
+        lengths = workloads.row_lengths(cfg, device)
+        self.total_nnz = int(lengths.sum().item())
+        if world > 1:
+            # nnz-balanced contiguous row blocks (same rule as mcsparseB200ShardRowBounds)
+            ptr = torch.zeros(cfg.rows + 1, dtype=torch.int64, device=device)
+            torch.cumsum(lengths, 0, out=ptr[1:])
+            targets = torch.tensor([(g * self.total_nnz) // world for g in range(world + 1)], device=device)
+            bounds = torch.searchsorted(ptr, targets, right=False).tolist()
+            bounds[0], bounds[-1] = 0, cfg.rows
+            del ptr, targets
+        else:
+            bounds = [0, cfg.rows]
+        del lengths
+        self.bounds = bounds
+        r0, r1 = bounds[rank], bounds[rank + 1]
+        w = workloads.generate(cfg, device, row_range=(r0, r1))
+        self.w = w
+        self.y_full = torch.zeros(cfg.rows, dtype=cfg.dtype, device=device)
+        if cfg.beta != 0:
+            self.y_full[r0:r1] = w.y0
+        self.y = self.y_full[r0:r1]
+        self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+        self.X, self.Y = mc.DnVec(w.x), mc.DnVec(self.y)
+        self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y), dtype=torch.uint8, device=device)
+        mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf)
+        self.parts = [self.y_full[bounds[g]:bounds[g + 1]] for g in range(world)]
+        self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta)
+        self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta)
+        self.flops = 2 * self.total_nnz
+        self.launches_per_step = 2  # tile kernel + carry fix-up
+
+    def compute(self):
+        self.mc.spmv(self.h, self.A, self.X, self.Y, self.buf, alpha=self.cfg.alpha, beta=self.cfg.beta)
+
+    def step(self):
+        self.compute()
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather(self.parts, self.y)
+
+
+class SpmmJob:
+    def __init__(self, name, n, device, handle):
+        import torch
+
+        import mcsparse_b200 as mc
+        from mcsparse_b200 import workloads
+
+        self.torch, self.mc, self.h = torch, mc, handle
+        cfg = workloads.CONFIGS[name]
+        self.cfg, self.n, self.world = cfg, n, 1
+        w = workloads.generate(cfg, device)
+        self.w = w
+        self.total_nnz = w.nnz
+        self.C = torch.zeros(w.rows, n, dtype=cfg.dtype, device=device)
+        self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+        self.Bm, self.Cm = mc.DnMat(w.B[n], w.cols, n, n), mc.DnMat(self.C, w.rows, n, n)
+        self.buf = torch.empty(256, dtype=torch.uint8, device=device)
+        self.bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, 4, cfg.beta, dense_cols=n)
+        self.gather_model_bytes = w.nnz * (8 + 4 * n) + (w.rows + 1) * 4 + w.rows * n * 4
+        self.flops = 2 * w.nnz * n
+        self.launches_per_step = 1
+
+    def step(self):
+        self.mc.spmm(self.h, self.A, self.Bm, self.Cm, self.buf, alpha=self.cfg.alpha, beta=self.cfg.beta)
+
+    compute = step
+
+
+def time_steps(torch, fn, steps, warmup, flush_buf=None, barrier=None):
+    """Returns (total_ms over exactly `steps` calls, list of per-call ms). With flush_buf, a buffer larger than
+    L2 is rewritten before every call (outside the per-call events) and total_ms is the sum of the calls."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+        torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for a, b in evs:
+        if flush_buf is not None:
+            flush_buf.add_(1)
+        a.record()
+        fn()
+        b.record()
+    t1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+        torch.cuda.synchronize()
+    per = [a.elapsed_time(b) for a, b in evs]
+    total = sum(per) if flush_buf is not None else t0.elapsed_time(t1)
+    return total, per
+
+
+def measure_job(torch, job, steps, warmup, peak, flush_buf):
+    flush = flush_buf if job.bytes < 4 * L2_BYTES else None
+    total, per = time_steps(torch, job.compute, steps, warmup, flush)
+    ms = total / steps
+    gbs = job.bytes / (ms * 1e-3) / 1e9
+    out = {"ms_per_step": round(ms, 5), "best_ms": round(min(per), 5), "gbs": round(gbs, 1),
+           "gflops": round(job.flops / (ms * 1e-3) / 1e9, 1), "frac_of_measured_hbm": round(gbs / peak, 4),
+           "frac_of_nominal_8tbs": round(gbs / 8000.0, 4), "bytes": job.bytes, "nnz": job.total_nnz,
+           "l2": "flushed between steps" if flush is not None else "inputs exceed L2"}
+    if hasattr(job, "gather_model_bytes"):
+        g = job.gather_model_bytes / (ms * 1e-3) / 1e9
+        out["gather_model_gbs"] = round(g, 1)
+        out["gather_model_frac"] = round(g / peak, 4)
+    return out
+
+
+def cpu_baseline(name, seconds=8.0, steps=None, warmup=1):
+    """Times the OpenMP CSR kernel of oracle/ on a bounded row block of the workload (host cores)."""
+    import numpy as np
+    import torch
+
+    from mcsparse_b200 import workloads
+    from oracle import oracle
+
+    cfg = workloads.CONFIGS[name]
+    target_nnz = 40_000_000
+    lengths_mean = {"C1": 5, "C2": 16, "C3": 12, "C4": 32, "C5": 27}[name]
+    rows = min(cfg.rows, max(1, target_nnz // lengths_mean))
+    if cfg.op == "spmm":
+        rows = min(rows, 131072)
+    w = workloads.generate(cfg, "cpu", row_range=(0, rows), with_dense=False)
+    rp, col, val = w.row_ptr.numpy(), w.col.numpy(), w.val.numpy()
+    vsize = val.dtype.itemsize
+    if cfg.op == "spmv":
+        x = workloads.dense_values(cfg, "cpu", cfg.rows, 41, normal=cfg.values == "normal").numpy()
+        y = np.zeros(rows, val.dtype)
+        fn = lambda: oracle.baseline_spmv(rp, col, val, x, cfg.alpha, cfg.beta, y)
+        # x bytes: the part of x this row block can touch (a stencil block reaches one plane beyond itself)
+        reach = {"stencil2d": cfg.grid + 1, "stencil3d": cfg.grid * cfg.grid + cfg.grid + 1}.get(cfg.kind, cfg.rows)
+        nbytes = workloads.algorithmic_bytes(rows, min(cfg.rows, rows + reach), w.nnz, vsize, cfg.beta)
+        desc = f"rows [0, {rows}) of {name} ({w.nnz} nnz), x of full length"
+    else:
+        n = cfg.dense_cols[0]
+        B = workloads.dense_values(cfg, "cpu", cfg.rows * n, 61 + n).numpy().reshape(cfg.rows, n)
+        Cm = np.zeros((rows, n), val.dtype)
+        fn = lambda: oracle.baseline_spmm(rp, col, val, B, n, cfg.alpha, cfg.beta, Cm)
+        nbytes = workloads.algorithmic_bytes(rows, cfg.rows, w.nnz, vsize, cfg.beta, dense_cols=n)
+        desc = f"rows [0, {rows}) of {name} ({w.nnz} nnz), B {cfg.rows} x {n}"
+    for _ in range(warmup):
+        fn()
+    t = time.perf_counter()
+    fn()
+    one = time.perf_counter() - t
+    if steps is None:
+        steps = int(min(50, max(3, seconds / max(one, 1e-6))))
+    t = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t) / steps
+    return {"value": round(nbytes / dt / 1e9, 2), "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{desc}; {steps} passes, {dt * 1e3:.2f} ms each",
+            "gflops": round(2 * w.nnz * (1 if cfg.op == "spmv" else cfg.dense_cols[0]) / dt / 1e9, 2)}, dt, steps
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    base, dt, steps = cpu_baseline(args.workload, steps=args.steps, warmup=max(1, min(args.warmup, 3)))
+    from mcsparse_b200 import workloads
+
+    cfg = workloads.CONFIGS[args.workload]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64" if cfg.dtype.itemsize == 8 else "f32",
+        "data": "synthetic",
+        "config": {"workload": workload_label(args.workload), "note": "OpenMP C CSR kernel of oracle/ on host cores; "
+                   "the mcSparse reference has no CPU path and builds only with the MetaX toolchain"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_label(name):
+    return {
+        "C1": "C1 CSR SpMV fp32 5-point Poisson 1024x1024",
+        "C2": "C2 CSR SpMV fp64 Poisson(16) rows n=4194304 beta=0.5",
+        "C3": "C3 CSR SpMV fp32 power-law rows n=16777216 nnz~2e8",
+        "C4": "C4 CSR SpMM fp32 Poisson(32) rows n=1048576, B row-major 64/128 columns",
+        "C5": "C5 CSR SpMV fp64 27-point stencil 256^3",
+    }[name]
+
+
+def run_gpu(args, rank, world, local_rank):
+    import torch
+
+    import mcsparse_b200 as mc
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    barrier = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+        barrier = dist.barrier
+    peak, peak_kind = hbm_peak()
+    h = mc.Handle()
+    flush_buf = torch.zeros(4 * L2_BYTES // 4, dtype=torch.float32, device=device)
+
+    job = SpmvJob(args.workload, device, rank, world, h, args.scale)
+    flush = flush_buf if job.local_bytes < 4 * L2_BYTES else None
+
+    # kernel-only timing of the local SpMV call (roofline), then the full step (with y assembly at N > 1)
+    _, per_compute = time_steps(torch, job.compute, max(10, args.steps // 4), args.warmup, flush, barrier)
+    with ClockSampler(visible_device_index(local_rank)) as clocks:
+        total_ms, per = time_steps(torch, job.step, args.steps, args.warmup, flush, barrier)
+    t = torch.tensor([total_ms, statistics.mean(per_compute)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, compute_ms = t.tolist()
+    ms_per_step = total_ms / args.steps
+    value = job.bytes / (ms_per_step * 1e-3) / 1e9
+
+    # end to end: x from pinned host memory every step, y back to pinned host memory
+    x_host = job.w.x.cpu().pin_memory()
+    y_host = torch.empty(job.y.numel(), dtype=job.cfg.dtype).pin_memory()
+
+    def e2e_step():
+        job.w.x.copy_(x_host, non_blocking=True)
+        job.step()
+        y_host.copy_(job.y, non_blocking=True)
+
+    e2e_steps = max(5, min(args.steps, 50))
+    e2e_total, _ = time_steps(torch, e2e_step, e2e_steps, 3, None, barrier)
+    t = torch.tensor([e2e_total], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+
+    if rank == 0:
+        local_gbs = job.local_bytes / (compute_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64" if job.vsize == 8 else "f32",
+            "data": "synthetic",
+            "config": {"workload": workload_label(args.workload) + ("" if args.scale == 1 else f" / {args.scale}"), "rows": job.cfg.rows, "nnz": job.total_nnz,
+                       "alpha": job.cfg.alpha, "beta": job.cfg.beta, "index_base": 0,
+                       "sharding": "replicas only (N=1)" if world == 1 else
+                       f"{world} nnz-balanced row blocks, x replicated, y all-gathered (NCCL)",
+                       "l2": "inputs exceed L2" if flush is None else "L2 flushed between steps",
+                       "algorithmic_bytes": job.bytes},
+            "gflops": round(job.flops / (ms_per_step * 1e-3) / 1e9, 1),
+            "roofline": {"bound": "hbm", "achieved": round(local_gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(local_gbs / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "frac_of_nominal_8tbs": round(local_gbs / 8000.0, 4),
+                         "kernel": "spmv_tile_kernel (+ carry fix-up) per rank", "ms": round(compute_ms, 5)},
+            "e2e": {"value": round(job.bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": UNIT,
+                    "h2d_bytes_per_step": x_host.numel() * job.vsize, "d2h_bytes_per_step": y_host.numel() * job.vsize,
+                    "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": job.launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and args.scale == 1:
+            base, _, _ = cpu_baseline(args.workload)
+            line["cpu_baseline"] = base
+        if world == 1 and args.scale == 1 and not args.headline_only:
+            extra = {}
+            del job
+            torch.cuda.empty_cache()
+            for name in ("C1", "C2", "C3"):
+                j = SpmvJob(name, device, 0, 1, h)
+                extra[name] = measure_job(torch, j, 100, 5, peak, flush_buf)
+                del j
+                torch.cuda.empty_cache()
+            for n in (64, 128):
+                j = SpmmJob("C4", n, device, h)
+                extra[f"C4_n{n}"] = measure_job(torch, j, 30, 3, peak, flush_buf)
+                del j
+                torch.cuda.empty_cache()
+            line["configs"] = extra
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="C5", choices=["C1", "C2", "C3", "C5"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--scale", type=int, default=1, help="shrink the workload's rows by this factor (profiling)")
+    ap.add_argument("--headline-only", action="store_true", help="skip the per-configuration block at N=1")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_gpu(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

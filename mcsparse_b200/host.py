@@ -15,7 +15,13 @@ _DTYPE = {torch.float32: capi.MACA_R_32F, torch.float64: capi.MACA_R_64F}
 
 
 def _ptr(t):
-    return C.c_void_p(t.data_ptr())
+    """Device address of a tensor. torch reports a null data_ptr() for zero-element tensors; the
+    C API (like the reference) rejects null arrays even when they are empty, so an empty view
+    is given the address of its storage instead."""
+    p = t.data_ptr()
+    if p == 0 and t.untyped_storage().nbytes() > 0:
+        p = t.untyped_storage().data_ptr() + t.storage_offset() * t.element_size()
+    return C.c_void_p(p)
 
 
 def _scalar(value, dtype):

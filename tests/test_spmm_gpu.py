@@ -1,0 +1,176 @@
+"""GPU parity tests of mcsparseSpMM and the legacy csrmm entry points, through the C ABI."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import mcsparse_b200 as mc
+from mcsparse_b200 import capi, workloads
+from mcsparse_b200.capi import lib
+from oracle import oracle
+from tests.util import ADVERSARIAL_LENGTHS, TOL, assert_close, csr_from_lengths
+
+pytestmark = pytest.mark.gpu
+ROW, COL = capi.MCSPARSE_ORDER_ROW, capi.MCSPARSE_ORDER_COL
+
+
+def dense(rng, rows, cols, ld, order, dtype):
+    """Backing array of a rows x cols matrix with leading dimension ld, padding filled with a sentinel."""
+    major = rows if order == ROW else cols
+    a = np.full(major * ld, 777.0, dtype)
+    v = a.reshape(major, ld)
+    minor = cols if order == ROW else rows
+    v[:, :minor] = rng.uniform(-1, 1, (major, minor)).astype(dtype)
+    return a
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [1, 3, 4, 5, 32, 64, 100, 128, 256])
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+def test_spmm_row_major(handle, device, dtype, n, beta):
+    lengths = ADVERSARIAL_LENGTHS["lengths_1_to_33"] + ADVERSARIAL_LENGTHS["empty_start_mid_end"] + [300]
+    k = 400
+    base = n % 2
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=n, base=base)
+    m = len(lengths)
+    rng = np.random.default_rng(n)
+    ldb, ldc = n + (4 if n % 3 == 0 else 0), n + (8 if n % 5 == 0 else 0)
+    B, C0 = dense(rng, k, n, ldb, ROW, dtype), dense(rng, m, n, ldc, ROW, dtype)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B, C0.copy())]
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2], base=base)
+    Bm, Cm = mc.DnMat(t[3], k, n, ldb, ROW), mc.DnMat(t[4], m, n, ldc, ROW)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=-1.5, beta=beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, B, ldb, ROW, n, -1.5, beta, C0, ldc, ROW, base=base)
+    got = t[4].cpu().numpy().reshape(m, ldc)
+    assert_close(got[:, :n], ref, d, TOL[np.dtype(dtype)], f"n={n}")
+    assert (got[:, n:] == 777.0).all(), "padding columns of C must stay untouched"
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("order_b,order_c", [(COL, COL), (ROW, COL), (COL, ROW)])
+def test_spmm_other_layouts(handle, device, dtype, order_b, order_c):
+    lengths = ADVERSARIAL_LENGTHS["lengths_63_65"] + [0, 1, 2]
+    k, n = 90, 12
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=2)
+    m = len(lengths)
+    rng = np.random.default_rng(1)
+    ldb = (n if order_b == ROW else k) + 3
+    ldc = (n if order_c == ROW else m) + 2
+    B, C0 = dense(rng, k, n, ldb, order_b, dtype), dense(rng, m, n, ldc, order_c, dtype)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B, C0.copy())]
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2])
+    Bm, Cm = mc.DnMat(t[3], k, n, ldb, order_b), mc.DnMat(t[4], m, n, ldc, order_c)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=2.0, beta=-1.0)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, B, ldb, order_b, n, 2.0, -1.0, C0, ldc, order_c)
+    raw = t[4].cpu().numpy()
+    got = raw.reshape(m, ldc)[:, :n] if order_c == ROW else raw.reshape(n, ldc)[:, :m].T
+    assert_close(got, ref, d, TOL[np.dtype(dtype)], "layouts")
+
+
+def test_spmm_op_b_transpose(handle, device):
+    """op(B) = B^T with B stored n x k column-major is the same memory as k x n row-major."""
+    dtype = np.float32
+    lengths = [5, 0, 17, 33]
+    k, n = 40, 8
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=5)
+    rng = np.random.default_rng(5)
+    Bkn = rng.uniform(-1, 1, (k, n)).astype(dtype)  # k x n row-major == (n x k) column-major with ld n
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, Bkn.ravel())]
+    Cout = torch.zeros(len(lengths) * n, dtype=torch.float32, device=device)
+    A = mc.CsrMatrix(len(lengths), k, t[0], t[1], t[2])
+    Bm, Cm = mc.DnMat(t[3], n, k, n, COL), mc.DnMat(Cout, len(lengths), n, n, ROW)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    mc.spmm(handle, A, Bm, Cm, buf, op_b=capi.MCSPARSE_OPERATION_TRANSPOSE)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, Bkn, n, ROW, n, 1.0, 0.0)
+    assert_close(Cout.cpu().numpy().reshape(-1, n), ref, d, 1e-5, "opB=T")
+
+
+@pytest.mark.parametrize("n", [64, 128])
+def test_spmm_scaled_config(handle, device, n):
+    cfg = workloads.scaled("C4", 64)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    Cout = torch.full((w.rows, n), float("nan"), dtype=cfg.dtype, device=device)  # beta = 0 must not read it
+    Bm, Cm = mc.DnMat(w.B[n], w.cols, n, n), mc.DnMat(Cout, w.rows, n, n)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    mc.spmm(handle, A, Bm, Cm, buf)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(w.row_ptr, w.col, w.val, w.B[n], n, ROW, n, 1.0, 0.0)
+    assert_close(Cout.cpu().numpy(), ref, d, 1e-5, f"C4 n={n}")
+
+
+def test_spmm_status_codes(handle, device):
+    rp, col, val = csr_from_lengths([2, 3], 4, np.float32)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val)]
+    A = mc.CsrMatrix(2, 4, *t)
+    Bt, Ct = torch.ones(4 * 8, device=device), torch.zeros(2 * 8, device=device)
+    B, Cm = mc.DnMat(Bt, 4, 8, 8), mc.DnMat(Ct, 2, 8, 8)
+    Bbad = mc.DnMat(Bt, 5, 6, 6)
+    Cld = mc.DnMat(Ct, 2, 8, 4)
+    one = C.c_float(1.0)
+    pa = C.cast(C.pointer(one), C.c_void_p)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    pb = C.c_void_p(buf.data_ptr())
+    f32 = capi.MACA_R_32F
+    call = lib.mcsparseSpMM
+    assert call(handle.h, 0, 0, pa, A.d, B.d, pa, Cm.d, f32, 0, pb) == 0
+    assert call(handle.h, 0, 0, pa, A.d, B.d, pa, Cm.d, f32, 0, None) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, 0, 0, pa, None, B.d, pa, Cm.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, 1, 0, pa, A.d, B.d, pa, Cm.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert call(handle.h, 0, 0, pa, A.d, B.d, pa, Cm.d, capi.MACA_R_64F, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert call(handle.h, 0, 0, pa, A.d, Bbad.d, pa, Cm.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, 0, 0, pa, A.d, B.d, pa, Cld.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    sz = C.c_size_t()
+    assert lib.mcsparseSpMM_bufferSize(handle.h, 0, 0, pa, A.d, B.d, pa, Cm.d, f32, 0, C.byref(sz)) == 0
+    assert sz.value == 128
+    assert lib.mcsparseSpMM_preprocess(handle.h, 0, 0, pa, A.d, B.d, pa, Cm.d, f32, 0, pb) == 0
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("trans_b", [0, 1])
+def test_legacy_csrmm2(handle, device, dtype, trans_b):
+    lengths = ADVERSARIAL_LENGTHS["lengths_1_to_33"]
+    k, n, base = 50, 7, 1
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=3, base=base)
+    m = len(lengths)
+    rng = np.random.default_rng(8)
+    if trans_b:  # B is n x k column-major, ldb >= n
+        ldb = n + 1
+        B = dense(rng, n, k, ldb, COL, dtype)
+        B_for_oracle, ld_o, order_o = B, ldb, ROW  # same memory read as k x n row-major
+    else:  # B is k x n column-major, ldb >= k
+        ldb = k + 2
+        B = dense(rng, k, n, ldb, COL, dtype)
+        B_for_oracle, ld_o, order_o = B, ldb, COL
+    ldc = m + 3
+    C0 = dense(rng, m, n, ldc, COL, dtype)
+    ref, d = oracle.spmm(rp, col, val, B_for_oracle, ld_o, order_o, n, 1.5, 0.5, C0, ldc, COL, base=base)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B, C0.copy())]
+    descr = C.c_void_p()
+    capi.check(lib.mcsparseCreateMatDescr(C.byref(descr)))
+    capi.check(lib.mcsparseSetMatIndexBase(descr, base))
+    ct = C.c_float if dtype == np.float32 else C.c_double
+    a, b = ct(1.5), ct(0.5)
+    P = lambda x: C.c_void_p(x.data_ptr())
+    fn = lib.mcsparseScsrmm2 if dtype == np.float32 else lib.mcsparseDcsrmm2
+    capi.check(fn(handle.h, 0, trans_b, m, n, k, col.size, C.cast(C.pointer(a), C.c_void_p), descr, P(t[2]), P(t[0]),
+                  P(t[1]), P(t[3]), ldb, C.cast(C.pointer(b), C.c_void_p), P(t[4]), ldc))
+    torch.cuda.synchronize()
+    got = t[4].cpu().numpy().reshape(n, ldc)[:, :m].T
+    assert_close(got, ref, d, TOL[np.dtype(dtype)], "csrmm2")
+    if not trans_b:
+        t[4].copy_(torch.from_numpy(C0))
+        fn1 = lib.mcsparseScsrmm if dtype == np.float32 else lib.mcsparseDcsrmm
+        capi.check(fn1(handle.h, 0, m, n, k, col.size, C.cast(C.pointer(a), C.c_void_p), descr, P(t[2]), P(t[0]),
+                       P(t[1]), P(t[3]), ldb, C.cast(C.pointer(b), C.c_void_p), P(t[4]), ldc))
+        torch.cuda.synchronize()
+        assert_close(t[4].cpu().numpy().reshape(n, ldc)[:, :m].T, ref, d, TOL[np.dtype(dtype)], "csrmm")
+    lib.mcsparseDestroyMatDescr(descr)

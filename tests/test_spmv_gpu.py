@@ -1,0 +1,240 @@
+"""GPU parity tests of mcsparseSpMV and the legacy csrmv entry points, through the C ABI."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import mcsparse_b200 as mc
+from mcsparse_b200 import capi, workloads
+from mcsparse_b200.capi import lib
+from oracle import oracle
+from tests.util import ADVERSARIAL_LENGTHS, TOL, assert_close, csr_from_lengths
+
+pytestmark = pytest.mark.gpu
+DT = {np.float32: torch.float32, np.float64: torch.float64}
+MACA = {np.float32: capi.MACA_R_32F, np.float64: capi.MACA_R_64F}
+
+
+def run_spmv(handle, device, rp, col, val, x, y0, alpha, beta, base=0, preprocess=False, offset_elems=0):
+    """Uploads, runs mcsparseSpMV, returns (y, buffer, descriptor holder). offset_elems > 0 puts col/val at a
+    misaligned address to reach the scalar-load variant."""
+    def up(a, off=0):
+        t = torch.empty(a.size + off + 1, dtype=torch.from_numpy(a[:0]).dtype, device=device)
+        t[off:off + a.size] = torch.from_numpy(a).to(device)
+        return t[off:off + a.size]
+
+    d_rp, d_col, d_val = up(rp), up(col, offset_elems), up(val, offset_elems)
+    d_x, d_y = up(x), up(y0.copy())
+    m = rp.size - 1
+    A = mc.CsrMatrix(m, x.size, d_rp, d_col, d_val, base=base)
+    X, Y = mc.DnVec(d_x), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+    if preprocess:
+        mc.spmv_preprocess(handle, A, X, Y, buf)
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=beta)
+    torch.cuda.synchronize()
+    return d_y.cpu().numpy(), buf, (A, X, Y)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("beta", [0.0, -0.75])
+@pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
+def test_spmv_adversarial_shapes(handle, device, name, dtype, base, beta):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    ncols = max(max(lengths), 1) + 17
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=11, base=base)
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-1, 1, ncols).astype(dtype)
+    y0 = rng.uniform(-1, 1, len(lengths)).astype(dtype)
+    y, buf, keep = run_spmv(handle, device, rp, col, val, x, y0, 1.25, beta, base)
+    ref, d = oracle.spmv(rp, col, val, x, 1.25, beta, y0, base=base)
+    assert_close(y, ref, d, TOL[np.dtype(dtype)], name)
+    # the work partition in the buffer is bit-exact against the CPU partition
+    nnz = col.size
+    ipt = capi.SPMV_TILE_ITEMS[MACA[dtype]]
+    part = oracle.merge_path_partition(rp, nnz, ipt, base)
+    items, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
+    capi.check(lib.mcsparseB200SpMVPartitionView(keep[0].d, C.c_void_p(buf.data_ptr()), C.byref(items), C.byref(nt),
+                                                 C.byref(p)))
+    assert items.value == ipt and nt.value == part.shape[0] - 1
+    off = p.value - buf.data_ptr()
+    got = buf[off:off + part.size * 4].view(torch.int32).cpu().numpy().reshape(-1, 2)
+    np.testing.assert_array_equal(got, part)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_spmv_beta_zero_does_not_read_y(handle, device, dtype):
+    rp, col, val = csr_from_lengths([3, 0, 40, 5000, 1], 6000, dtype, seed=1)
+    x = np.random.default_rng(0).uniform(-1, 1, 6000).astype(dtype)
+    y0 = np.full(5, np.nan, dtype)
+    y, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 2.0, 0.0)
+    ref, d = oracle.spmv(rp, col, val, x, 2.0, 0.0)
+    assert_close(y, ref, d, TOL[np.dtype(dtype)], "beta=0 with NaN in y")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_spmv_alpha_zero_scales_y(handle, device, dtype):
+    rp, col, val = csr_from_lengths([3, 2, 0, 9], 12, dtype, seed=1)
+    x = np.ones(12, dtype)
+    y0 = np.arange(4).astype(dtype)
+    y, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 0.0, 3.0)
+    np.testing.assert_array_equal(y, 3.0 * y0)
+    # alpha = beta = 0 writes zeros; nnz = 0 scales y (the reference leaves y untouched in both cases)
+    y, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 0.0, 0.0)
+    np.testing.assert_array_equal(y, np.zeros(4, dtype))
+    rp0 = np.zeros(5, np.int32)
+    y, _, _ = run_spmv(handle, device, rp0, np.zeros(1, np.int32)[:0], np.zeros(0, dtype), x, y0, 1.0, 2.0)
+    np.testing.assert_array_equal(y, 2.0 * y0)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("offset", [1, 2, 3])
+def test_spmv_unaligned_arrays(handle, device, dtype, offset):
+    lengths = ADVERSARIAL_LENGTHS["tile_straddle"] + ADVERSARIAL_LENGTHS["lengths_1_to_33"]
+    ncols = 5000
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=4)
+    rng = np.random.default_rng(3)
+    x, y0 = rng.uniform(-1, 1, ncols).astype(dtype), rng.uniform(-1, 1, len(lengths)).astype(dtype)
+    y, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 1.0, 1.0, offset_elems=offset)
+    ref, d = oracle.spmv(rp, col, val, x, 1.0, 1.0, y0)
+    assert_close(y, ref, d, TOL[np.dtype(dtype)], f"offset {offset}")
+
+
+@pytest.mark.parametrize("name,factor", [("C1", 16), ("C2", 64), ("C3", 64), ("C5", 64)])
+def test_spmv_scaled_configs(handle, device, name, factor):
+    cfg = workloads.scaled(name, factor)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    y = w.y0.clone()
+    X, Y = mc.DnVec(w.x), mc.DnVec(y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+    mc.spmv_preprocess(handle, A, X, Y, buf)
+    for _ in range(2):  # second call reuses the recorded analysis
+        y.copy_(w.y0)
+        mc.spmv(handle, A, X, Y, buf, alpha=w.alpha, beta=w.beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(w.row_ptr, w.col, w.val, w.x, w.alpha, w.beta, w.y0)
+    assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], name)
+
+
+def test_spmv_is_reproducible(handle, device):
+    cfg = workloads.scaled("C3", 64)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    ys = []
+    for _ in range(3):
+        y = torch.zeros(w.rows, dtype=cfg.dtype, device=device)
+        X, Y = mc.DnVec(w.x), mc.DnVec(y)
+        buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+        mc.spmv(handle, A, X, Y, buf)
+        ys.append(y)
+    torch.cuda.synchronize()
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2])
+
+
+def test_spmv_device_pointer_mode_and_stream(device):
+    stream = torch.cuda.Stream()
+    h = mc.Handle(stream)
+    s = C.c_void_p()
+    capi.check(lib.mcsparseGetStream(h.h, C.byref(s)))
+    assert (s.value or 0) == stream.cuda_stream
+    h.set_pointer_mode(capi.MCSPARSE_POINTER_MODE_DEVICE)
+    rp, col, val = csr_from_lengths(ADVERSARIAL_LENGTHS["long_then_short"], 9100, np.float64, seed=8)
+    rng = np.random.default_rng(4)
+    x, y0 = rng.uniform(-1, 1, 9100), rng.uniform(-1, 1, rp.size - 1)
+    d_rp, d_col, d_val = (torch.from_numpy(a).to(device) for a in (rp, col, val))
+    d_x, d_y = torch.from_numpy(x).to(device), torch.from_numpy(y0.copy()).to(device)
+    alpha = torch.tensor([1.5], dtype=torch.float64, device=device)
+    beta = torch.tensor([-2.0], dtype=torch.float64, device=device)
+    A = mc.CsrMatrix(rp.size - 1, 9100, d_rp, d_col, d_val)
+    X, Y = mc.DnVec(d_x), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(h, A, X, Y, alpha, beta), dtype=torch.uint8, device=device)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        mc.spmv(h, A, X, Y, buf, alpha=alpha, beta=beta)
+    stream.synchronize()
+    ref, d = oracle.spmv(rp, col, val, x, 1.5, -2.0, y0)
+    assert_close(d_y.cpu().numpy(), ref, d, 1e-12, "device scalars")
+    h.close()
+
+
+def test_spmv_status_codes(handle, device):
+    rp, col, val = csr_from_lengths([2, 3], 4, np.float32)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val)]
+    x = torch.ones(4, device=device)
+    y = torch.zeros(2, device=device)
+    A = mc.CsrMatrix(2, 4, *t)
+    X, Y, Ywrong = mc.DnVec(x), mc.DnVec(y), mc.DnVec(torch.zeros(3, device=device))
+    X64 = mc.DnVec(torch.ones(4, dtype=torch.float64, device=device))
+    one = C.c_float(1.0)
+    pa = C.cast(C.pointer(one), C.c_void_p)
+    buf = torch.empty(4096, dtype=torch.uint8, device=device)
+    pb = C.c_void_p(buf.data_ptr())
+    N, T, H = 0, 1, 2
+    f32 = capi.MACA_R_32F
+    call = lib.mcsparseSpMV
+    assert call(handle.h, N, None, A.d, X.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, N, pa, None, X.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, None) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, N, pa, A.d, X.d, pa, Ywrong.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, H, pa, A.d, Y.d, pa, X.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert call(handle.h, T, pa, A.d, Y.d, pa, X.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, capi.MACA_R_64F, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert call(handle.h, N, pa, A.d, X64.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    mode = C.c_int(capi.MCSPARSE_FILL_MODE_LOWER)
+    capi.check(lib.mcsparseSpMatSetAttribute(A.d, capi.MCSPARSE_SPMAT_FILL_MODE, C.byref(mode), 4))
+    assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    mode = C.c_int(capi.MCSPARSE_FILL_MODE_FULL)
+    capi.check(lib.mcsparseSpMatSetAttribute(A.d, capi.MCSPARSE_SPMAT_FILL_MODE, C.byref(mode), 4))
+    assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, pb) == 0
+    sz = C.c_size_t()
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, None) == 3
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, C.byref(sz)) == 0
+    assert sz.value >= 128
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "many_short", "uniform_27", "one_row_all_nnz", "all_empty"])
+def test_legacy_csrmv_and_csrmvex(handle, device, dtype, name):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    ncols = max(max(lengths), 1) + 5
+    base = 1
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=6, base=base)
+    rng = np.random.default_rng(9)
+    x, y0 = rng.uniform(-1, 1, ncols).astype(dtype), rng.uniform(-1, 1, len(lengths)).astype(dtype)
+    ref, d = oracle.spmv(rp, col, val, x, 0.5, 1.5, y0, base=base)
+    pad = lambda a: np.concatenate([a, np.zeros(1, a.dtype)])  # keep device pointers non-null for empty arrays
+    t = {k: torch.from_numpy(pad(v)).to(device) for k, v in dict(rp=rp, col=col, val=val, x=x).items()}
+    descr = C.c_void_p()
+    capi.check(lib.mcsparseCreateMatDescr(C.byref(descr)))
+    capi.check(lib.mcsparseSetMatIndexBase(descr, base))
+    ct = C.c_float if dtype == np.float32 else C.c_double
+    a, b = ct(0.5), ct(1.5)
+    pa, pb = C.cast(C.pointer(a), C.c_void_p), C.cast(C.pointer(b), C.c_void_p)
+    P = lambda k: C.c_void_p(t[k].data_ptr())
+    m, nnz = len(lengths), col.size
+
+    y = torch.from_numpy(pad(y0)).to(device)
+    fn = lib.mcsparseScsrmv if dtype == np.float32 else lib.mcsparseDcsrmv
+    capi.check(fn(handle.h, 0, m, ncols, nnz, pa, descr, P("val"), P("rp"), P("col"), P("x"), pb,
+                  C.c_void_p(y.data_ptr())))
+    torch.cuda.synchronize()
+    assert_close(y.cpu().numpy()[:m], ref, d, TOL[np.dtype(dtype)], "csrmv")
+    assert fn(handle.h, 1, m, ncols, nnz, pa, descr, P("val"), P("rp"), P("col"), P("x"), pb,
+              C.c_void_p(y.data_ptr())) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+
+    y = torch.from_numpy(pad(y0)).to(device)
+    dt = MACA[dtype]
+    sz = C.c_size_t()
+    ex_args = (handle.h, capi.MCSPARSE_ALG_MERGE_PATH, 0, m, ncols, nnz, pa, dt, descr, P("val"), dt, P("rp"),
+               P("col"), P("x"), dt, pb, dt, C.c_void_p(y.data_ptr()), dt, dt)
+    capi.check(lib.mcsparseCsrmvEx_bufferSize(*ex_args, C.byref(sz)))
+    buf = torch.empty(sz.value, dtype=torch.uint8, device=device)
+    capi.check(lib.mcsparseCsrmvEx(*ex_args, C.c_void_p(buf.data_ptr())))
+    torch.cuda.synchronize()
+    assert_close(y.cpu().numpy()[:m], ref, d, TOL[np.dtype(dtype)], "CsrmvEx")
+    lib.mcsparseDestroyMatDescr(descr)
