@@ -63,10 +63,7 @@ template <>
 struct Quad<float> {
     float4 v;
     __device__ __forceinline__ void load(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
-    __device__ __forceinline__ float get(int i) const { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-    __device__ __forceinline__ static void store(float* p, float a, float b, float c, float d) {
-        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
 };
 template <>
 struct Quad<double> {
@@ -75,23 +72,33 @@ struct Quad<double> {
         lo = __ldcs(reinterpret_cast<const double2*>(p));
         hi = __ldcs(reinterpret_cast<const double2*>(p) + 1);
     }
-    __device__ __forceinline__ double get(int i) const { return i == 0 ? lo.x : i == 1 ? lo.y : i == 2 ? hi.x : hi.y; }
-    __device__ __forceinline__ static void store(double* p, double a, double b, double c, double d) {
-        reinterpret_cast<double2*>(p)[0] = make_double2(a, b);
-        reinterpret_cast<double2*>(p)[1] = make_double2(c, d);
+    __device__ __forceinline__ void store(double* p) const {
+        reinterpret_cast<double2*>(p)[0] = lo;
+        reinterpret_cast<double2*>(p)[1] = hi;
     }
 };
 
 // ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
-//   phase 1  128-bit coalesced loads of col/val, gather x, products -> shared memory
-//   phase 2  each thread walks IPT consecutive merge items over the shared products
-//            (sequential sum per row segment, row totals into shared y slots)
-//   phase 3  thread carries (a row open at a thread boundary) are combined with a
-//            warp-shuffle segmented scan, then across the 8 warps in a fixed order
-//   phase 4  coalesced epilogue y = alpha * s + beta * y for the rows that end in the tile;
-//            the sum of the row still open at the tile's end goes to carry_{row,val}[t]
+//
+//   phase 1  the tile's slice of col/val is staged in shared memory with 128-bit coalesced
+//            streaming loads (all of a thread's loads are issued before the first use), together
+//            with the row ends of the tile's rows.
+//   phase 2  one of two block-uniform paths, chosen from the longest row piece in the tile:
+//     short rows  G lanes per row (G = 1, 2, ... 32), each lane walking its share of the row in
+//                 shared memory: sum += val * x[col]. With one or two lanes per row the lanes of a
+//                 warp are consecutive rows, so for banded / stencil matrices one gather
+//                 instruction touches a handful of L1 sectors instead of one per lane. Results are
+//                 written to y straight from registers.
+//     long rows   products are formed in place (lane-consecutive gathers), then each thread walks
+//                 WALK consecutive merge items (balanced whatever the row lengths); thread carries
+//                 (a row open at a thread boundary) are combined with a warp-shuffle segmented scan
+//                 and across the 8 warps in a fixed order; coalesced epilogue from shared memory.
+//   Both paths leave the sum of the row still open at the tile's end in carry_{row,val}[t].
+//
+// On B200 the L1 data pipe (wavefronts of the x gathers plus shared-memory traffic) saturates
+// before HBM does, so the kernel is organised to spend few L1 wavefronts per nonzero.
 // No atomics: every addition has a fixed place, so results are reproducible run to run.
 // VEC = false is the same kernel with scalar loads for arrays that are not 16-byte aligned.
 // ---------------------------------------------------------------------------------------
@@ -103,13 +110,16 @@ __global__ void __launch_bounds__(THREADS)
                      T* __restrict__ carry_val) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
-    constexpr int CPT = IPT / 4;  // 4-element chunks per thread in the unrolled pass
+    constexpr int CPT = IPT / 4;     // 4-element chunks per thread in the unrolled staging pass
+    constexpr int WALK = IPT + 1;    // merge items per thread in the long-row walk: odd, so that the
+                                     // stride-WALK shared reads of a warp fall in distinct banks
     static_assert(IPT % 4 == 0, "items per thread must be a multiple of 4");
 
-    __shared__ __align__(32) T s_buf[TILE + 8];  // products, then the row sums behind them
-    __shared__ int s_row_end[TILE + 4];
-    __shared__ int s_warp_row[NWARPS];
+    __shared__ __align__(32) T s_val[TILE + 8];  // values (then products); long-row path: row sums behind them
+    __shared__ __align__(16) int s_col[TILE + 8];  // column indices, then the tile's row ends behind them
+    __shared__ int s_warp_row[NWARPS];  // long-row path: last carry of each warp
     __shared__ T s_warp_sum[NWARPS];
+    __shared__ int s_warp_maxlen[NWARPS];
 
     const int tid = threadIdx.x;
     const int t = blockIdx.x;
@@ -121,23 +131,13 @@ __global__ void __launch_bounds__(THREADS)
     const int nnz_tile = nz_e - nz_s;
     const int tile_items = nrows + nnz_tile;
 
-    const int a0 = VEC ? (nz_s & ~3) : nz_s;  // products are stored at index (nonzero - a0)
+    const int a0 = VEC ? (nz_s & ~3) : nz_s;  // nonzero a0 + k is staged at index k
     const int head = nz_s - a0;
-    T* const s_prod = s_buf + head;             // s_prod[k]: k-th nonzero of the tile
-    T* const s_y = s_buf + head + nnz_tile;     // s_y[i]: row row_s + i, i in [0, nrows]
+    const int* const colv = s_col + head;  // colv[k], valv[k]: k-th nonzero of the tile
+    T* const valv = s_val + head;
+    int* const s_row_end = s_col + head + nnz_tile;  // nrows + 1 entries; nrows + nnz_tile <= TILE
 
-    // Row ends in tile-local nonzero coordinates; entry nrows is the row left open.
-    for (int i = tid; i <= nrows; i += THREADS) {
-        const int r = row_s + i;
-        int e = (r < m) ? __ldg(row_ptr + r + 1) - base : nz_e;
-        e = min(e, nz_e);
-        s_row_end[i] = e - nz_s;
-        s_y[i] = T(0);
-    }
-
-    // ---- phase 1
-    const int* const colb = col;
-    const T* const xb = x - base;
+    // ---- phase 1: stage col / val
     if (VEC) {
         const int nchunks = (head + nnz_tile + 3) >> 2;
         int4 cc[CPT];
@@ -149,17 +149,15 @@ __global__ void __launch_bounds__(THREADS)
             const int g = a0 + 4 * c;
             full[k] = (c < nchunks) && (g >= nz_s) && (g + 4 <= nz_e);
             if (full[k]) {
-                cc[k] = __ldcs(reinterpret_cast<const int4*>(colb + g));
+                cc[k] = __ldcs(reinterpret_cast<const int4*>(col + g));
                 vv[k].load(val + g);
             }
         }
 #pragma unroll
         for (int k = 0; k < CPT; ++k) {
             if (full[k]) {
-                const T x0 = __ldg(xb + cc[k].x), x1 = __ldg(xb + cc[k].y);
-                const T x2 = __ldg(xb + cc[k].z), x3 = __ldg(xb + cc[k].w);
-                Quad<T>::store(s_buf + 4 * (tid + k * THREADS), vv[k].get(0) * x0, vv[k].get(1) * x1,
-                               vv[k].get(2) * x2, vv[k].get(3) * x3);
+                *reinterpret_cast<int4*>(s_col + 4 * (tid + k * THREADS)) = cc[k];
+                vv[k].store(s_val + 4 * (tid + k * THREADS));
             }
         }
         // Ragged chunks (the tile's first and last) and the one chunk beyond the unrolled pass.
@@ -170,21 +168,92 @@ __global__ void __launch_bounds__(THREADS)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int gi = g + e;
-                    if (gi >= nz_s && gi < nz_e) s_buf[4 * c + e] = __ldcs(val + gi) * __ldg(xb + __ldcs(colb + gi));
+                    if (gi >= nz_s && gi < nz_e) {
+                        s_col[4 * c + e] = __ldcs(col + gi);
+                        s_val[4 * c + e] = __ldcs(val + gi);
+                    }
                 }
             }
         }
     } else {
         for (int k = tid; k < nnz_tile; k += THREADS) {
-            const int gi = nz_s + k;
-            s_prod[k] = __ldcs(val + gi) * __ldg(xb + __ldcs(colb + gi));
+            s_col[k] = __ldcs(col + nz_s + k);
+            s_val[k] = __ldcs(val + nz_s + k);
         }
     }
+
+    // Row ends in tile-local nonzero coordinates; entry nrows is the row left open.
+    // Alongside: the longest piece of a row inside this tile, which selects the phase-2 path.
+    int maxlen = 0;
+    for (int i = tid; i <= nrows; i += THREADS) {
+        const int r = row_s + i;
+        int e = (r < m) ? __ldg(row_ptr + r + 1) - base : nz_e;
+        e = min(e, nz_e);
+        const int b = (r < m) ? max(__ldg(row_ptr + r) - base, nz_s) : nz_e;
+        maxlen = max(maxlen, e - b);
+        s_row_end[i] = e - nz_s;
+    }
+    maxlen = __reduce_max_sync(0xffffffffu, maxlen);
+    if ((tid & 31) == 0) s_warp_maxlen[tid >> 5] = maxlen;
     __syncthreads();
 
-    // ---- phase 2: merge walk over this thread's IPT items
-    const int d0 = min(tid * IPT, tile_items);
-    const int d1 = min(d0 + IPT, tile_items);
+    // ---- phase 2
+    maxlen = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) maxlen = max(maxlen, s_warp_maxlen[w]);
+    int lgG = 0;
+    while ((32 << lgG) < maxlen) ++lgG;  // lanes per row so that each lane sums <= 32 products ...
+    while (lgG < 2 && ((nrows + 1) << (lgG + 1)) <= THREADS) ++lgG;  // ... and idle threads are put to use
+    const bool short_rows = lgG <= 5 && (((nrows + 1) << lgG) <= 8 * THREADS);
+    const T* const xb = x - base;
+    const T alpha = alpha_arg.get();
+    const T beta = beta_arg.get();
+
+    if (short_rows) {
+        const int G = 1 << lgG;
+        const int ngroups = THREADS >> lgG;
+        const int gidx = tid >> lgG, glane = tid & (G - 1);
+        for (int i0 = 0; i0 <= nrows; i0 += ngroups) {  // block-uniform trip count
+            const int i = i0 + gidx;
+            int b = 0, e = 0;
+            if (i <= nrows) {
+                b = (i == 0) ? 0 : s_row_end[i - 1];
+                e = s_row_end[i];
+            }
+            T sum = T(0);
+            int k = b + glane;
+            for (; k + 3 * G < e; k += 4 * G) {  // four independent gathers in flight per lane
+                const T x0 = __ldg(xb + colv[k]), x1 = __ldg(xb + colv[k + G]);
+                const T x2 = __ldg(xb + colv[k + 2 * G]), x3 = __ldg(xb + colv[k + 3 * G]);
+                sum += valv[k] * x0;
+                sum += valv[k + G] * x1;
+                sum += valv[k + 2 * G] * x2;
+                sum += valv[k + 3 * G] * x3;
+            }
+            for (; k < e; k += G) sum += valv[k] * __ldg(xb + colv[k]);
+            for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+            if (glane == 0 && i <= nrows) {
+                if (i < nrows) {
+                    T v = alpha * sum;
+                    if (beta != T(0)) v += beta * y[row_s + i];
+                    y[row_s + i] = v;
+                } else {
+                    carry_row[t] = row_s + nrows;
+                    carry_val[t] = sum;
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- long rows: products in place, merge walk, segmented reduction of the carries
+    T* const s_y = valv + nnz_tile;  // s_y[i]: row row_s + i, i in [0, nrows]
+    for (int k = tid; k < nnz_tile; k += THREADS) valv[k] *= __ldg(xb + colv[k]);
+    for (int i = tid; i <= nrows; i += THREADS) s_y[i] = T(0);
+    __syncthreads();
+
+    const int d0 = min(tid * WALK, tile_items);
+    const int d1 = min(d0 + WALK, tile_items);
     int lo = max(d0 - nnz_tile, 0), hi = min(d0, nrows);
     while (lo < hi) {
         const int mid = (lo + hi) >> 1;
@@ -198,10 +267,10 @@ __global__ void __launch_bounds__(THREADS)
     int end = s_row_end[r];
     T sum = T(0);
 #pragma unroll
-    for (int it = 0; it < IPT; ++it) {
+    for (int it = 0; it < WALK; ++it) {
         if (d0 + it < d1) {
             if (k < end) {
-                sum += s_prod[k];
+                sum += valv[k];
                 ++k;
             } else {
                 s_y[r] = sum;
@@ -212,7 +281,7 @@ __global__ void __launch_bounds__(THREADS)
         }
     }
 
-    // ---- phase 3: segmented reduction of the per-thread carries (key = r, value = sum)
+    // segmented reduction of the per-thread carries (key = r, value = sum)
     const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -235,9 +304,6 @@ __global__ void __launch_bounds__(THREADS)
     }
     __syncthreads();
 
-    // ---- phase 4
-    const T alpha = alpha_arg.get();
-    const T beta = beta_arg.get();
     for (int i = tid; i < nrows; i += THREADS) {
         T v = alpha * s_y[i];
         if (beta != T(0)) v += beta * y[row_s + i];
