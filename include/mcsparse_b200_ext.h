@@ -60,6 +60,34 @@ mcsparseStatus_t mcsparseB200ShardLocalRowOffsets(mcsparseHandle_t handle, const
                                                   int64_t firstRow, int64_t numRows,
                                                   mcsparseIndexBase_t idxBase, int32_t* localOffsets);
 
+/*
+ * mcsparseB200SpMVNoAlloc: y = alpha * A * x + beta * y like mcsparseSpMV, for callers that
+ * are not allowed to allocate device memory and therefore have no external buffer to pass:
+ * code running inside a memory-budgeted plugin or solver callback whose host hands it x and y
+ * but forbids cudaMalloc, code that must not trigger the implicit synchronisation of an
+ * allocation, or a late stage of a job whose memory is already fully committed. It has no
+ * counterpart in the reference, whose SpMV always takes a caller-allocated buffer.
+ *
+ * The merge-path partition and the per-tile carries are kept in a fixed array compiled into
+ * the library (MCSPARSE_B200_NOALLOC_SCRATCH_BYTES per GPU that loads it, held until the
+ * process exits). The call allocates nothing, on the host side of CUDA or through any library.
+ *   - Limit: the work area must hold the partition of (rows + nnz) merge items; larger
+ *     matrices are refused with MCSPARSE_STATUS_INSUFFICIENT_RESOURCES and a message on stderr
+ *     (about 8.5e8 items for fp64 values, 2.1e9 for fp32). Use mcsparseSpMV for those.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array and it keeps what the previous call left.
+ *     Every entry a call reads is written earlier in the same call, so nothing needs clearing,
+ *     but two calls that overlap on the GPU (different streams, or threads) would overwrite each
+ *     other's partition: run them one after the other.
+ * Arguments and status codes are those of mcsparseSpMV without the buffer.
+ */
+#define MCSPARSE_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
+mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                         mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                         mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                         mcsparseSpMVAlg_t alg);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,8 @@ MCSPARSE_STATUS_INVALID_VALUE = 3
 MCSPARSE_STATUS_EXECUTION_FAILED = 6
 MCSPARSE_STATUS_INTERNAL_ERROR = 7
 MCSPARSE_STATUS_NOT_SUPPORTED = 10
+MCSPARSE_STATUS_INSUFFICIENT_RESOURCES = 11
+NOALLOC_SCRATCH_BYTES = 8 << 20
 # operations
 MCSPARSE_OPERATION_NON_TRANSPOSE = 0
 MCSPARSE_OPERATION_TRANSPOSE = 1
@@ -107,6 +109,7 @@ PROTOTYPES = {
     "mcsparseDcsrmm2": (_i, _CSRMM2),
     "mcsparseScsrmm": (_i, _CSRMM),
     "mcsparseDcsrmm": (_i, _CSRMM),
+    "mcsparseB200SpMVNoAlloc": (_i, _SPMV_ARGS),
     "mcsparseB200SpMVPartitionView": (_i, [_vp, _vp, _pi, _pi64, _pvp]),
     "mcsparseB200ShardRowBounds": (_i, [_vp, _i64, _i64, _i, _vp, _i, _pi64]),
     "mcsparseB200ShardLocalRowOffsets": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),

@@ -697,6 +697,53 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
     return MCSPARSE_STATUS_SUCCESS;
 }
 
+// SpMV for callers that may not allocate device memory: same arithmetic and kernels as
+// mcsparseSpMV, with the work area taken from the fixed array inside the library instead of an
+// external buffer. Nothing here (or below it) allocates. The analysis is redone on every call
+// because the shared work area may have been used for another matrix in between.
+mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                         mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                         mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                         mcsparseSpMVAlg_t alg) {
+    (void)alg;
+    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, false, nullptr);
+    if (st != OK) return pub(st);
+    if (matA->rows == nullptr || matA->cols == nullptr || matA->vals == nullptr || vecX->values == nullptr ||
+        vecY->values == nullptr || matA->mat_descr == nullptr)
+        return pub(BAD_POINTER);
+    if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
+    DeviceGuard guard(handle->device);
+    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType));
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    cudaError_t e = spmv_static_scratch(&scratch, &scratch_bytes);
+    if (e != cudaSuccess) return pub(from_cuda(e));
+    if (ws.bytes > scratch_bytes) {
+        char msg[200];
+        std::snprintf(msg, sizeof msg,
+                      "mcsparseB200SpMVNoAlloc: matrix needs %zu bytes of work area, the built-in one has %zu; "
+                      "use mcsparseSpMV with an external buffer",
+                      ws.bytes, scratch_bytes);
+        log_error(msg);
+        return MCSPARSE_STATUS_INSUFFICIENT_RESOURCES;
+    }
+    const int base = matA->mat_descr->base;
+    const int32_t* rows = static_cast<const int32_t*>(matA->rows);
+    e = spmv_analysis(handle->stream, matA->row_num, matA->nnz, base, rows, ws, scratch);
+    if (e != cudaSuccess) return pub(from_cuda(e));
+    if (computeType == MACA_R_64F)
+        e = spmv_tiled<double>(handle->stream, matA->row_num, matA->nnz, base, rows,
+                               static_cast<const int32_t*>(matA->cols), static_cast<const double*>(matA->vals),
+                               static_cast<const double*>(vecX->values), static_cast<double*>(vecY->values),
+                               scalar_arg<double>(handle, alpha), scalar_arg<double>(handle, beta), ws, scratch);
+    else
+        e = spmv_tiled<float>(handle->stream, matA->row_num, matA->nnz, base, rows,
+                              static_cast<const int32_t*>(matA->cols), static_cast<const float*>(matA->vals),
+                              static_cast<const float*>(vecX->values), static_cast<float*>(vecY->values),
+                              scalar_arg<float>(handle, alpha), scalar_arg<float>(handle, beta), ws, scratch);
+    return pub(from_cuda(e));
+}
+
 // ----------------------------------------------------------------------------- SpMM
 
 mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperation_t opA, mcsparseOperation_t opB,

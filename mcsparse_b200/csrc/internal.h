@@ -93,6 +93,9 @@ cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
                           const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,
                           ScalarArg<T> beta);
 
+// Fixed device work area behind mcsparseB200SpMVNoAlloc (address on the current device).
+cudaError_t spmv_static_scratch(void** ptr, size_t* bytes);
+
 // Dense operand addressed as element(r, c) = ptr[r * row_stride + c * col_stride].
 template <typename T>
 cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,

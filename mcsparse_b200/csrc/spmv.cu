@@ -436,6 +436,37 @@ cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
     return launch_rowgroup<T, 32>(s, m, base, row_ptr, col, val, x, y, alpha, beta);
 }
 
+// ---------------------------------------------------------------------------------------
+// Built-in work area for mcsparseB200SpMVNoAlloc: callers that must not allocate device
+// memory (and so cannot size and provide the external buffer) get the partition and carry
+// arrays from this fixed array instead. It is part of the loaded module, so every GPU that
+// loads the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_spmv_static_scratch[MCSPARSE_B200_NOALLOC_SCRATCH_BYTES];
+
+// Device address of the array above on the current device. The array's name is only a
+// host-side handle for the symbol; kernels need the address cudaGetSymbolAddress reports for
+// the device that is current. Looked up once per device and remembered.
+cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex lock;
+    static void* cached[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> g(lock);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_spmv_static_scratch);
+        if (e != cudaSuccess) return e;
+        cached[dev] = p;
+    }
+    *ptr = cached[dev];
+    *bytes = sizeof(g_spmv_static_scratch);
+    return cudaSuccess;
+}
+
 #define INSTANTIATE(T)                                                                                         \
     template cudaError_t spmv_tiled<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,    \
                                        const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>,                     \
