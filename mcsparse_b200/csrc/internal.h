@@ -71,11 +71,12 @@ struct ScalarArg {
 };
 
 // Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
-//   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles]
+//   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status
+// status stays 0 unless a kernel gave up a bounded wait (zeroed by the analysis kernel).
 struct SpmvWorkspace {
     int items_per_tile = 0;
     int64_t num_tiles = 0;
-    size_t off_carry_row = 0, off_carry_val = 0, bytes = 0;
+    size_t off_carry_row = 0, off_carry_val = 0, off_status = 0, bytes = 0;
 };
 SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size);
 inline void* align_up_256(void* p) {

@@ -35,8 +35,10 @@ struct TileCfg<double> {
 // equal to a nonzero index is taken first) as the CPU partition it is checked against.
 // ---------------------------------------------------------------------------------------
 __global__ void merge_path_partition_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr,
-                                            int items_per_tile, long long num_tiles, int2* __restrict__ starts) {
+                                            int items_per_tile, long long num_tiles, int2* __restrict__ starts,
+                                            int* __restrict__ status) {
     long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t == 0) *status = 0;
     if (t > num_tiles) return;
     long long items = (long long)m + nnz;
     long long diag = t * items_per_tile;
@@ -54,37 +56,62 @@ __global__ void merge_path_partition_kernel(int m, int nnz, int base, const int*
 }
 
 // ---------------------------------------------------------------------------------------
-// Streaming 4-element loads of the matrix arrays (evict-first: A is read exactly once and
-// must not push x out of L2).
+// Bulk asynchronous copies (TMA, untiled form) and the mbarrier they complete on.
 // ---------------------------------------------------------------------------------------
-template <typename T>
-struct Quad;
-template <>
-struct Quad<float> {
-    float4 v;
-    __device__ __forceinline__ void load(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
-    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
-};
-template <>
-struct Quad<double> {
-    double2 lo, hi;
-    __device__ __forceinline__ void load(const double* p) {
-        lo = __ldcs(reinterpret_cast<const double2*>(p));
-        hi = __ldcs(reinterpret_cast<const double2*>(p) + 1);
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Global -> this CTA's shared memory; src, dst and bytes are multiples of 16. The data is read
+// exactly once, so it is marked evict-first in L2 to leave the cache to x.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar,
+                                              unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+// Waits for phase `parity` of the barrier for at most about a second of SM clocks. Returns
+// false on timeout, which the kernel reports in the status word instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 2000000000LL) return false;
     }
-    __device__ __forceinline__ void store(double* p) const {
-        reinterpret_cast<double2*>(p)[0] = lo;
-        reinterpret_cast<double2*>(p)[1] = hi;
-    }
-};
+    return true;
+}
 
 // ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
 //
-//   phase 1  the tile's slice of col/val is staged in shared memory with 128-bit coalesced
-//            streaming loads (all of a thread's loads are issued before the first use), together
-//            with the row ends of the tile's rows.
+//   phase 1  one thread issues two bulk asynchronous copies (TMA) that bring the tile's slice
+//            of col and val into shared memory, widened to 16-byte boundaries; the few elements
+//            such a boundary would push outside the arrays are fetched with ordinary loads.
+//            Meanwhile all threads stage the row ends of the tile's rows. The copies complete on
+//            an mbarrier. They cost no registers and no load/store-unit traffic, and a resident
+//            CTA keeps up to 24 KB in flight, which is what hides HBM latency here.
 //   phase 2  one of two block-uniform paths, chosen from the longest row piece in the tile:
 //     short rows  G lanes per row (G = 1, 2, ... 32), each lane walking its share of the row in
 //                 shared memory: sum += val * x[col]. With one or two lanes per row the lanes of a
@@ -99,24 +126,23 @@ struct Quad<double> {
 //
 // On B200 the L1 data pipe (wavefronts of the x gathers plus shared-memory traffic) saturates
 // before HBM does, so the kernel is organised to spend few L1 wavefronts per nonzero.
-// No atomics: every addition has a fixed place, so results are reproducible run to run.
-// VEC = false is the same kernel with scalar loads for arrays that are not 16-byte aligned.
+// No atomics on the data path: every addition has a fixed place, so results are reproducible.
 // ---------------------------------------------------------------------------------------
-template <typename T, int THREADS, int IPT, bool VEC>
+template <typename T, int THREADS, int IPT>
 __global__ void __launch_bounds__(THREADS)
-    spmv_tile_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+    spmv_tile_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
-                     T* __restrict__ carry_val) {
+                     T* __restrict__ carry_val, int* __restrict__ status) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
-    constexpr int CPT = IPT / 4;     // 4-element chunks per thread in the unrolled staging pass
-    constexpr int WALK = IPT + 1;    // merge items per thread in the long-row walk: odd, so that the
-                                     // stride-WALK shared reads of a warp fall in distinct banks
-    static_assert(IPT % 4 == 0, "items per thread must be a multiple of 4");
+    constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
+                                   // stride-WALK shared reads of a warp fall in distinct banks
+    constexpr int GV = 16 / (int)sizeof(T);  // values per 16 bytes
 
-    __shared__ __align__(32) T s_val[TILE + 8];  // values (then products); long-row path: row sums behind them
-    __shared__ __align__(16) int s_col[TILE + 8];  // column indices, then the tile's row ends behind them
+    __shared__ __align__(128) T s_val[TILE + 16];   // values (then products); long-row path: row sums behind them
+    __shared__ __align__(128) int s_col[TILE + 16];  // column indices, then the tile's row ends behind them
+    __shared__ __align__(8) unsigned long long s_mbar;
     __shared__ int s_warp_row[NWARPS];  // long-row path: last carry of each warp
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_warp_maxlen[NWARPS];
@@ -131,54 +157,50 @@ __global__ void __launch_bounds__(THREADS)
     const int nnz_tile = nz_e - nz_s;
     const int tile_items = nrows + nnz_tile;
 
-    const int a0 = VEC ? (nz_s & ~3) : nz_s;  // nonzero a0 + k is staged at index k
-    const int head = nz_s - a0;
-    const int* const colv = s_col + head;  // colv[k], valv[k]: k-th nonzero of the tile
-    T* const valv = s_val + head;
-    int* const s_row_end = s_col + head + nnz_tile;  // nrows + 1 entries; nrows + nnz_tile <= TILE
+    // Element nz_s + k of col is staged at s_col[head_c + k]; head_c is chosen so that the element
+    // at index 0 of s_col sits on a 16-byte boundary in global memory. Likewise for val.
+    const int head_c = (int)((reinterpret_cast<uintptr_t>(col) >> 2) + (unsigned)nz_s) & 3;
+    const int head_v = (int)((reinterpret_cast<uintptr_t>(val) / sizeof(T)) + (unsigned)nz_s) & (GV - 1);
+    const int* const colv = s_col + head_c;  // colv[k], valv[k]: k-th nonzero of the tile
+    T* const valv = s_val + head_v;
+    const int span_c = (head_c + nnz_tile + 3) & ~3;  // staged extent of s_col, in elements
+    int* const s_row_end = s_col + span_c;            // nrows + 1 entries; nrows + nnz_tile <= TILE
 
-    // ---- phase 1: stage col / val
-    if (VEC) {
-        const int nchunks = (head + nnz_tile + 3) >> 2;
-        int4 cc[CPT];
-        Quad<T> vv[CPT];
-        bool full[CPT];
-#pragma unroll
-        for (int k = 0; k < CPT; ++k) {
-            const int c = tid + k * THREADS;
-            const int g = a0 + 4 * c;
-            full[k] = (c < nchunks) && (g >= nz_s) && (g + 4 <= nz_e);
-            if (full[k]) {
-                cc[k] = __ldcs(reinterpret_cast<const int4*>(col + g));
-                vv[k].load(val + g);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < CPT; ++k) {
-            if (full[k]) {
-                *reinterpret_cast<int4*>(s_col + 4 * (tid + k * THREADS)) = cc[k];
-                vv[k].store(s_val + 4 * (tid + k * THREADS));
-            }
-        }
-        // Ragged chunks (the tile's first and last) and the one chunk beyond the unrolled pass.
-        for (int c = tid; c < nchunks; c += THREADS) {
-            const int g = a0 + 4 * c;
-            const bool done = (c < CPT * THREADS) && (g >= nz_s) && (g + 4 <= nz_e);
-            if (!done) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int gi = g + e;
-                    if (gi >= nz_s && gi < nz_e) {
-                        s_col[4 * c + e] = __ldcs(col + gi);
-                        s_val[4 * c + e] = __ldcs(val + gi);
-                    }
-                }
-            }
-        }
-    } else {
-        for (int k = tid; k < nnz_tile; k += THREADS) {
-            s_col[k] = __ldcs(col + nz_s + k);
-            s_val[k] = __ldcs(val + nz_s + k);
+    // ---- phase 1: bulk copies of the 16-byte aligned part that lies inside the arrays
+    int lo_c = nz_s - head_c, hi_c = lo_c + span_c;  // global element range of the col copy
+    if (lo_c < 0) lo_c += 4;
+    if (hi_c > nnz) hi_c -= 4;
+    int lo_v = nz_s - head_v, hi_v = lo_v + ((head_v + nnz_tile + GV - 1) & ~(GV - 1));
+    if (lo_v < 0) lo_v += GV;
+    if (hi_v > nnz) hi_v -= GV;
+    const bool copy_c = hi_c > lo_c, copy_v = hi_v > lo_v;
+    if (tid == 0) mbar_init(&s_mbar, 1);
+    __syncthreads();
+    if (tid == 0 && (copy_c || copy_v)) {
+        const unsigned long long policy = l2_evict_first_policy();
+        const uint32_t bytes_c = copy_c ? (uint32_t)(hi_c - lo_c) * 4u : 0u;
+        const uint32_t bytes_v = copy_v ? (uint32_t)(hi_v - lo_v) * (uint32_t)sizeof(T) : 0u;
+        mbar_expect_tx(&s_mbar, bytes_c + bytes_v);
+        if (copy_c) bulk_copy_g2s(s_col + (lo_c - (nz_s - head_c)), col + lo_c, bytes_c, &s_mbar, policy);
+        if (copy_v) bulk_copy_g2s(s_val + (lo_v - (nz_s - head_v)), val + lo_v, bytes_v, &s_mbar, policy);
+    }
+    // Elements of the tile that the aligned copies leave out: at most 3 at either end of an array
+    // (all of the tile, at most 6 elements, when no aligned group lies inside the array).
+    // Lanes 0-15 of warp 0 handle col, lanes 16-31 val; sub-lanes 0-7 the front part, 8-15 the back.
+    if (tid < 32) {
+        const bool is_val = tid >= 16;
+        const int u = tid & 15;
+        const bool cp = is_val ? copy_v : copy_c;
+        const int lo = is_val ? lo_v : lo_c, hi = is_val ? hi_v : hi_c;
+        const int front = cp ? max(0, min(lo, nz_e) - nz_s) : nnz_tile;
+        const int back0 = cp ? max(hi, nz_s) : nz_e;
+        const int g = u < 8 ? nz_s + u : back0 + (u - 8);
+        const bool mine = u < 8 ? (u < front) : (g < nz_e);
+        if (mine) {
+            if (is_val)
+                s_val[head_v + (g - nz_s)] = __ldcs(val + g);
+            else
+                s_col[head_c + (g - nz_s)] = __ldcs(col + g);
         }
     }
 
@@ -195,6 +217,13 @@ __global__ void __launch_bounds__(THREADS)
     }
     maxlen = __reduce_max_sync(0xffffffffu, maxlen);
     if ((tid & 31) == 0) s_warp_maxlen[tid >> 5] = maxlen;
+    if (copy_c || copy_v) {
+        if (!mbar_wait_bounded(&s_mbar, 0)) {  // never expected; reported, not spun on
+            if (tid == 0) atomicExch(status, 1);
+            mbar_wait_bounded(&s_mbar, 0);
+            return;
+        }
+    }
     __syncthreads();
 
     // ---- phase 2
@@ -372,7 +401,8 @@ SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size) {
     auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
     ws.off_carry_row = up(size_t(ws.num_tiles + 1) * 8);
     ws.off_carry_val = ws.off_carry_row + up(size_t(ws.num_tiles) * 4);
-    ws.bytes = ws.off_carry_val + up(size_t(ws.num_tiles) * value_size);
+    ws.off_status = ws.off_carry_val + up(size_t(ws.num_tiles) * value_size);
+    ws.bytes = ws.off_status + 256;
     return ws;
 }
 
@@ -381,8 +411,9 @@ cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
     const long long n = ws.num_tiles + 1;
     const int threads = 128;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
-    merge_path_partition_kernel<<<blocks, threads, 0, s>>>((int)m, (int)nnz, base, row_ptr, ws.items_per_tile,
-                                                           ws.num_tiles, reinterpret_cast<int2*>(buf));
+    merge_path_partition_kernel<<<blocks, threads, 0, s>>>(
+        (int)m, (int)nnz, base, row_ptr, ws.items_per_tile, ws.num_tiles, reinterpret_cast<int2*>(buf),
+        reinterpret_cast<int*>(static_cast<char*>(buf) + ws.off_status));
     return cudaGetLastError();
 }
 
@@ -390,22 +421,16 @@ template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
                        const SpmvWorkspace& ws, void* buf) {
-    (void)nnz;
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     constexpr int IPT = TileCfg<T>::kItemsPerThread;
-    const bool aligned =
-        ((reinterpret_cast<uintptr_t>(col) | reinterpret_cast<uintptr_t>(val)) & 15) == 0;
+    int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
     const unsigned grid = (unsigned)ws.num_tiles;
-    if (aligned)
-        spmv_tile_kernel<T, kThreads, IPT, true><<<grid, kThreads, 0, s>>>(
-            (int)m, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val);
-    else
-        spmv_tile_kernel<T, kThreads, IPT, false><<<grid, kThreads, 0, s>>>(
-            (int)m, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val);
+    spmv_tile_kernel<T, kThreads, IPT><<<grid, kThreads, 0, s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha,
+                                                                 beta, starts, carry_row, carry_val, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const int threads = 256;
