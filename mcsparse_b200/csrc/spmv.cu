@@ -9,6 +9,7 @@
 // organised around wide, coalesced, streaming loads of col/val with many bytes in flight
 // per SM, while x is gathered through L1/L2 with default caching.
 #include <cstdio>
+#include <cstdlib>
 
 #include "internal.h"
 
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ int s_warp_row[NWARPS];  // long-row path: last carry of each warp
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_warp_maxlen[NWARPS];
+    __shared__ int s_failed;
 
     const int tid = threadIdx.x;
     const int t = blockIdx.x;
@@ -217,14 +219,19 @@ __global__ void __launch_bounds__(THREADS)
     }
     maxlen = __reduce_max_sync(0xffffffffu, maxlen);
     if ((tid & 31) == 0) s_warp_maxlen[tid >> 5] = maxlen;
-    if (copy_c || copy_v) {
-        if (!mbar_wait_bounded(&s_mbar, 0)) {  // never expected; reported, not spun on
-            if (tid == 0) atomicExch(status, 1);
-            mbar_wait_bounded(&s_mbar, 0);
-            return;
+    // One thread polls the barrier (a whole CTA polling would crowd the shared-memory pipe that the
+    // other resident CTAs need); the block barrier then publishes the copied data to everyone.
+    if (tid == 0) {
+        int failed = 0;
+        if ((copy_c || copy_v) && !mbar_wait_bounded(&s_mbar, 0)) {  // never expected; reported, not spun on
+            atomicExch(status, 1);
+            mbar_wait_bounded(&s_mbar, 0);  // second bounded wait for the copies before giving the tile up
+            failed = 1;
         }
+        s_failed = failed;
     }
     __syncthreads();
+    if (s_failed) return;
 
     // ---- phase 2
     maxlen = 0;
@@ -277,7 +284,20 @@ __global__ void __launch_bounds__(THREADS)
 
     // ---- long rows: products in place, merge walk, segmented reduction of the carries
     T* const s_y = valv + nnz_tile;  // s_y[i]: row row_s + i, i in [0, nrows]
-    for (int k = tid; k < nnz_tile; k += THREADS) valv[k] *= __ldg(xb + colv[k]);
+    {
+        // Lane-consecutive nonzeros; all of a thread's gathers are issued before the first product.
+        T xv[IPT];
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) {
+            const int k = tid + j * THREADS;
+            xv[j] = (k < nnz_tile) ? __ldg(xb + colv[k]) : T(0);
+        }
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) {
+            const int k = tid + j * THREADS;
+            if (k < nnz_tile) valv[k] *= xv[j];
+        }
+    }
     for (int i = tid; i <= nrows; i += THREADS) s_y[i] = T(0);
     __syncthreads();
 
@@ -417,6 +437,16 @@ cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
     return cudaGetLastError();
 }
 
+// Extra dynamic shared memory per CTA (bytes), read once from MCSPARSE_B200_SPMV_PAD_SMEM: lowers
+// the number of resident CTAs per SM for tuning experiments. 0 (the default) in normal use.
+static size_t tuning_pad_smem() {
+    static const size_t pad = [] {
+        const char* v = std::getenv("MCSPARSE_B200_SPMV_PAD_SMEM");
+        return v ? (size_t)std::strtoul(v, nullptr, 10) : (size_t)0;
+    }();
+    return pad;
+}
+
 template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
@@ -429,7 +459,7 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const i
     constexpr int IPT = TileCfg<T>::kItemsPerThread;
     int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
     const unsigned grid = (unsigned)ws.num_tiles;
-    spmv_tile_kernel<T, kThreads, IPT><<<grid, kThreads, 0, s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha,
+    spmv_tile_kernel<T, kThreads, IPT><<<grid, kThreads, tuning_pad_smem(), s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha,
                                                                  beta, starts, carry_row, carry_val, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
