@@ -121,30 +121,36 @@ class SpmvJob:
         self.cfg, self.world, self.rank = cfg, world, rank
         self.vsize = 8 if cfg.dtype == torch.float64 else 4
         lengths = workloads.row_lengths(cfg, device)
-        self.total_nnz = int(lengths.sum().item())
         if world > 1:
-            # nnz-balanced contiguous row blocks (same rule as mcsparseB200ShardRowBounds)
-            ptr = torch.zeros(cfg.rows + 1, dtype=torch.int64, device=device)
-            torch.cumsum(lengths, 0, out=ptr[1:])
-            targets = torch.tensor([(g * self.total_nnz) // world for g in range(world + 1)], device=device)
-            bounds = torch.searchsorted(ptr, targets, right=False).tolist()
-            bounds[0], bounds[-1] = 0, cfg.rows
-            del ptr, targets
+            from mcsparse_b200 import sharding
+
+            bounds, self.total_nnz = sharding.shard_bounds(lengths, world)  # nnz-balanced contiguous row blocks
         else:
-            bounds = [0, cfg.rows]
+            bounds, self.total_nnz = [0, cfg.rows], int(lengths.sum().item())
         del lengths
         self.bounds = bounds
         r0, r1 = bounds[rank], bounds[rank + 1]
         w = workloads.generate(cfg, device, row_range=(r0, r1))
         self.w = w
-        self.y_full = torch.zeros(cfg.rows, dtype=cfg.dtype, device=device)
-        if cfg.beta != 0:
-            self.y_full[r0:r1] = w.y0
-        self.y = self.y_full[r0:r1]
         self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
-        self.X, self.Y = mc.DnVec(w.x), mc.DnVec(self.y)
-        self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y), dtype=torch.uint8, device=device)
-        mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf)
+        if world > 1:
+            from mcsparse_b200 import sharding
+
+            # product path: the kernel pushes finished rows into every peer's y over NVLink
+            self.sharded = sharding.ShardedSpmv(handle, self.A, w.x, r0, cfg.rows)
+            self.y_full = self.sharded.y.tensor
+            self.y = self.sharded.y_local
+            self.X, self.Y, self.buf = self.sharded.X, self.sharded.Y, self.sharded.buffer
+        else:
+            self.sharded = None
+            self.y_full = torch.zeros(cfg.rows, dtype=cfg.dtype, device=device)
+            self.y = self.y_full[r0:r1]
+            self.X, self.Y = mc.DnVec(w.x), mc.DnVec(self.y)
+            self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y), dtype=torch.uint8,
+                                   device=device)
+            mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf)
+        if cfg.beta != 0:
+            self.y.copy_(w.y0)
         self.parts = [self.y_full[bounds[g]:bounds[g + 1]] for g in range(world)]
         self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta)
         self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta)
@@ -152,14 +158,22 @@ class SpmvJob:
         self.launches_per_step = 2  # tile kernel + carry fix-up
 
     def compute(self):
+        """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""
         self.mc.spmv(self.h, self.A, self.X, self.Y, self.buf, alpha=self.cfg.alpha, beta=self.cfg.beta)
 
     def step(self):
-        self.compute()
-        if self.world > 1:
-            import torch.distributed as dist
+        """One full step: at N > 1 the SpMV with the fused push of y to all GPUs, then the ordering collective."""
+        if self.sharded is not None:
+            self.sharded.step(self.cfg.alpha, self.cfg.beta)
+        else:
+            self.compute()
 
-            dist.all_gather(self.parts, self.y)
+    def step_allgather(self):
+        """Baseline assembly for comparison: local SpMV, then a ragged NCCL all-gather of y."""
+        from mcsparse_b200 import sharding
+
+        self.compute()
+        sharding.all_gather_ragged(self.parts, self.y)
 
 
 class SpmmJob:
@@ -336,10 +350,14 @@ def run_gpu(args, rank, world, local_rank):
     _, per_compute = time_steps(torch, job.compute, max(10, args.steps // 4), args.warmup, flush, barrier)
     with ClockSampler(visible_device_index(local_rank)) as clocks:
         total_ms, per = time_steps(torch, job.step, args.steps, args.warmup, flush, barrier)
-    t = torch.tensor([total_ms, statistics.mean(per_compute)], dtype=torch.float64, device=device)
+    ag_ms = 0.0
+    if world > 1:
+        ag_total, _ = time_steps(torch, job.step_allgather, max(10, args.steps // 4), args.warmup, flush, barrier)
+        ag_ms = ag_total / max(10, args.steps // 4)
+    t = torch.tensor([total_ms, statistics.mean(per_compute), ag_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, compute_ms = t.tolist()
+    total_ms, compute_ms, ag_ms = t.tolist()
     ms_per_step = total_ms / args.steps
     value = job.bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -369,7 +387,8 @@ def run_gpu(args, rank, world, local_rank):
             "config": {"workload": workload_label(args.workload) + ("" if args.scale == 1 else f" / {args.scale}"), "rows": job.cfg.rows, "nnz": job.total_nnz,
                        "alpha": job.cfg.alpha, "beta": job.cfg.beta, "index_base": 0,
                        "sharding": "replicas only (N=1)" if world == 1 else
-                       f"{world} nnz-balanced row blocks, x replicated, y all-gathered (NCCL)",
+                       f"{world} nnz-balanced row blocks, x replicated, y rows pushed to every GPU by the kernel over "
+                       "NVLink peer stores + one 4-byte NCCL all-reduce per step to order the GPUs",
                        "l2": "inputs exceed L2" if flush is None else "L2 flushed between steps",
                        "algorithmic_bytes": job.bytes},
             "gflops": round(job.flops / (ms_per_step * 1e-3) / 1e9, 1),
@@ -381,6 +400,10 @@ def run_gpu(args, rank, world, local_rank):
                     "h2d_bytes_per_step": x_host.numel() * job.vsize, "d2h_bytes_per_step": y_host.numel() * job.vsize,
                     "ms_per_step": round(e2e_ms, 4)},
             "gpu_launches": job.launches_per_step * args.steps,
+            "multi_gpu": None if world == 1 else {
+                "kernel_only_ms": round(compute_ms, 5), "fused_push_ms": round(ms_per_step, 5),
+                "nccl_allgather_ms": round(ag_ms, 5),
+                "nvlink_lower_bound_ms": round((world - 1) / world * job.cfg.rows * job.vsize / 770e9 * 1e3, 5)},
             "clocks": clocks.summary(),
         }
         if world == 1 and args.scale == 1:
@@ -403,6 +426,7 @@ def run_gpu(args, rank, world, local_rank):
             line["configs"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
+        job.sharded.close()
         dist.barrier()
         dist.destroy_process_group()
 

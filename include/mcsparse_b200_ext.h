@@ -61,6 +61,36 @@ mcsparseStatus_t mcsparseB200ShardLocalRowOffsets(mcsparseHandle_t handle, const
                                                   mcsparseIndexBase_t idxBase, int32_t* localOffsets);
 
 /*
+ * Row-sharded SpMV with the assembly of y fused into the kernel. Same arguments as
+ * mcsparseSpMV for this GPU's row block (matA: the block with local row offsets; vecX: the
+ * full x; vecY: this block's slice of the local full-length y), plus the destinations of the
+ * push: peerY[p] is the full-length y of another GPU as an address valid on this device
+ * (see mcsparseB200PeerOpen), rowOffset the global index of the block's first row. Every
+ * finished y value is stored to vecY and to peerY[p][rowOffset + row] for all p, with
+ * ordinary stores over NVLink while the kernel runs; no separate all-gather of y is needed.
+ * The caller orders the GPUs afterwards (any collective or barrier on the same streams)
+ * before x is overwritten or y is read. numPeers <= 7. The reference is single-device
+ * (mcsparse/src/common/mcsp_handle.cpp:5-8); this call has no counterpart there.
+ */
+mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                      mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                      mcsparseDnVecDescr_t vecY, macaDataType computeType, mcsparseSpMVAlg_t alg,
+                                      void* externalBuffer, int numPeers, void* const* peerY, int64_t rowOffset);
+
+/*
+ * Device buffers that other processes on the same node can map (one process per GPU):
+ * PeerAlloc/PeerFree allocate with the plain CUDA allocator; PeerExport fills a 64-byte
+ * handle that another process passes to PeerOpen to obtain an address valid on its current
+ * device (peer access is enabled on first use); PeerClose unmaps it. No reference counterpart.
+ */
+#define MCSPARSE_B200_PEER_HANDLE_BYTES 64
+mcsparseStatus_t mcsparseB200PeerAlloc(void** devPtr, size_t bytes);
+mcsparseStatus_t mcsparseB200PeerFree(void* devPtr);
+mcsparseStatus_t mcsparseB200PeerExport(void* devPtr, void* handleOut);
+mcsparseStatus_t mcsparseB200PeerOpen(const void* handleIn, void** mappedPtr);
+mcsparseStatus_t mcsparseB200PeerClose(void* mappedPtr);
+
+/*
  * mcsparseB200SpMVNoAlloc: y = alpha * A * x + beta * y like mcsparseSpMV, for callers that
  * are not allowed to allocate device memory and therefore have no external buffer to pass:
  * code running inside a memory-budgeted plugin or solver callback whose host hands it x and y

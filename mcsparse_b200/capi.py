@@ -110,6 +110,12 @@ PROTOTYPES = {
     "mcsparseScsrmm": (_i, _CSRMM),
     "mcsparseDcsrmm": (_i, _CSRMM),
     "mcsparseB200SpMVNoAlloc": (_i, _SPMV_ARGS),
+    "mcsparseB200SpMVPush": (_i, _SPMV_ARGS + [_vp, _i, _pvp, _i64]),
+    "mcsparseB200PeerAlloc": (_i, [_pvp, _sz]),
+    "mcsparseB200PeerFree": (_i, [_vp]),
+    "mcsparseB200PeerExport": (_i, [_vp, _vp]),
+    "mcsparseB200PeerOpen": (_i, [_vp, _pvp]),
+    "mcsparseB200PeerClose": (_i, [_vp]),
     "mcsparseB200SpMVPartitionView": (_i, [_vp, _vp, _pi, _pi64, _pvp]),
     "mcsparseB200ShardRowBounds": (_i, [_vp, _i64, _i64, _i, _vp, _i, _pi64]),
     "mcsparseB200ShardLocalRowOffsets": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),

@@ -131,9 +131,16 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     return OK;
 }
 
+struct PushArgs {
+    int count = 0;
+    void* const* y = nullptr;
+    int64_t row_offset = 0;
+};
+
 template <typename T>
 St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
-            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute) {
+            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute,
+            const PushArgs& push = PushArgs()) {
     const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T));
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
@@ -143,16 +150,20 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mc
         if (e != cudaSuccess) return from_cuda(e);
     }
     if (!compute) return OK;
+    PeerList<T> peers;
+    peers.count = push.count;
+    peers.row_offset = push.row_offset;
+    for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
     cudaError_t e = spmv_tiled<T>(h->stream, A->row_num, A->nnz, base, rows, static_cast<const int32_t*>(A->cols),
                                   static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
                                   static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
-                                  buf);
+                                  buf, peers);
     return from_cuda(e);
 }
 
 St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
-              void* buffer, bool preprocess_only) {
+              void* buffer, bool preprocess_only, const PushArgs& push = PushArgs()) {
     St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr);
     if (st != OK) return st;
     // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
@@ -175,8 +186,8 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         }
     }
     if (computeType == MACA_R_64F)
-        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only);
-    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only);
+        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, push);
+    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, push);
 }
 
 // Legacy csrmv family: raw arrays plus a matrix descriptor
@@ -881,6 +892,51 @@ mcsparseStatus_t mcsparseDcsrmm(mcsparseHandle_t handle, mcsparseOperation_t tra
 }
 
 // ----------------------------------------------------------------------------- sharding helpers
+
+mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                      mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                      mcsparseDnVecDescr_t vecY, macaDataType computeType, mcsparseSpMVAlg_t alg,
+                                      void* externalBuffer, int numPeers, void* const* peerY, int64_t rowOffset) {
+    (void)alg;
+    if (numPeers < 0 || numPeers > PeerList<float>::kMax || rowOffset < 0) return pub(BAD_SIZE);
+    if (numPeers > 0 && peerY == nullptr) return pub(BAD_POINTER);
+    for (int p = 0; p < numPeers; ++p)
+        if (peerY[p] == nullptr) return pub(BAD_POINTER);
+    PushArgs push;
+    push.count = numPeers;
+    push.y = peerY;
+    push.row_offset = rowOffset;
+    return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
+}
+
+mcsparseStatus_t mcsparseB200PeerAlloc(void** devPtr, size_t bytes) {
+    if (devPtr == nullptr) return pub(BAD_POINTER);
+    return pub(from_cuda(cudaMalloc(devPtr, bytes)));
+}
+
+mcsparseStatus_t mcsparseB200PeerFree(void* devPtr) { return pub(from_cuda(cudaFree(devPtr))); }
+
+mcsparseStatus_t mcsparseB200PeerExport(void* devPtr, void* handleOut) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == MCSPARSE_B200_PEER_HANDLE_BYTES, "handle size");
+    if (devPtr == nullptr || handleOut == nullptr) return pub(BAD_POINTER);
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, devPtr);
+    if (e != cudaSuccess) return pub(from_cuda(e));
+    std::memcpy(handleOut, &h, sizeof h);
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseB200PeerOpen(const void* handleIn, void** mappedPtr) {
+    if (handleIn == nullptr || mappedPtr == nullptr) return pub(BAD_POINTER);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handleIn, sizeof h);
+    return pub(from_cuda(cudaIpcOpenMemHandle(mappedPtr, h, cudaIpcMemLazyEnablePeerAccess)));
+}
+
+mcsparseStatus_t mcsparseB200PeerClose(void* mappedPtr) {
+    if (mappedPtr == nullptr) return MCSPARSE_STATUS_SUCCESS;
+    return pub(from_cuda(cudaIpcCloseMemHandle(mappedPtr)));
+}
 
 mcsparseStatus_t mcsparseB200ShardRowBounds(mcsparseHandle_t handle, int64_t rows, int64_t nnz,
                                             mcsparseIndexBase_t idxBase, const int32_t* rowOffsets, int numShards,

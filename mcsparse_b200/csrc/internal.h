@@ -70,6 +70,16 @@ struct ScalarArg {
 #endif
 };
 
+// Destinations of the fused row push of a row-sharded SpMV: the full-length y vectors of the
+// other GPUs (addresses valid on this device) and the global index of this shard's first row.
+template <typename T>
+struct PeerList {
+    static constexpr int kMax = 7;
+    int count = 0;
+    long long row_offset = 0;
+    T* y[kMax] = {};
+};
+
 // Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
 //   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status
 // status stays 0 unless a kernel gave up a bounded wait (zeroed by the analysis kernel).
@@ -88,7 +98,7 @@ cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
 template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
-                       const SpmvWorkspace& ws, void* buf);
+                       const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers = PeerList<T>());
 template <typename T>
 cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                           const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,

@@ -103,6 +103,23 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
     return true;
 }
 
+// Explicit fused multiply-add: the same rounding in every instantiation of the kernels (left
+// to the compiler, contraction choices differed between template variants by one ulp).
+__device__ __forceinline__ float mad(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double mad(double a, double b, double c) { return fma(a, b, c); }
+
+// PUSH variants: a finished y value is also stored, with ordinary global stores through
+// peer-mapped pointers, into the full-length y of every other GPU of a row-sharded run, at
+// the row's global position. The NVLink traffic thus overlaps the kernel instead of
+// following it as a separate all-gather. A row that continues from an earlier tile is the
+// exception: its value is final only after the carry fix-up, which pushes it then.
+template <typename T>
+__device__ __forceinline__ void push_to_peers(const PeerList<T>& peers, long long row, T v) {
+#pragma unroll
+    for (int p = 0; p < PeerList<T>::kMax; ++p)
+        if (p < peers.count) peers.y[p][peers.row_offset + row] = v;
+}
+
 // ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
@@ -129,12 +146,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
 // before HBM does, so the kernel is organised to spend few L1 wavefronts per nonzero.
 // No atomics on the data path: every addition has a fixed place, so results are reproducible.
 // ---------------------------------------------------------------------------------------
-template <typename T, int THREADS, int IPT>
+template <typename T, int THREADS, int IPT, bool PUSH>
 __global__ void __launch_bounds__(THREADS)
     spmv_tile_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
-                     T* __restrict__ carry_val, int* __restrict__ status) {
+                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
     constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
@@ -158,6 +175,8 @@ __global__ void __launch_bounds__(THREADS)
     const int nz_e = s1.y;
     const int nnz_tile = nz_e - nz_s;
     const int tile_items = nrows + nnz_tile;
+    // The tile's first row started in an earlier tile: its sum here is partial until the fix-up.
+    const bool continued = PUSH && row_s < m && nz_s > __ldg(row_ptr + row_s) - base;
 
     // Element nz_s + k of col is staged at s_col[head_c + k]; head_c is chosen so that the element
     // at index 0 of s_col sits on a 16-byte boundary in global memory. Likewise for val.
@@ -261,18 +280,19 @@ __global__ void __launch_bounds__(THREADS)
             for (; k + 3 * G < e; k += 4 * G) {  // four independent gathers in flight per lane
                 const T x0 = __ldg(xb + colv[k]), x1 = __ldg(xb + colv[k + G]);
                 const T x2 = __ldg(xb + colv[k + 2 * G]), x3 = __ldg(xb + colv[k + 3 * G]);
-                sum += valv[k] * x0;
-                sum += valv[k + G] * x1;
-                sum += valv[k + 2 * G] * x2;
-                sum += valv[k + 3 * G] * x3;
+                sum = mad(valv[k], x0, sum);
+                sum = mad(valv[k + G], x1, sum);
+                sum = mad(valv[k + 2 * G], x2, sum);
+                sum = mad(valv[k + 3 * G], x3, sum);
             }
-            for (; k < e; k += G) sum += valv[k] * __ldg(xb + colv[k]);
+            for (; k < e; k += G) sum = mad(valv[k], __ldg(xb + colv[k]), sum);
             for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
             if (glane == 0 && i <= nrows) {
                 if (i < nrows) {
                     T v = alpha * sum;
-                    if (beta != T(0)) v += beta * y[row_s + i];
+                    if (beta != T(0)) v = mad(beta, y[row_s + i], v);
                     y[row_s + i] = v;
+                    if (PUSH && !(i == 0 && continued)) push_to_peers(peers, row_s + i, v);
                 } else {
                     carry_row[t] = row_s + nrows;
                     carry_val[t] = sum;
@@ -355,8 +375,9 @@ __global__ void __launch_bounds__(THREADS)
 
     for (int i = tid; i < nrows; i += THREADS) {
         T v = alpha * s_y[i];
-        if (beta != T(0)) v += beta * y[row_s + i];
+        if (beta != T(0)) v = mad(beta, y[row_s + i], v);
         y[row_s + i] = v;
+        if (PUSH && !(i == 0 && continued)) push_to_peers(peers, row_s + i, v);
     }
     if (tid == 0) {
         carry_row[t] = row_s + nrows;
@@ -366,9 +387,10 @@ __global__ void __launch_bounds__(THREADS)
 
 // Adds the carries of rows that cross tile boundaries. The first tile of each run of equal
 // carry rows sums the run in tile order, so the result does not depend on scheduling.
-template <typename T>
+template <typename T, bool PUSH>
 __global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* __restrict__ carry_row,
-                                        const T* __restrict__ carry_val, T* __restrict__ y, ScalarArg<T> alpha_arg) {
+                                        const T* __restrict__ carry_val, T* __restrict__ y, ScalarArg<T> alpha_arg,
+                                        PeerList<T> peers) {
     long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (t >= num_tiles) return;
     const int r = carry_row[t];
@@ -376,7 +398,9 @@ __global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* _
     if (t > 0 && carry_row[t - 1] == r) return;
     T sum = carry_val[t];
     for (long long u = t + 1; u < num_tiles && carry_row[u] == r; ++u) sum += carry_val[u];
-    y[r] += alpha_arg.get() * sum;
+    const T v = mad(alpha_arg.get(), sum, y[r]);
+    y[r] = v;
+    if (PUSH) push_to_peers(peers, r, v);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -396,14 +420,14 @@ __global__ void __launch_bounds__(kThreads)
     if (active) {
         const int j0 = __ldg(row_ptr + gid) - base, j1 = __ldg(row_ptr + gid + 1) - base;
         const T* xb = x - base;
-        for (int j = j0 + lane; j < j1; j += G) sum += __ldcs(val + j) * __ldg(xb + __ldcs(col + j));
+        for (int j = j0 + lane; j < j1; j += G) sum = mad(__ldcs(val + j), __ldg(xb + __ldcs(col + j)), sum);
     }
 #pragma unroll
     for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, G);
     if (active && lane == 0) {
         const T alpha = alpha_arg.get(), beta = beta_arg.get();
         T v = alpha * sum;
-        if (beta != T(0)) v += beta * y[gid];
+        if (beta != T(0)) v = mad(beta, y[gid], v);
         y[gid] = v;
     }
 }
@@ -450,7 +474,7 @@ static size_t tuning_pad_smem() {
 template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
-                       const SpmvWorkspace& ws, void* buf) {
+                       const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers) {
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
@@ -459,13 +483,22 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const i
     constexpr int IPT = TileCfg<T>::kItemsPerThread;
     int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
     const unsigned grid = (unsigned)ws.num_tiles;
-    spmv_tile_kernel<T, kThreads, IPT><<<grid, kThreads, tuning_pad_smem(), s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha,
-                                                                 beta, starts, carry_row, carry_val, status);
+    const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
+    if (peers.count > 0) {
+        spmv_tile_kernel<T, kThreads, IPT, true><<<grid, kThreads, tuning_pad_smem(), s>>>(
+            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
+                                                                  peers);
+        return cudaGetLastError();
+    }
+    spmv_tile_kernel<T, kThreads, IPT, false><<<grid, kThreads, tuning_pad_smem(), s>>>(
+        (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const int threads = 256;
-    spmv_carry_fixup_kernel<T><<<(unsigned)((ws.num_tiles + threads - 1) / threads), threads, 0, s>>>(
-        (int)m, ws.num_tiles, carry_row, carry_val, y, alpha);
+    spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
+                                                               peers);
     return cudaGetLastError();
 }
 
@@ -525,7 +558,7 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
 #define INSTANTIATE(T)                                                                                         \
     template cudaError_t spmv_tiled<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,    \
                                        const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>,                     \
-                                       const SpmvWorkspace&, void*);                                           \
+                                       const SpmvWorkspace&, void*, const PeerList<T>&);                       \
     template cudaError_t spmv_rowgroup<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, \
                                           const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>);
 INSTANTIATE(float)

@@ -50,7 +50,7 @@ class Handle:
         self.pointer_mode = mode
 
     def close(self):
-        if self.h is not None:
+        if self.h is not None and lib is not None:
             lib.mcsparseDestroy(self.h)
             self.h = None
 
@@ -77,7 +77,7 @@ class CsrMatrix:
         return self.values.dtype
 
     def __del__(self):
-        if getattr(self, "d", None) is not None:
+        if getattr(self, "d", None) is not None and lib is not None:  # lib is None at interpreter shutdown
             lib.mcsparseDestroySpMat(self.d)
             self.d = None
 
@@ -91,7 +91,7 @@ class DnVec:
         self.d = d
 
     def __del__(self):
-        if getattr(self, "d", None) is not None:
+        if getattr(self, "d", None) is not None and lib is not None:  # lib is None at interpreter shutdown
             lib.mcsparseDestroyDnVec(self.d)
             self.d = None
 
@@ -107,7 +107,7 @@ class DnMat:
         self.d = d
 
     def __del__(self):
-        if getattr(self, "d", None) is not None:
+        if getattr(self, "d", None) is not None and lib is not None:  # lib is None at interpreter shutdown
             lib.mcsparseDestroyDnMat(self.d)
             self.d = None
 

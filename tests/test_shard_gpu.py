@@ -1,0 +1,135 @@
+"""GPU tests of the sharding entry points. The bounds / local-offset kernels need one GPU; the
+fused row push (mcsparseB200SpMVPush over peer-mapped y) and the NCCL ragged all-gather need two
+and are skipped on a single-GPU box."""
+
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import mcsparse_b200 as mc
+from mcsparse_b200 import capi, sharding, workloads
+from mcsparse_b200.capi import lib
+from oracle import oracle
+from tests.util import ADVERSARIAL_LENGTHS, TOL, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("name", ["long_then_short", "empty_start_mid_end", "many_short", "all_empty"])
+def test_shard_bounds_and_local_offsets_bit_exact(handle, device, name, base):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    rp = (np.concatenate([[0], np.cumsum(lengths)]) + base).astype(np.int32)
+    nnz, m = int(rp[-1] - base), len(lengths)
+    d_rp = torch.from_numpy(rp).to(device)
+    for G in (1, 2, 3, 8):
+        out = (C.c_int64 * (G + 1))()
+        capi.check(lib.mcsparseB200ShardRowBounds(handle.h, m, nnz, base, C.c_void_p(d_rp.data_ptr()), G, out))
+        want = oracle.shard_row_bounds(rp, nnz, G, base)
+        assert list(out) == want.tolist()
+        for g in range(G):
+            r0, n = int(want[g]), int(want[g + 1] - want[g])
+            loc = torch.empty(n + 1, dtype=torch.int32, device=device)
+            capi.check(lib.mcsparseB200ShardLocalRowOffsets(handle.h, C.c_void_p(d_rp.data_ptr()), r0, n, base,
+                                                            C.c_void_p(loc.data_ptr())))
+            torch.cuda.synchronize()
+            np.testing.assert_array_equal(loc.cpu().numpy(), oracle.shard_local_row_offsets(rp, r0, n, base))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, name, factor, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = workloads.scaled(name, factor)
+        lengths = workloads.row_lengths(cfg, dev)
+        bounds, nnz = sharding.shard_bounds(lengths, world)
+        r0, r1 = bounds[rank], bounds[rank + 1]
+        w = workloads.generate(cfg, dev, row_range=(r0, r1))
+        h = mc.Handle()
+        A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+        whole = workloads.generate(cfg, "cpu")
+        alpha, beta = 1.5, 0.5
+        ref, d = oracle.spmv(whole.row_ptr, whole.col, whole.val, whole.x, alpha, beta, whole.y0)
+
+        # product path: rows pushed to the peers by the kernel, one tiny collective to order the GPUs
+        job = sharding.ShardedSpmv(h, A, w.x, r0, cfg.rows)
+        for _ in range(2):  # second step: the work buffer and the peer mappings are reused
+            job.y.tensor.fill_(float("nan"))
+            job.y_local.copy_(w.y0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            job.step(alpha, beta)
+            torch.cuda.synchronize()
+            assert_close(job.y.tensor.cpu().numpy(), ref, d, TOL[cfg.dtype], f"push, rank {rank}")
+        dist.barrier()
+
+        # baseline path: local SpMV, then a ragged NCCL all-gather
+        y_full = torch.zeros(cfg.rows, dtype=cfg.dtype, device=dev)
+        y_loc = y_full[r0:r1]
+        y_loc.copy_(w.y0)
+        X, Y = mc.DnVec(w.x), mc.DnVec(y_loc)
+        buf = torch.empty(mc.spmv_buffer_size(h, A, X, Y), dtype=torch.uint8, device=dev)
+        mc.spmv(h, A, X, Y, buf, alpha=alpha, beta=beta)
+        sharding.all_gather_ragged([y_full[bounds[g]:bounds[g + 1]] for g in range(world)], y_loc)
+        torch.cuda.synchronize()
+        assert_close(y_full.cpu().numpy(), ref, d, TOL[cfg.dtype], f"all-gather, rank {rank}")
+        assert torch.equal(y_full, job.y.tensor)  # both assemblies hold the very same bits
+        job.close()
+        out[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,factor", [("C5", 512), ("C3", 256)])
+def test_sharded_spmv_push_and_allgather_two_gpus(name, factor):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    port = _free_port()
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    os.environ.update(env)
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(2, port, name, factor, out), nprocs=2, join=True)
+        assert sorted(out.keys()) == [0, 1]
+
+
+@pytest.mark.parametrize("name,factor", [("C3", 256), ("C5", 512), ("C2", 512)])
+def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor):
+    """One-GPU stand-in for a peer: the push destination is another buffer on the same device. The
+    pushed copy, the local result and plain mcsparseSpMV must agree bit for bit, with the pushed
+    rows landing at rowOffset + row."""
+    from mcsparse_b200 import host
+
+    cfg = workloads.scaled(name, factor)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    y_plain, y_push = w.y0.clone(), w.y0.clone()
+    offset = 5
+    peer = torch.full((w.rows + 2 * offset,), float("nan"), dtype=cfg.dtype, device=device)
+    X, Y1, Y2 = mc.DnVec(w.x), mc.DnVec(y_plain), mc.DnVec(y_push)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y1), dtype=torch.uint8, device=device)
+    mc.spmv(handle, A, X, Y1, buf, alpha=1.5, beta=0.5)
+    pa, pb, keep = host._scalars(handle, 1.5, 0.5, cfg.dtype)
+    arr = (C.c_void_p * 1)(peer.data_ptr())
+    capi.check(lib.mcsparseB200SpMVPush(handle.h, 0, pa, A.d, X.d, pb, Y2.d, host._DTYPE[cfg.dtype], 0,
+                                        host._ptr(buf), 1, arr, offset))
+    torch.cuda.synchronize()
+    assert torch.equal(y_plain, y_push)
+    assert torch.equal(peer[offset:offset + w.rows], y_push)
+    assert torch.isnan(peer[:offset]).all() and torch.isnan(peer[offset + w.rows:]).all()
+    assert lib.mcsparseB200SpMVPush(handle.h, 0, pa, A.d, X.d, pb, Y2.d, host._DTYPE[cfg.dtype], 0, host._ptr(buf),
+                                    8, arr, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
