@@ -31,6 +31,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes (read + write) of one spmv_tile_kernel launch divided by its algorithmic bytes, from the ncu
+# captures summarised under profiles/ (taken at reduced scale and scaled by the units processed).
+TRAFFIC_RATIO = {"C5": 0.985}
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "csr_spmv_spmm_algorithmic_hbm_throughput"
 UNIT = "GB/s"
@@ -393,7 +396,10 @@ def run_gpu(args, rank, world, local_rank):
                        "algorithmic_bytes": job.bytes},
             "gflops": round(job.flops / (ms_per_step * 1e-3) / 1e9, 1),
             "roofline": {"bound": "hbm", "achieved": round(local_gbs, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(local_gbs / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "frac": round(local_gbs / peak, 4),
+                         "traffic": (round(TRAFFIC_RATIO[args.workload] * job.local_bytes)
+                                     if args.workload in TRAFFIC_RATIO and args.scale == 1 else None),
+                         "peak_kind": peak_kind,
                          "frac_of_nominal_8tbs": round(local_gbs / 8000.0, 4),
                          "kernel": "spmv_tile_kernel (+ carry fix-up) per rank", "ms": round(compute_ms, 5)},
             "e2e": {"value": round(job.bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": UNIT,
