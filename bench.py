@@ -340,6 +340,8 @@ def run_gpu(args, rank, world, local_rank):
     if world > 1:
         import torch.distributed as dist
 
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
         barrier = dist.barrier
     peak, peak_kind = hbm_peak()
@@ -353,14 +355,17 @@ def run_gpu(args, rank, world, local_rank):
     _, per_compute = time_steps(torch, job.compute, max(10, args.steps // 4), args.warmup, flush, barrier)
     with ClockSampler(visible_device_index(local_rank)) as clocks:
         total_ms, per = time_steps(torch, job.step, args.steps, args.warmup, flush, barrier)
-    ag_ms = 0.0
-    if world > 1:
-        ag_total, _ = time_steps(torch, job.step_allgather, max(10, args.steps // 4), args.warmup, flush, barrier)
-        ag_ms = ag_total / max(10, args.steps // 4)
-    t = torch.tensor([total_ms, statistics.mean(per_compute), ag_ms], dtype=torch.float64, device=device)
+    ag_ms = push_ms = 0.0
+    if world > 1 and not args.quick:
+        k = max(10, args.steps // 4)
+        ag_total, _ = time_steps(torch, job.step_allgather, k, args.warmup, flush, barrier)
+        push_total, _ = time_steps(torch, lambda: job.sharded.compute(job.cfg.alpha, job.cfg.beta), k, args.warmup,
+                                   flush, barrier)
+        ag_ms, push_ms = ag_total / k, push_total / k
+    t = torch.tensor([total_ms, statistics.mean(per_compute), ag_ms, push_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, compute_ms, ag_ms = t.tolist()
+    total_ms, compute_ms, ag_ms, push_ms = t.tolist()
     ms_per_step = total_ms / args.steps
     value = job.bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -373,7 +378,7 @@ def run_gpu(args, rank, world, local_rank):
         job.step()
         y_host.copy_(job.y, non_blocking=True)
 
-    e2e_steps = max(5, min(args.steps, 50))
+    e2e_steps = 3 if args.quick else max(5, min(args.steps, 50))
     e2e_total, _ = time_steps(torch, e2e_step, e2e_steps, 3, None, barrier)
     t = torch.tensor([e2e_total], dtype=torch.float64, device=device)
     if world > 1:
@@ -407,7 +412,8 @@ def run_gpu(args, rank, world, local_rank):
                     "ms_per_step": round(e2e_ms, 4)},
             "gpu_launches": job.launches_per_step * args.steps,
             "multi_gpu": None if world == 1 else {
-                "kernel_only_ms": round(compute_ms, 5), "fused_push_ms": round(ms_per_step, 5),
+                "kernel_only_ms": round(compute_ms, 5), "push_kernels_ms": round(push_ms, 5),
+                "fused_push_ms": round(ms_per_step, 5),
                 "nccl_allgather_ms": round(ag_ms, 5),
                 "nvlink_lower_bound_ms": round((world - 1) / world * job.cfg.rows * job.vsize / 770e9 * 1e3, 5)},
             "clocks": clocks.summary(),
@@ -445,6 +451,7 @@ def main():
     ap.add_argument("--workload", default="C5", choices=["C1", "C2", "C3", "C5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--scale", type=int, default=1, help="shrink the workload's rows by this factor (profiling)")
+    ap.add_argument("--quick", action="store_true", help="tuning runs: skip the comparison timings")
     ap.add_argument("--headline-only", action="store_true", help="skip the per-configuration block at N=1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

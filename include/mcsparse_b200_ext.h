@@ -66,8 +66,12 @@ mcsparseStatus_t mcsparseB200ShardLocalRowOffsets(mcsparseHandle_t handle, const
  * full x; vecY: this block's slice of the local full-length y), plus the destinations of the
  * push: peerY[p] is the full-length y of another GPU as an address valid on this device
  * (see mcsparseB200PeerOpen), rowOffset the global index of the block's first row. Every
- * finished y value is stored to vecY and to peerY[p][rowOffset + row] for all p, with
- * ordinary stores over NVLink while the kernel runs; no separate all-gather of y is needed.
+ * finished y value ends up in vecY and in peerY[p][rowOffset + row] for all p, moved over
+ * NVLink while the SpMV is still running: either the tile kernel stores each finished row to
+ * all peers itself, or the tiles are computed in a few launches and each chunk's rows are copied
+ * by the copy engines on a second, higher-priority stream while the next chunk computes (chosen
+ * from the number of peers; MCSPARSE_B200_PUSH_CHUNKS=0..8 overrides). No separate all-gather
+ * of y is needed. The first call with a given buffer analyses the matrix and synchronises once.
  * The caller orders the GPUs afterwards (any collective or barrier on the same streams)
  * before x is overwritten or y is read. numPeers <= 7. The reference is single-device
  * (mcsparse/src/common/mcsp_handle.cpp:5-8); this call has no counterpart there.

@@ -277,6 +277,62 @@ St csrmm_entry(mcsparseHandle_t h, mcsparseOperation_t transA, mcsparseOperation
                              scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
 }
 
+// How mcsparseB200SpMVPush moves finished rows to the peers. Measured on B200 / NVSwitch with the
+// 27-point stencil: with one peer, computing the tiles in 4 launches and copying each chunk's rows
+// with the copy engines while the next chunk computes is fastest; with more peers the serial copies
+// lose to the variant whose tile kernel stores every finished row to all peers itself (0 chunks).
+// MCSPARSE_B200_PUSH_CHUNKS overrides the choice (0 ... 8), read on every call.
+int push_chunks_setting(int num_peers) {
+    const char* e = std::getenv("MCSPARSE_B200_PUSH_CHUNKS");
+    const int c = e ? std::atoi(e) : (num_peers <= 1 ? 4 : 0);
+    return c < 0 ? 0 : (c > kMaxPushChunks ? kMaxPushChunks : c);
+}
+
+template <typename T>
+St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X,
+                              mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer,
+                              const PushArgs& push, int chunks) {
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T));
+    void* buf = align_up_256(buffer);
+    const int base = A->mat_descr->base;
+    const int32_t* rows = static_cast<const int32_t*>(A->rows);
+    if (h->side_stream == nullptr) {
+        // Highest priority: as CTAs of the running tile kernel retire, the block scheduler places the
+        // waiting copy CTAs first, so the copy really runs beside the next chunk instead of after it.
+        int least = 0, greatest = 0;
+        cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        if (cudaStreamCreateWithPriority(&h->side_stream, cudaStreamNonBlocking, greatest) != cudaSuccess)
+            return INTERNAL;
+        for (auto& ev : h->events)
+            if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL;
+    }
+    {
+        std::lock_guard<std::mutex> g(A->lock);
+        if (!(A->push_buffer == buffer && A->push_rows_ptr == A->rows && A->push_chunks == chunks)) {
+            // First use with this buffer: analyse, then read back where each chunk of tiles starts.
+            cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
+            if (e != cudaSuccess) return from_cuda(e);
+            for (int c = 0; c <= chunks; ++c) A->push_chunk_tiles[c] = ws.num_tiles * c / chunks;
+            e = spmv_read_tile_rows(h->stream, buf, chunks + 1, A->push_chunk_tiles, A->push_chunk_rows);
+            if (e != cudaSuccess) return from_cuda(e);
+            A->push_buffer = buffer;
+            A->push_rows_ptr = A->rows;
+            A->push_chunks = chunks;
+            A->analysed_buffer = buffer;
+            A->analysed_rows = A->rows;
+            A->analysed_items_per_tile = ws.items_per_tile;
+        }
+    }
+    PeerList<T> peers;
+    peers.count = push.count;
+    peers.row_offset = push.row_offset;
+    for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
+    return from_cuda(spmv_tiled_pipelined<T>(
+        h->stream, h->side_stream, h->events, chunks, A->push_chunk_tiles, A->push_chunk_rows, A->row_num, A->nnz, base,
+        rows, static_cast<const int32_t*>(A->cols), static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
+        static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, buf, peers));
+}
+
 }  // namespace
 
 extern "C" {
@@ -296,6 +352,12 @@ mcsparseStatus_t mcsparseCreate(mcsparseHandle_t* handle) {
 }
 
 mcsparseStatus_t mcsparseDestroy(mcsparseHandle_t handle) {
+    if (handle != nullptr && handle->side_stream != nullptr) {
+        DeviceGuard guard(handle->device);
+        cudaStreamDestroy(handle->side_stream);
+        for (auto& ev : handle->events)
+            if (ev != nullptr) cudaEventDestroy(ev);
+    }
     delete handle;
     return MCSPARSE_STATUS_SUCCESS;
 }
@@ -539,6 +601,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
                                         void* csrValues) {
     if (d == nullptr) return pub(BAD_POINTER);
     std::lock_guard<std::mutex> g(d->lock);
+    d->push_buffer = nullptr;
     d->rows = csrRowOffsets;
     d->cols = csrColInd;
     d->vals = csrValues;
@@ -906,7 +969,19 @@ mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation
     push.count = numPeers;
     push.y = peerY;
     push.row_offset = rowOffset;
-    return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
+    const int chunks = push_chunks_setting(numPeers);
+    if (chunks == 0 || numPeers == 0)
+        return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
+    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, true, externalBuffer, false, nullptr);
+    if (st != OK) return pub(st);
+    if (matA->rows == nullptr || matA->cols == nullptr || matA->vals == nullptr || vecX->values == nullptr ||
+        vecY->values == nullptr || matA->mat_descr == nullptr)
+        return pub(BAD_POINTER);
+    if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
+    DeviceGuard guard(handle->device);
+    if (computeType == MACA_R_64F)
+        return pub(spmv_push_pipelined<double>(handle, matA, vecX, vecY, alpha, beta, externalBuffer, push, chunks));
+    return pub(spmv_push_pipelined<float>(handle, matA, vecX, vecY, alpha, beta, externalBuffer, push, chunks));
 }
 
 mcsparseStatus_t mcsparseB200PeerAlloc(void** devPtr, size_t bytes) {

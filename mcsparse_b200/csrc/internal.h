@@ -12,11 +12,17 @@
 // Descriptor payloads. Field meaning follows the reference's structs
 // (mcsparse/src/include/mcsp_internal_types.h:86-92,127-145,184-223 and
 // mcsparse/src/include/mcsp_handle.h:11-27) minus everything the CSR path never reads.
+constexpr int kMaxPushChunks = 8;
+
 struct mcsparseContext {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
     mcsparsePointerMode_t ptr_mode = MCSPARSE_POINTER_MODE_HOST;
+    // Created on the first pipelined mcsparseB200SpMVPush: a stream for the row copies that run
+    // beside the kernels, and the events that order the two streams.
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t events[kMaxPushChunks + 1] = {};
 };
 
 struct mcsparseMatDescr {
@@ -43,6 +49,12 @@ struct mcsparseSpMatDescr {
     void* analysed_buffer = nullptr;
     const void* analysed_rows = nullptr;
     int analysed_items_per_tile = 0;
+    // Chunk boundaries of the pipelined push (tiles and the rows they start at), read back once.
+    void* push_buffer = nullptr;
+    const void* push_rows_ptr = nullptr;
+    int push_chunks = 0;
+    int64_t push_chunk_tiles[kMaxPushChunks + 1] = {};
+    int64_t push_chunk_rows[kMaxPushChunks + 1] = {};
 };
 
 struct mcsparseDnVecDescr {
@@ -99,6 +111,16 @@ template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
                        const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers = PeerList<T>());
+// Rows at which the given tiles start, copied to the host (synchronises the stream).
+cudaError_t spmv_read_tile_rows(cudaStream_t s, const void* buf, int count, const int64_t* tiles, int64_t* rows);
+// The tiles in `chunks` launches; after each, a copy kernel on `side` pushes the rows that ended in
+// it to the peers while the next chunk computes; the carry fix-up (with its own pushes) comes last.
+template <typename T>
+cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t* events, int chunks,
+                                 const int64_t* chunk_tiles, const int64_t* chunk_rows, int64_t m, int64_t nnz,
+                                 int base, const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
+                                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
+                                 const PeerList<T>& peers);
 template <typename T>
 cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                           const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,

@@ -8,6 +8,7 @@
 // The path is HBM-bound: each nonzero moves sizeof(T) + 4 bytes once, so the kernels are
 // organised around wide, coalesced, streaming loads of col/val with many bytes in flight
 // per SM, while x is gathered through L1/L2 with default caching.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(THREADS)
     spmv_tile_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
-                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers) {
+                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
     constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ int s_failed;
 
     const int tid = threadIdx.x;
-    const int t = blockIdx.x;
+    const int t = blockIdx.x + tile_offset;  // a launch may cover a sub-range of the tiles
     const int2 s0 = tile_starts[t];
     const int2 s1 = tile_starts[t + 1];
     const int row_s = s0.x, nz_s = s0.y;
@@ -385,6 +386,43 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
+// Copies local rows [r0, r1) of y to the same global rows of every peer's y with 128-bit stores
+// aligned on the destination (NVLink carries large aligned writes near its peak; scattered 8-byte
+// stores reach about half of it). Runs on a side stream while later tiles are still computing.
+__device__ __forceinline__ void store_vec16(float* dst, const float* v) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_vec16(double* dst, const double* v) {
+    *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) push_rows_kernel(PeerList<T> peers, const T* __restrict__ y, long long r0,
+                                                        long long r1) {
+    constexpr int VW = 16 / (int)sizeof(T);
+    const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+#pragma unroll
+    for (int p = 0; p < PeerList<T>::kMax; ++p) {
+        if (p >= peers.count) break;
+        T* const dst = peers.y[p] + peers.row_offset;
+        const long long mis = (long long)((reinterpret_cast<uintptr_t>(dst + r0) / sizeof(T)) & (VW - 1));
+        long long v0 = r0 + ((VW - mis) & (VW - 1));  // first row whose destination is 16-byte aligned
+        if (v0 > r1) v0 = r1;
+        const long long nvec = (r1 - v0) / VW;
+        for (long long c = tid; c < nvec; c += nthreads) {
+            const long long i = v0 + c * VW;
+            T v[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) v[e] = y[i + e];
+            store_vec16(dst + i, v);
+        }
+        const long long tail0 = v0 + nvec * VW;  // fewer than VW rows before v0 and after tail0
+        if (tid < VW && r0 + tid < v0) dst[r0 + tid] = y[r0 + tid];
+        if (tid >= 32 && tid < 32 + VW && tail0 + (tid - 32) < r1) dst[tail0 + (tid - 32)] = y[tail0 + (tid - 32)];
+    }
+}
+
 // Adds the carries of rows that cross tile boundaries. The first tile of each run of equal
 // carry rows sums the run in tile order, so the result does not depend on scheduling.
 template <typename T, bool PUSH>
@@ -401,6 +439,25 @@ __global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* _
     const T v = mad(alpha_arg.get(), sum, y[r]);
     y[r] = v;
     if (PUSH) push_to_peers(peers, r, v);
+}
+
+// The same correction for the tiles [t0, t1) only, looking backwards: tile t finishes its first
+// row if at least one row ends in it, and then adds the carries that earlier tiles left for that
+// row, summed in tile order exactly as above (so both kernels produce the same bits). It needs
+// nothing from later tiles, so it can run right after a sub-range of the tiles has been computed.
+template <typename T>
+__global__ void spmv_carry_fixup_range_kernel(long long t0, long long t1, const int2* __restrict__ tile_starts,
+                                              const int* __restrict__ carry_row, const T* __restrict__ carry_val,
+                                              T* __restrict__ y, ScalarArg<T> alpha_arg) {
+    const long long t = t0 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t >= t1 || t == 0) return;
+    const int r = tile_starts[t].x;
+    if (tile_starts[t + 1].x <= r) return;  // no row ends in this tile
+    long long u = t - 1;                    // carry_row[t - 1] == r by construction
+    while (u > 0 && carry_row[u - 1] == r) --u;
+    T sum = carry_val[u];
+    for (++u; u < t; ++u) sum += carry_val[u];
+    y[r] = mad(alpha_arg.get(), sum, y[r]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -486,7 +543,8 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const i
     const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
     if (peers.count > 0) {
         spmv_tile_kernel<T, kThreads, IPT, true><<<grid, kThreads, tuning_pad_smem(), s>>>(
-            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers);
+            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
+            0);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
@@ -494,12 +552,92 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const i
         return cudaGetLastError();
     }
     spmv_tile_kernel<T, kThreads, IPT, false><<<grid, kThreads, tuning_pad_smem(), s>>>(
-        (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers);
+        (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers, 0);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
                                                                peers);
     return cudaGetLastError();
+}
+
+// CTAs (of 512 threads) of one row-copy kernel: MCSPARSE_B200_PUSH_CTAS, default 64. Enough to keep
+// NVLink busy, few enough to leave most SM slots to the tile kernel running beside it.
+static long long push_copy_ctas() {
+    const char* e = std::getenv("MCSPARSE_B200_PUSH_CTAS");
+    const long long v = e ? std::atoll(e) : 64;
+    return v < 1 ? 1 : (v > 1184 ? 1184 : v);
+}
+
+// MCSPARSE_B200_PUSH_ENGINE=sm selects the copy kernel; the default is the copy engines.
+static bool push_with_copy_engines() {
+    const char* e = std::getenv("MCSPARSE_B200_PUSH_ENGINE");
+    return !(e && e[0] == 's');
+}
+
+cudaError_t spmv_read_tile_rows(cudaStream_t s, const void* buf, int count, const int64_t* tiles, int64_t* rows) {
+    const int2* starts = static_cast<const int2*>(buf);
+    int2 v;
+    for (int c = 0; c < count; ++c) {
+        cudaError_t e = cudaMemcpyAsync(&v, starts + tiles[c], sizeof v, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) return e;
+        rows[c] = v.x;
+    }
+    return cudaSuccess;
+}
+
+template <typename T>
+cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t* events, int chunks,
+                                 const int64_t* chunk_tiles, const int64_t* chunk_rows, int64_t m, int64_t nnz,
+                                 int base, const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
+                                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
+                                 const PeerList<T>& peers) {
+    if (ws.num_tiles == 0) return cudaSuccess;
+    char* base_ptr = static_cast<char*>(buf);
+    const int2* starts = reinterpret_cast<const int2*>(base_ptr);
+    int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
+    T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
+    int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
+    constexpr int IPT = TileCfg<T>::kItemsPerThread;
+    const PeerList<T> none;
+    cudaError_t e = cudaSuccess;
+    for (int c = 0; c < chunks && e == cudaSuccess; ++c) {
+        const int64_t t0 = chunk_tiles[c], t1 = chunk_tiles[c + 1];
+        if (t1 > t0) {
+            spmv_tile_kernel<T, kThreads, IPT, false><<<(unsigned)(t1 - t0), kThreads, tuning_pad_smem(), s>>>(
+                (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, none,
+                (int)t0);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(events[c], s);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(side, events[c], 0);
+        if (e == cudaSuccess && t1 > t0) {
+            // On the side stream, so that the tile kernels run back to back on the main one: rows that
+            // end in this chunk get their carries, and the copy below then sends final values.
+            spmv_carry_fixup_range_kernel<T><<<(unsigned)((t1 - t0 + 255) / 256), 256, 0, side>>>(
+                t0, t1, starts, carry_row, carry_val, y, alpha);
+            e = cudaGetLastError();
+        }
+        const int64_t r0 = chunk_rows[c], r1 = chunk_rows[c + 1];
+        if (e == cudaSuccess && r1 > r0) {
+            if (push_with_copy_engines()) {
+                // one peer-to-peer copy per destination: the copy engines drive NVLink at its full
+                // rate and take no SM away from the tile kernel running beside them
+                for (int p = 0; p < peers.count && e == cudaSuccess; ++p)
+                    e = cudaMemcpyAsync(peers.y[p] + peers.row_offset + r0, y + r0, size_t(r1 - r0) * sizeof(T),
+                                        cudaMemcpyDeviceToDevice, side);
+            } else {
+                const long long vecs = (r1 - r0) * (long long)sizeof(T) / 16 + 1;
+                const unsigned grid = (unsigned)std::min<long long>((vecs + 511) / 512, push_copy_ctas());
+                push_rows_kernel<T><<<grid, 512, 0, side>>>(peers, y, r0, r1);
+                e = cudaGetLastError();
+            }
+        }
+    }
+    // Whatever the caller enqueues next on its stream comes after the last row copy.
+    if (e == cudaSuccess) e = cudaEventRecord(events[chunks], side);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, events[chunks], 0);
+    return e;
 }
 
 template <typename T, int G>
@@ -560,7 +698,11 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
                                        const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>,                     \
                                        const SpmvWorkspace&, void*, const PeerList<T>&);                       \
     template cudaError_t spmv_rowgroup<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, \
-                                          const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>);
+                                          const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>);                 \
+    template cudaError_t spmv_tiled_pipelined<T>(cudaStream_t, cudaStream_t, cudaEvent_t*, int, const int64_t*, \
+                                                 const int64_t*, int64_t, int64_t, int, const int32_t*,        \
+                                                 const int32_t*, const T*, const T*, T*, ScalarArg<T>,         \
+                                                 ScalarArg<T>, const SpmvWorkspace&, void*, const PeerList<T>&);
 INSTANTIATE(float)
 INSTANTIATE(double)
 #undef INSTANTIATE

@@ -48,8 +48,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, name, factor, out):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+def _worker(rank, world, port, name, factor, chunks, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), MCSPARSE_B200_PUSH_CHUNKS=str(chunks))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -94,8 +94,9 @@ def _worker(rank, world, port, name, factor, out):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("chunks", [0, 4])  # 0: rows stored to the peers by the tile kernel; 4: pipelined row copies
 @pytest.mark.parametrize("name,factor", [("C5", 512), ("C3", 256)])
-def test_sharded_spmv_push_and_allgather_two_gpus(name, factor):
+def test_sharded_spmv_push_and_allgather_two_gpus(name, factor, chunks):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     port = _free_port()
@@ -103,17 +104,19 @@ def test_sharded_spmv_push_and_allgather_two_gpus(name, factor):
     os.environ.update(env)
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(2, port, name, factor, out), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, port, name, factor, chunks, out), nprocs=2, join=True)
         assert sorted(out.keys()) == [0, 1]
 
 
+@pytest.mark.parametrize("chunks", [0, 1, 4, 8])
 @pytest.mark.parametrize("name,factor", [("C3", 256), ("C5", 512), ("C2", 512)])
-def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor):
+def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor, chunks, monkeypatch):
     """One-GPU stand-in for a peer: the push destination is another buffer on the same device. The
     pushed copy, the local result and plain mcsparseSpMV must agree bit for bit, with the pushed
     rows landing at rowOffset + row."""
     from mcsparse_b200 import host
 
+    monkeypatch.setenv("MCSPARSE_B200_PUSH_CHUNKS", str(chunks))
     cfg = workloads.scaled(name, factor)
     w = workloads.generate(cfg, device)
     A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
