@@ -121,6 +121,41 @@ __device__ __forceinline__ void push_to_peers(const PeerList<T>& peers, long lon
         if (p < peers.count) peers.y[p][peers.row_offset + row] = v;
 }
 
+__device__ __forceinline__ void store_vec16(float* dst, const float* v) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_vec16(double* dst, const double* v) {
+    *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
+}
+
+// Stores the n finished values vals[0..n) (shared memory) of local rows row0.. to every peer, with
+// 128-bit stores aligned on the destination address: one warp instruction then moves 512
+// contiguous bytes, and NVLink carries a few large writes much better than many 8-byte ones.
+template <typename T, int THREADS>
+__device__ __forceinline__ void push_tile_rows(const PeerList<T>& peers, const T* vals, long long row0, int n,
+                                               int tid) {
+    constexpr int VW = 16 / (int)sizeof(T);
+#pragma unroll
+    for (int p = 0; p < PeerList<T>::kMax; ++p) {
+        if (p < peers.count) {
+            T* const dst = peers.y[p] + peers.row_offset + row0;
+            const int mis = (int)((reinterpret_cast<uintptr_t>(dst) / sizeof(T)) & (VW - 1));
+            const int head = min(n, (VW - mis) & (VW - 1));
+            const int nvec = (n - head) / VW;
+            for (int c = tid; c < nvec; c += THREADS) {
+                T v[VW];
+#pragma unroll
+                for (int e = 0; e < VW; ++e) v[e] = vals[head + c * VW + e];
+                store_vec16(dst + head + c * VW, v);
+            }
+            const int tail0 = head + nvec * VW;
+            const int u = THREADS - 1 - tid;  // the scalar edges go to the last threads, idle above
+            if (u < head) dst[u] = vals[u];
+            if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
@@ -166,6 +201,8 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_warp_maxlen[NWARPS];
     __shared__ int s_failed;
+    constexpr int PUSHCAP = PUSH ? 512 : 1;  // finished rows of a short-row tile staged for the push
+    __shared__ T s_push[PUSHCAP];
 
     const int tid = threadIdx.x;
     const int t = blockIdx.x + tile_offset;  // a launch may cover a sub-range of the tiles
@@ -176,8 +213,6 @@ __global__ void __launch_bounds__(THREADS)
     const int nz_e = s1.y;
     const int nnz_tile = nz_e - nz_s;
     const int tile_items = nrows + nnz_tile;
-    // The tile's first row started in an earlier tile: its sum here is partial until the fix-up.
-    const bool continued = PUSH && row_s < m && nz_s > __ldg(row_ptr + row_s) - base;
 
     // Element nz_s + k of col is staged at s_col[head_c + k]; head_c is chosen so that the element
     // at index 0 of s_col sits on a 16-byte boundary in global memory. Likewise for val.
@@ -293,12 +328,21 @@ __global__ void __launch_bounds__(THREADS)
                     T v = alpha * sum;
                     if (beta != T(0)) v = mad(beta, y[row_s + i], v);
                     y[row_s + i] = v;
-                    if (PUSH && !(i == 0 && continued)) push_to_peers(peers, row_s + i, v);
+                    if (PUSH) {
+                        if (nrows <= PUSHCAP)
+                            s_push[i] = v;
+                        else
+                            push_to_peers(peers, row_s + i, v);
+                    }
                 } else {
                     carry_row[t] = row_s + nrows;
                     carry_val[t] = sum;
                 }
             }
+        }
+        if (PUSH && nrows <= PUSHCAP) {
+            __syncthreads();
+            push_tile_rows<T, THREADS>(peers, s_push, row_s, nrows, tid);
         }
         return;
     }
@@ -378,7 +422,17 @@ __global__ void __launch_bounds__(THREADS)
         T v = alpha * s_y[i];
         if (beta != T(0)) v = mad(beta, y[row_s + i], v);
         y[row_s + i] = v;
-        if (PUSH && !(i == 0 && continued)) push_to_peers(peers, row_s + i, v);
+        if (PUSH) s_y[i] = v;  // only this thread touches s_y[i] here
+    }
+    if (PUSH) {
+        const T open_sum = s_y[nrows];
+        __syncthreads();
+        push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        if (tid == 0) {
+            carry_row[t] = row_s + nrows;
+            carry_val[t] = open_sum;
+        }
+        return;
     }
     if (tid == 0) {
         carry_row[t] = row_s + nrows;
@@ -389,13 +443,6 @@ __global__ void __launch_bounds__(THREADS)
 // Copies local rows [r0, r1) of y to the same global rows of every peer's y with 128-bit stores
 // aligned on the destination (NVLink carries large aligned writes near its peak; scattered 8-byte
 // stores reach about half of it). Runs on a side stream while later tiles are still computing.
-__device__ __forceinline__ void store_vec16(float* dst, const float* v) {
-    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void store_vec16(double* dst, const double* v) {
-    *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(512) push_rows_kernel(PeerList<T> peers, const T* __restrict__ y, long long r0,
                                                         long long r1) {
