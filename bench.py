@@ -180,14 +180,14 @@ class SpmvJob:
 
 
 class SpmmJob:
-    def __init__(self, name, n, device, handle):
+    def __init__(self, name, n, device, handle, scale=1):
         import torch
 
         import mcsparse_b200 as mc
         from mcsparse_b200 import workloads
 
         self.torch, self.mc, self.h = torch, mc, handle
-        cfg = workloads.CONFIGS[name]
+        cfg = workloads.CONFIGS[name] if scale == 1 else workloads.scaled(name, scale)
         self.cfg, self.n, self.world = cfg, n, 1
         w = workloads.generate(cfg, device)
         self.w = w
@@ -195,7 +195,9 @@ class SpmmJob:
         self.C = torch.zeros(w.rows, n, dtype=cfg.dtype, device=device)
         self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
         self.Bm, self.Cm = mc.DnMat(w.B[n], w.cols, n, n), mc.DnMat(self.C, w.rows, n, n)
-        self.buf = torch.empty(256, dtype=torch.uint8, device=device)
+        self.buf = torch.empty(mc.spmm_buffer_size(handle, self.A, self.Bm, self.Cm), dtype=torch.uint8, device=device)
+        mc.spmm_preprocess(handle, self.A, self.Bm, self.Cm, self.buf)
+        self.panel_buffer_bytes = self.buf.numel()
         self.bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, 4, cfg.beta, dense_cols=n)
         self.gather_model_bytes = w.nnz * (8 + 4 * n) + (w.rows + 1) * 4 + w.rows * n * 4
         self.flops = 2 * w.nnz * n
@@ -347,6 +349,15 @@ def run_gpu(args, rank, world, local_rank):
     peak, peak_kind = hbm_peak()
     h = mc.Handle()
     flush_buf = torch.zeros(4 * L2_BYTES // 4, dtype=torch.float32, device=device)
+    if args.workload == "C4":  # SpMM: single GPU ("replicas only"), one compact line
+        if rank == 0:
+            j = SpmmJob("C4", args.dense_cols, device, h, args.scale)
+            r = measure_job(torch, j, args.steps, args.warmup, peak, flush_buf)
+            r.update({"metric": METRIC, "value": r["gbs"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": workload_label("C4"), "dense_cols": args.dense_cols}})
+            print(json.dumps(r), flush=True)
+        return
 
     job = SpmvJob(args.workload, device, rank, world, h, args.scale)
     flush = flush_buf if job.local_bytes < 4 * L2_BYTES else None
@@ -448,7 +459,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="C5", choices=["C1", "C2", "C3", "C5"])
+    ap.add_argument("--workload", default="C5", choices=["C1", "C2", "C3", "C4", "C5"])
+    ap.add_argument("--dense-cols", type=int, default=64, help="columns of B for the SpMM workload C4 (64 or 128)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--scale", type=int, default=1, help="shrink the workload's rows by this factor (profiling)")
     ap.add_argument("--quick", action="store_true", help="tuning runs: skip the comparison timings")

@@ -19,6 +19,8 @@ from .host import (  # noqa: F401
     DnVec,
     Handle,
     spmm,
+    spmm_buffer_size,
+    spmm_preprocess,
     spmv,
     spmv_buffer_size,
     spmv_preprocess,
@@ -26,5 +28,5 @@ from .host import (  # noqa: F401
 
 __all__ = [
     "capi", "lib", "load_library", "check", "McsparseError", "Handle", "CsrMatrix", "DnVec", "DnMat",
-    "spmv", "spmv_buffer_size", "spmv_preprocess", "spmm",
+    "spmv", "spmv_buffer_size", "spmv_preprocess", "spmm", "spmm_buffer_size", "spmm_preprocess",
 ]

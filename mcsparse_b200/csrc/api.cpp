@@ -245,9 +245,21 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
     return OK;
 }
 
+// True when B (as op(B)) and C are both addressed row-major with unit column stride: the layout the
+// vectorised and column-panel kernels handle.
+bool spmm_row_major(mcsparseOperation_t opB, const mcsparseDnMatDescr* B, const mcsparseDnMatDescr* C) {
+    const bool b_row = (B->order == MCSPARSE_ORDER_ROW) != (opB == MCSPARSE_OPERATION_TRANSPOSE);
+    return b_row && C->order == MCSPARSE_ORDER_ROW;
+}
+
+SpmmPlan spmm_plan_for(mcsparseOperation_t opB, const mcsparseSpMatDescr* A, const mcsparseDnMatDescr* B,
+                       const mcsparseDnMatDescr* C, macaDataType computeType) {
+    return spmm_plan(A->row_num, A->col_num, C->col_num, A->nnz, value_size(computeType), spmm_row_major(opB, B, C));
+}
+
 template <typename T>
 St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, mcsparseDnMatDescr* B,
-            mcsparseDnMatDescr* C, const void* alpha, const void* beta) {
+            mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr) {
     int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
     if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
     const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
@@ -255,7 +267,7 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
                              static_cast<const int32_t*>(A->rows), static_cast<const int32_t*>(A->cols),
                              static_cast<const T*>(A->vals), static_cast<const T*>(B->values), b_rs, b_cs,
                              static_cast<T*>(C->values), c_rs, c_cs, scalar_arg<T>(h, alpha),
-                             scalar_arg<T>(h, beta)));
+                             scalar_arg<T>(h, beta), num_panels, panel_ptr));
 }
 
 // Legacy csrmm / csrmm2: column-major B and C (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:19-80).
@@ -602,6 +614,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     if (d == nullptr) return pub(BAD_POINTER);
     std::lock_guard<std::mutex> g(d->lock);
     d->push_buffer = nullptr;
+    d->spmm_buffer = nullptr;
     d->rows = csrRowOffsets;
     d->cols = csrColInd;
     d->vals = csrValues;
@@ -828,7 +841,9 @@ mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     St st = spmm_check(handle, opA, opB, alpha, matA, matB, beta, matC, computeType, false, nullptr);
     if (st != OK) return pub(st);
     if (bufferSize == nullptr) return pub(BAD_POINTER);
-    *bufferSize = 128;  // MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15)
+    // 128 is MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15); a B too large
+    // for L2 adds the per-row panel offsets that mcsparseSpMM_preprocess computes.
+    *bufferSize = spmm_plan_for(opB, matA, matB, matC, computeType).bytes;
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -837,10 +852,26 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
                                          const void* beta, mcsparseDnMatDescr_t matC, macaDataType computeType,
                                          mcsparseSpMMAlg_t alg, void* externalBuffer) {
     // The reference returns success without looking at any argument
-    // (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:965-970); so does this build, which
-    // needs no per-matrix state for SpMM.
-    (void)handle; (void)opA; (void)opB; (void)alpha; (void)matA; (void)matB; (void)beta; (void)matC;
-    (void)computeType; (void)alg; (void)externalBuffer;
+    // (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:965-970). Here the call is optional too and never
+    // fails: when the arguments describe a row-major product whose B does not fit in L2, it computes the
+    // column-panel offsets into externalBuffer and records them on matA; otherwise it does nothing.
+    (void)alg;
+    if (spmm_check(handle, opA, opB, alpha, matA, matB, beta, matC, computeType, true, externalBuffer) != OK)
+        return MCSPARSE_STATUS_SUCCESS;
+    if (matA->rows == nullptr || matA->cols == nullptr || matA->mat_descr == nullptr) return MCSPARSE_STATUS_SUCCESS;
+    const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
+    std::lock_guard<std::mutex> g(matA->lock);
+    matA->spmm_buffer = nullptr;
+    if (plan.num_panels <= 1) return MCSPARSE_STATUS_SUCCESS;
+    DeviceGuard guard(handle->device);
+    if (spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base, static_cast<const int32_t*>(matA->rows),
+                        static_cast<const int32_t*>(matA->cols), plan, align_up_256(externalBuffer)) != cudaSuccess)
+        return MCSPARSE_STATUS_SUCCESS;
+    matA->spmm_buffer = externalBuffer;
+    matA->spmm_rows = matA->rows;
+    matA->spmm_cols = matA->cols;
+    matA->spmm_panels = plan.num_panels;
+    matA->spmm_n = matC->col_num;
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -856,8 +887,20 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
         return pub(BAD_POINTER);
     if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
-    if (computeType == MACA_R_64F) return pub(spmm_run<double>(handle, opB, matA, matB, matC, alpha, beta));
-    return pub(spmm_run<float>(handle, opB, matA, matB, matC, alpha, beta));
+    int panels = 1;
+    const int* panel_ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> g(matA->lock);
+        const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
+        if (matA->spmm_buffer == externalBuffer && matA->spmm_rows == matA->rows && matA->spmm_cols == matA->cols &&
+            matA->spmm_n == matC->col_num && matA->spmm_panels == plan.num_panels && plan.num_panels > 1) {
+            panels = plan.num_panels;
+            panel_ptr = static_cast<const int*>(align_up_256(externalBuffer));
+        }
+    }
+    if (computeType == MACA_R_64F)
+        return pub(spmm_run<double>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+    return pub(spmm_run<float>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
 }
 
 // ----------------------------------------------------------------------------- legacy entry points

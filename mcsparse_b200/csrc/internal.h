@@ -55,6 +55,12 @@ struct mcsparseSpMatDescr {
     int push_chunks = 0;
     int64_t push_chunk_tiles[kMaxPushChunks + 1] = {};
     int64_t push_chunk_rows[kMaxPushChunks + 1] = {};
+    // Column panels recorded by mcsparseSpMM_preprocess: buffer, arrays and shape they were built for.
+    void* spmm_buffer = nullptr;
+    const void* spmm_rows = nullptr;
+    const void* spmm_cols = nullptr;
+    int spmm_panels = 0;
+    int64_t spmm_n = 0;
 };
 
 struct mcsparseDnVecDescr {
@@ -129,11 +135,23 @@ cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
 // Fixed device work area behind mcsparseB200SpMVNoAlloc (address on the current device).
 cudaError_t spmv_static_scratch(void** ptr, size_t* bytes);
 
+// Column-panel plan of an SpMM whose B does not fit in L2 (num_panels == 1: no panels). The work
+// buffer then holds int32 panel_ptr[(num_panels + 1) * m]: where each panel starts inside each row.
+struct SpmmPlan {
+    int num_panels = 1;
+    int panel_cols = 0;
+    size_t bytes = 128;
+};
+SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_size, bool row_major_operands);
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
+                            const SpmmPlan& plan, void* buf);
+
 // Dense operand addressed as element(r, c) = ptr[r * row_stride + c * col_stride].
 template <typename T>
 cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
                  const T* val, const T* B, int64_t b_row_stride, int64_t b_col_stride, T* C, int64_t c_row_stride,
-                 int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta);
+                 int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels = 1,
+                 const int* panel_ptr = nullptr);
 
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host);

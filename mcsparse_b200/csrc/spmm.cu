@@ -6,6 +6,9 @@
 // row-major B is first transposed into a temporary allocation. Here a row of A is read once
 // and every nonzero is applied to a whole row of B with 128-bit loads; row-major B and C are
 // used in place. No temporary memory, no stream synchronisation.
+#include <algorithm>
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace mcsp_b200 {
@@ -69,11 +72,19 @@ __device__ __forceinline__ double2 zero_vec<double2>() {
 // and W FMAs. The loop over the G nonzeros is unrolled so several B rows are in flight.
 // B rows are fetched with default caching: B is the operand with reuse (through L2).
 // ---------------------------------------------------------------------------------------
-template <typename T, int G>
+//
+// PANEL variant: B is too large for L2, so the product is done in column panels of A whose slice of
+// B fits; the launch for panel p covers, in each row, only the nonzeros between panel_lo[row] and
+// panel_hi[row] (found once by spmm_panel_ptr_kernel; columns sorted within a row) and adds into
+// C. Successive rows hit the same L2-resident slice of B instead of all of B, which trades the
+// random re-reads of B from HBM for streaming re-reads of C. Rows with nothing in a later panel
+// are skipped entirely.
+template <typename T, int G, bool PANEL>
 __global__ void __launch_bounds__(kThreads)
     spmm_rowmajor_kernel(int m, int n, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
                          const T* __restrict__ val, const T* __restrict__ B, long long ldb, T* __restrict__ C,
-                         long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
+                         long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg,
+                         const int* __restrict__ panel_lo, const int* __restrict__ panel_hi, int first_panel) {
     using V = typename VecOf<T>::type;
     constexpr int W = VecOf<T>::W;
     const int lane = threadIdx.x & (G - 1);
@@ -84,8 +95,13 @@ __global__ void __launch_bounds__(kThreads)
     // Shuffles below use the full-warp mask with width G: all 32 lanes always execute them.
     int j0 = 0, j1 = 0;
     if (row_ok) {
-        j0 = __ldg(row_ptr + row) - base;
-        j1 = __ldg(row_ptr + row + 1) - base;
+        if (PANEL) {
+            j0 = __ldg(panel_lo + row);
+            j1 = __ldg(panel_hi + row);
+        } else {
+            j0 = __ldg(row_ptr + row) - base;
+            j1 = __ldg(row_ptr + row + 1) - base;
+        }
     }
     V acc = zero_vec<V>();
     const T* const Bc = B + c0 - (long long)base * ldb;
@@ -113,8 +129,41 @@ __global__ void __launch_bounds__(kThreads)
     if (row_ok && col_ok) {
         const T alpha = alpha_arg.get(), beta = beta_arg.get();
         V* out = reinterpret_cast<V*>(C + row * ldc + c0);
-        *out = (beta != T(0)) ? axpby(alpha, acc, beta, *out) : scale(alpha, acc);
+        if (!PANEL || first_panel) {
+            *out = (beta != T(0)) ? axpby(alpha, acc, beta, *out) : scale(alpha, acc);
+        } else if (j1 > j0) {  // later panels add to what the earlier ones left; C streams through L2
+            __stcs(out, axpby(alpha, acc, T(1), __ldcs(out)));
+        }
     }
+}
+
+// One thread per row: where each column panel starts inside the row (lower bound of the panel's first
+// column among the row's sorted columns). A row whose columns are not sorted is given to panel 0 whole.
+__global__ void spmm_panel_ptr_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+                                      int num_panels, int panel_cols, int* __restrict__ panel_ptr) {
+    const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (r >= m) return;
+    const int j0 = row_ptr[r] - base, j1 = row_ptr[r + 1] - base;
+    bool sorted = true;
+    for (int j = j0 + 1; j < j1; ++j) sorted &= col[j - 1] <= col[j];
+    panel_ptr[r] = j0;
+    for (int p = 1; p < num_panels; ++p) {
+        int lo = j0, hi = j1;
+        if (sorted) {
+            const long long first_col = (long long)p * panel_cols + base;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (col[mid] < first_col)
+                    lo = mid + 1;
+                else
+                    hi = mid;
+            }
+        } else {
+            lo = j1;
+        }
+        panel_ptr[(long long)p * m + r] = lo;
+    }
+    panel_ptr[(long long)num_panels * m + r] = j1;
 }
 
 // Any layout, any n: one thread per C element, addressed through (row, col) strides.
@@ -148,33 +197,77 @@ __global__ void __launch_bounds__(kThreads)
 template <typename T, int G>
 cudaError_t launch_rowmajor(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr,
                             const int32_t* col, const T* val, const T* B, int64_t ldb, T* C, int64_t ldc,
-                            ScalarArg<T> alpha, ScalarArg<T> beta) {
+                            ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
     constexpr int W = VecOf<T>::W;
     const long long threads_total = m * G;
     dim3 grid((unsigned)((threads_total + kThreads - 1) / kThreads), (unsigned)((n + G * W - 1) / (G * W)));
-    spmm_rowmajor_kernel<T, G><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C, ldc,
-                                                         alpha, beta);
-    return cudaGetLastError();
+    if (num_panels <= 1 || panel_ptr == nullptr) {
+        spmm_rowmajor_kernel<T, G, false><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C,
+                                                                    ldc, alpha, beta, nullptr, nullptr, 1);
+        return cudaGetLastError();
+    }
+    for (int p = 0; p < num_panels; ++p) {
+        spmm_rowmajor_kernel<T, G, true><<<grid, kThreads, 0, s>>>(
+            (int)m, (int)n, base, row_ptr, col, val, B, ldb, C, ldc, alpha, beta, panel_ptr + (size_t)p * m,
+            panel_ptr + (size_t)(p + 1) * m, p == 0);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace
 
+// L2 budget for one panel of B in MiB: MCSPARSE_B200_SPMM_PANEL_MB. Panels are off unless it is set:
+// on the 1M x 1M, 32 nonzeros per row benchmark they cut DRAM traffic from 6.9 GB to 3.4 GB (n = 64,
+// four panels) but each pass is latency-bound on its short row pieces and the total was slower
+// (1.74 ms against 1.46 ms), so the single-pass kernel stays the default.
+static long long spmm_panel_budget_bytes() {
+    const char* e = std::getenv("MCSPARSE_B200_SPMM_PANEL_MB");
+    const long long mb = e ? std::atoll(e) : 0;
+    return mb <= 0 ? 0 : mb << 20;
+}
+
+SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_size, bool row_major_operands) {
+    SpmmPlan plan;
+    const long long budget = spmm_panel_budget_bytes();
+    const long long b_bytes = (long long)k * n * (long long)value_size;
+    if (!row_major_operands || budget == 0 || m == 0 || n == 0 || b_bytes <= 2 * budget) return plan;
+    const long long panel_cols = std::max<long long>(1, budget / (n * (long long)value_size));
+    const long long panels = (k + panel_cols - 1) / panel_cols;
+    // Each extra panel re-reads and re-writes C once; worth it only while a row still brings a few
+    // nonzeros to every panel (the re-reads of B it saves are proportional to nnz).
+    if (panels < 2 || panels > 16 || nnz < 4 * (panels - 1) * m) return plan;
+    plan.num_panels = (int)panels;
+    plan.panel_cols = (int)panel_cols;
+    plan.bytes = 256 + size_t(panels + 1) * size_t(m) * 4;
+    return plan;
+}
+
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
+                            const SpmmPlan& plan, void* buf) {
+    if (plan.num_panels <= 1) return cudaSuccess;
+    spmm_panel_ptr_kernel<<<(unsigned)((m + 127) / 128), 128, 0, s>>>((int)m, base, row_ptr, col, plan.num_panels,
+                                                                    plan.panel_cols, static_cast<int*>(buf));
+    return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
                  const T* val, const T* B, int64_t b_rs, int64_t b_cs, T* C, int64_t c_rs, int64_t c_cs,
-                 ScalarArg<T> alpha, ScalarArg<T> beta) {
+                 ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
     if (m == 0 || n == 0) return cudaSuccess;
     constexpr int W = VecOf<T>::W;
     const bool vec_ok = b_cs == 1 && c_cs == 1 && n % W == 0 && b_rs % W == 0 && c_rs % W == 0 &&
                         ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
     if (vec_ok) {
         const int64_t lanes = n / W;
-        if (lanes <= 2) return launch_rowmajor<T, 2>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
-        if (lanes <= 4) return launch_rowmajor<T, 4>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
-        if (lanes <= 8) return launch_rowmajor<T, 8>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 2) return launch_rowmajor<T, 2>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 4) return launch_rowmajor<T, 4>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 8) return launch_rowmajor<T, 8>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
         if (lanes <= 16)
-            return launch_rowmajor<T, 16>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
-        return launch_rowmajor<T, 32>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+            return launch_rowmajor<T, 16>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        return launch_rowmajor<T, 32>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
     }
     const long long total = m * n;
     spmm_strided_kernel<T><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, s>>>(
@@ -184,9 +277,9 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* 
 
 template cudaError_t spmm<float>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, const float*,
                                  const float*, int64_t, int64_t, float*, int64_t, int64_t, ScalarArg<float>,
-                                 ScalarArg<float>);
+                                 ScalarArg<float>, int, const int*);
 template cudaError_t spmm<double>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
                                   const double*, const double*, int64_t, int64_t, double*, int64_t, int64_t,
-                                  ScalarArg<double>, ScalarArg<double>);
+                                  ScalarArg<double>, ScalarArg<double>, int, const int*);
 
 }  // namespace mcsp_b200

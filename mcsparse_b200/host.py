@@ -146,6 +146,24 @@ def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0):
     del keep
 
 
+def spmm_buffer_size(handle, A, B, Cmat, alpha=1.0, beta=0.0, op_b=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    size = C.c_size_t()
+    check(lib.mcsparseSpMM_bufferSize(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, op_b, pa, A.d, B.d, pb, Cmat.d,
+                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMM_ALG_DEFAULT, C.byref(size)),
+          "mcsparseSpMM_bufferSize")
+    del keep
+    return size.value
+
+
+def spmm_preprocess(handle, A, B, Cmat, buffer, alpha=1.0, beta=0.0, op_b=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
+    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+    check(lib.mcsparseSpMM_preprocess(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, op_b, pa, A.d, B.d, pb, Cmat.d,
+                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMM_ALG_DEFAULT, _ptr(buffer)),
+          "mcsparseSpMM_preprocess")
+    del keep
+
+
 def spmm(handle, A, B, Cmat, buffer, alpha=1.0, beta=0.0, op_b=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
     """C = alpha * A @ op(B) + beta * C through mcsparseSpMM."""
     pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)

@@ -174,3 +174,42 @@ def test_legacy_csrmm2(handle, device, dtype, trans_b):
         torch.cuda.synchronize()
         assert_close(t[4].cpu().numpy().reshape(n, ldc)[:, :m].T, ref, d, TOL[np.dtype(dtype)], "csrmm")
     lib.mcsparseDestroyMatDescr(descr)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+@pytest.mark.parametrize("shuffle_rows", [False, True])
+def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, monkeypatch):
+    """With a small L2 budget the preprocess call splits the product into column panels; the result must
+    not change. Rows whose columns are not sorted are handled whole by the first panel."""
+    monkeypatch.setenv("MCSPARSE_B200_SPMM_PANEL_MB", "1")
+    rng = np.random.default_rng(3)
+    m, k, n = 3000, 10000, 64
+    lengths = rng.integers(12, 40, size=m).tolist()
+    lengths[5], lengths[17] = 0, 1
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=14)
+    if shuffle_rows:
+        for r in range(0, m, 7):
+            seg = slice(rp[r], rp[r + 1])
+            perm = rng.permutation(rp[r + 1] - rp[r])
+            col[seg], val[seg] = col[seg][perm], val[seg][perm]
+    B = rng.uniform(-1, 1, (k, n)).astype(dtype)
+    C0 = rng.uniform(-1, 1, (m, n)).astype(dtype)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B.ravel(), C0.ravel().copy())]
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2])
+    Bm, Cm = mc.DnMat(t[3], k, n, n), mc.DnMat(t[4], m, n, n)
+    size = mc.spmm_buffer_size(handle, A, Bm, Cm)
+    panels = -(-k // ((1 << 20) // (n * np.dtype(dtype).itemsize)))
+    assert size == 256 + (panels + 1) * m * 4
+    buf = torch.empty(size, dtype=torch.uint8, device=device)
+    mc.spmm_preprocess(handle, A, Bm, Cm, buf)
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=1.25, beta=beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, B, n, ROW, n, 1.25, beta, C0, n, ROW)
+    assert_close(t[4].cpu().numpy().reshape(m, n), ref, d, TOL[np.dtype(dtype)], "column panels")
+    # the same call without a preprocess (another buffer) takes the single-pass kernel: same result within tolerance
+    t[4].copy_(torch.from_numpy(C0.ravel()))
+    other = torch.empty(size, dtype=torch.uint8, device=device)
+    mc.spmm(handle, A, Bm, Cm, other, alpha=1.25, beta=beta)
+    torch.cuda.synchronize()
+    assert_close(t[4].cpu().numpy().reshape(m, n), ref, d, TOL[np.dtype(dtype)], "single pass")
