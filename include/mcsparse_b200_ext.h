@@ -41,6 +41,15 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
                                                const int32_t** tileStarts);
 
 /*
+ * Device-side status of the SpMV calls that used externalBuffer since its last analysis: 0, or 1
+ * if a thread block gave up its bounded wait (about a second of SM clocks) for the bulk copies
+ * of its tile and left its rows unwritten. Synchronises the handle's stream. The reference has
+ * no device-side waits and no such query.
+ */
+mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMatDescr_t matA,
+                                           void* externalBuffer, int* status);
+
+/*
  * Row-block sharding of one CSR matrix over numShards GPUs, balanced by nonzeros:
  * bounds[g] = first row r with rowOffsets[r] - base >= floor(g * nnz / numShards),
  * bounds[0] = 0, bounds[numShards] = rows. rowOffsets is device memory; bounds is host

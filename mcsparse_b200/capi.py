@@ -116,6 +116,7 @@ PROTOTYPES = {
     "mcsparseB200PeerExport": (_i, [_vp, _vp]),
     "mcsparseB200PeerOpen": (_i, [_vp, _pvp]),
     "mcsparseB200PeerClose": (_i, [_vp]),
+    "mcsparseB200SpMVGetStatus": (_i, [_vp, _vp, _vp, _pi]),
     "mcsparseB200SpMVPartitionView": (_i, [_vp, _vp, _pi, _pi64, _pvp]),
     "mcsparseB200ShardRowBounds": (_i, [_vp, _i64, _i64, _i, _vp, _i, _pi64]),
     "mcsparseB200ShardLocalRowOffsets": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),

@@ -784,6 +784,19 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
     return MCSPARSE_STATUS_SUCCESS;
 }
 
+mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMatDescr_t matA,
+                                           void* externalBuffer, int* status) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (matA == nullptr || externalBuffer == nullptr || status == nullptr) return pub(BAD_POINTER);
+    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    DeviceGuard guard(handle->device);
+    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType));
+    const char* word = static_cast<const char*>(align_up_256(externalBuffer)) + ws.off_status;
+    cudaError_t e = cudaMemcpyAsync(status, word, sizeof(int), cudaMemcpyDeviceToHost, handle->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(handle->stream);
+    return pub(from_cuda(e));
+}
+
 // SpMV for callers that may not allocate device memory: same arithmetic and kernels as
 // mcsparseSpMV, with the work area taken from the fixed array inside the library instead of an
 // external buffer. Nothing here (or below it) allocates. The analysis is redone on every call

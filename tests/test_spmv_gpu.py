@@ -118,6 +118,9 @@ def test_spmv_scaled_configs(handle, device, name, factor):
     torch.cuda.synchronize()
     ref, d = oracle.spmv(w.row_ptr, w.col, w.val, w.x, w.alpha, w.beta, w.y0)
     assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], name)
+    status = C.c_int(-1)
+    capi.check(lib.mcsparseB200SpMVGetStatus(handle.h, A.d, C.c_void_p(buf.data_ptr()), C.byref(status)))
+    assert status.value == 0  # no thread block timed out waiting for its bulk copies
 
 
 def test_spmv_is_reproducible(handle, device):
