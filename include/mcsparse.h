@@ -6,7 +6,8 @@
  * changes. Each group cites the reference declaration it replaces (path inside the
  * mcSparse source tree : line).
  *
- * Supported compute path: MCSPARSE_FORMAT_CSR, MCSPARSE_OPERATION_NON_TRANSPOSE,
+ * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO as an input of
+ * mcsparseSpMV), MCSPARSE_OPERATION_NON_TRANSPOSE,
  * MACA_R_32F / MACA_R_64F, MCSPARSE_INDEX_32I offsets and columns, index base 0 or 1.
  * Everything else that the reference accepts on these entry points returns
  * MCSPARSE_STATUS_NOT_SUPPORTED here.
@@ -224,6 +225,20 @@ mcsparseStatus_t mcsparseSpMatGetAttribute(mcsparseSpMatDescr_t spMatDescr, mcsp
                                            void* data, size_t dataSize);
 mcsparseStatus_t mcsparseSpMatSetAttribute(mcsparseSpMatDescr_t spMatDescr, mcsparseSpMatAttribute_t attribute,
                                            const void* data, size_t dataSize);
+
+/* ---- COO (structure of arrays) sparse matrix descriptor, accepted by mcsparseSpMV as an input format.
+ *      Reference: mcsp_helper.h.in:52-58, mcsp_helper.cpp:433-438,526-560,597-605. Entries must be
+ *      sorted by row (any order inside a row); mcsparseSpMV derives CSR row offsets from cooRowInd
+ *      into the external buffer (the reference's coo2csr step,
+ *      mcsparse/src/kernels/conversion/coo2csr_device.hpp:8-24) and runs the CSR kernels. ---- */
+mcsparseStatus_t mcsparseCreateCoo(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                   void* cooRowInd, void* cooColInd, void* cooValues, mcsparseIndexType_t cooIdxType,
+                                   mcsparseIndexBase_t idxBase, macaDataType valueType);
+mcsparseStatus_t mcsparseCooGet(mcsparseSpMatDescr_t spMatDescr, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                void** cooRowInd, void** cooColInd, void** cooValues, mcsparseIndexType_t* idxType,
+                                mcsparseIndexBase_t* idxBase, macaDataType* valueType);
+mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t spMatDescr, void* cooRows, void* cooColumns,
+                                        void* cooValues);
 
 /* ---- Dense matrix descriptor. Reference: mcsp_helper.h.in:92-98, mcsp_helper.cpp:715-795. ---- */
 mcsparseStatus_t mcsparseCreateDnMat(mcsparseDnMatDescr_t* dnMatDescr, int64_t rows, int64_t cols, int64_t ld,

@@ -28,6 +28,7 @@ MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE = 2
 MCSPARSE_INDEX_BASE_ZERO, MCSPARSE_INDEX_BASE_ONE = 0, 1
 MCSPARSE_POINTER_MODE_HOST, MCSPARSE_POINTER_MODE_DEVICE = 0, 1
 MCSPARSE_FORMAT_CSR = 1
+MCSPARSE_FORMAT_COO = 3
 MCSPARSE_ORDER_COL, MCSPARSE_ORDER_ROW = 1, 2
 MCSPARSE_INDEX_16U, MCSPARSE_INDEX_32I, MCSPARSE_INDEX_64I = 1, 2, 3
 MCSPARSE_MATRIX_TYPE_GENERAL, MCSPARSE_MATRIX_TYPE_SYMMETRIC = 0, 1
@@ -82,6 +83,9 @@ PROTOTYPES = {
     "mcsparseCreateCsr": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i, _i]),
     "mcsparseCsrGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pvp, _pvp, _pi, _pi, _pi, _pi]),
     "mcsparseCsrSetPointers": (_i, [_vp, _vp, _vp, _vp]),
+    "mcsparseCreateCoo": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i]),
+    "mcsparseCooGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pvp, _pvp, _pi, _pi, _pi]),
+    "mcsparseCooSetPointers": (_i, [_vp, _vp, _vp, _vp]),
     "mcsparseDestroySpMat": (_i, [_vp]),
     "mcsparseSpMatGetSize": (_i, [_vp, _pi64, _pi64, _pi64]),
     "mcsparseSpMatGetFormat": (_i, [_vp, _pi]),

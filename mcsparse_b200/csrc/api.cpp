@@ -110,7 +110,8 @@ struct DeviceGuard {
 // (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:690-720 and :309-336).
 St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
-              bool need_buffer, const void* buffer, bool need_size_out, const void* size_out) {
+              bool need_buffer, const void* buffer, bool need_size_out, const void* size_out,
+              bool allow_coo = false) {
     if (h == nullptr) return BAD_HANDLE;
     if (alpha == nullptr || beta == nullptr || A == nullptr || X == nullptr || Y == nullptr) return BAD_POINTER;
     if (need_size_out && size_out == nullptr) return BAD_POINTER;
@@ -119,7 +120,7 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         too_big(A->row_num + A->nnz))
         return NOT_IMPL;
     if (need_buffer && buffer == nullptr) return BAD_POINTER;
-    if (A->format != MCSPARSE_FORMAT_CSR) return NOT_IMPL;
+    if (!(A->format == MCSPARSE_FORMAT_CSR || (allow_coo && A->format == MCSPARSE_FORMAT_COO))) return NOT_IMPL;
     const bool n_op = opA == MCSPARSE_OPERATION_NON_TRANSPOSE;
     if (!((n_op && X->size == A->col_num && Y->size == A->row_num) ||
           (!n_op && X->size == A->row_num && Y->size == A->col_num)))
@@ -145,6 +146,15 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mc
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
+    if (A->format == MCSPARSE_FORMAT_COO) {
+        // Row offsets derived from the sorted row indices live behind the SpMV work area.
+        int32_t* offsets = reinterpret_cast<int32_t*>(static_cast<char*>(buf) + ws.bytes);
+        if (analyse) {
+            cudaError_t e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, rows, offsets);
+            if (e != cudaSuccess) return from_cuda(e);
+        }
+        rows = offsets;
+    }
     if (analyse) {
         cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
         if (e != cudaSuccess) return from_cuda(e);
@@ -164,7 +174,7 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mc
 St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
               void* buffer, bool preprocess_only, const PushArgs& push = PushArgs()) {
-    St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr);
+    St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr, push.count == 0);
     if (st != OK) return st;
     // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
     if (A->rows == nullptr || A->cols == nullptr || A->vals == nullptr || X->values == nullptr ||
@@ -623,6 +633,38 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     return MCSPARSE_STATUS_SUCCESS;
 }
 
+mcsparseStatus_t mcsparseCreateCoo(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                   void* cooRowInd, void* cooColInd, void* cooValues, mcsparseIndexType_t cooIdxType,
+                                   mcsparseIndexBase_t idxBase, macaDataType valueType) {
+    mcsparseStatus_t st = mcsparseCreateCsr(spMatDescr, rows, cols, nnz, cooRowInd, cooColInd, cooValues, cooIdxType,
+                                            cooIdxType, idxBase, valueType);
+    if (st == MCSPARSE_STATUS_SUCCESS) (*spMatDescr)->format = MCSPARSE_FORMAT_COO;
+    return st;
+}
+
+mcsparseStatus_t mcsparseCooGet(mcsparseSpMatDescr_t d, int64_t* rows, int64_t* cols, int64_t* nnz, void** cooRowInd,
+                                void** cooColInd, void** cooValues, mcsparseIndexType_t* idxType,
+                                mcsparseIndexBase_t* idxBase, macaDataType* valueType) {
+    if (d == nullptr || rows == nullptr || cols == nullptr || nnz == nullptr || cooRowInd == nullptr ||
+        cooColInd == nullptr || cooValues == nullptr || idxType == nullptr || idxBase == nullptr ||
+        valueType == nullptr)
+        return pub(BAD_POINTER);
+    *rows = d->row_num;
+    *cols = d->col_num;
+    *nnz = d->nnz;
+    *cooRowInd = d->rows;
+    *cooColInd = d->cols;
+    *cooValues = d->vals;
+    *idxType = d->rowIdxType;
+    *idxBase = d->idxBase;
+    *valueType = d->valueType;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t d, void* cooRows, void* cooColumns, void* cooValues) {
+    return mcsparseCsrSetPointers(d, cooRows, cooColumns, cooValues);
+}
+
 mcsparseStatus_t mcsparseDestroySpMat(mcsparseSpMatDescr_t d) {
     if (d == nullptr) return MCSPARSE_STATUS_SUCCESS;
     delete d->mat_descr;
@@ -748,10 +790,12 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
                                          mcsparseDnVecDescr_t vecY, macaDataType computeType,
                                          mcsparseSpMVAlg_t alg, size_t* bufferSize) {
     (void)alg;
-    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize);
+    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize, true);
     if (st != OK) return pub(st);
-    // Work partition + carries, plus slack to align the caller's pointer to 256 bytes.
+    // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
+    // also needs room for the row offsets derived from its row indices.
     *bufferSize = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType)).bytes + 256;
+    if (matA->format == MCSPARSE_FORMAT_COO) *bufferSize += ((size_t(matA->row_num) + 1) * 4 + 255) & ~size_t(255);
     return MCSPARSE_STATUS_SUCCESS;
 }
 

@@ -36,7 +36,7 @@ struct mcsparseMatDescr {
 struct mcsparseSpMatDescr {
     mcsparseFormat_t format = MCSPARSE_FORMAT_CSR;
     int64_t row_num = 0, col_num = 0, nnz = 0;
-    void* rows = nullptr;  // row offsets (device)
+    void* rows = nullptr;  // CSR: row offsets; COO: row index of every entry (device)
     void* cols = nullptr;  // column indices (device)
     void* vals = nullptr;  // values (device)
     mcsparseIndexType_t rowIdxType = MCSPARSE_INDEX_32I, colIdxType = MCSPARSE_INDEX_32I;
@@ -153,6 +153,8 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* 
                  int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels = 1,
                  const int* panel_ptr = nullptr);
 
+cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
+                            int32_t* offsets);
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host);
 cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,

@@ -40,7 +40,31 @@ __global__ void shard_local_row_offsets_kernel(const int* __restrict__ row_ptr, 
     local[i] = __ldg(row_ptr + first_row + i) - __ldg(row_ptr + first_row) + base;
 }
 
+// CSR row offsets of a COO matrix sorted by row: offsets[r] = base + number of entries whose row is
+// smaller than r, found by a lower bound over the sorted row indices (one thread per offset).
+// Same result as the reference's scatter formulation (mcsparse/src/kernels/conversion/coo2csr_device.hpp:8-24).
+__global__ void coo_row_offsets_kernel(long long m, long long nnz, int base, const int* __restrict__ coo_rows,
+                                       int* __restrict__ offsets) {
+    const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (r > m) return;
+    long long lo = 0, hi = nnz;
+    while (lo < hi) {
+        const long long mid = (lo + hi) >> 1;
+        if ((long long)__ldg(coo_rows + mid) - base < r)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    offsets[r] = (int)lo + base;
+}
+
 }  // namespace
+
+cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
+                            int32_t* offsets) {
+    coo_row_offsets_kernel<<<(unsigned)((m + 1 + 255) / 256), 256, 0, s>>>(m, nnz, base, coo_rows, offsets);
+    return cudaGetLastError();
+}
 
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host) {

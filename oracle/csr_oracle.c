@@ -157,6 +157,15 @@ void oracle_shard_local_row_offsets(const int32_t* row_ptr, int64_t first_row, i
     for (int64_t i = 0; i <= num_rows; ++i) local[i] = row_ptr[first_row + i] - row_ptr[first_row] + base;
 }
 
+/* CSR row offsets of a COO matrix sorted by row, by counting (the reference's coo2csr step,
+ * mcsparse/src/kernels/conversion/coo2csr_device.hpp:8-24, states the same mapping as a scatter). */
+void oracle_coo_row_offsets(int64_t m, int64_t nnz, int base, const int32_t* coo_rows, int32_t* offsets) {
+    for (int64_t r = 0; r <= m; ++r) offsets[r] = 0;
+    for (int64_t j = 0; j < nnz; ++j) offsets[(int64_t)coo_rows[j] - base + 1] += 1;
+    offsets[0] = base;
+    for (int64_t r = 0; r < m; ++r) offsets[r + 1] += offsets[r];
+}
+
 /* Host-side structural check of a CSR matrix: 0 when valid, else the number of the first
  * rule broken (1 first offset, 2 monotone offsets, 3 last offset, 4 column range). */
 int oracle_csr_validate(int64_t m, int64_t cols, int64_t nnz, int base, const int32_t* row_ptr,

@@ -112,6 +112,13 @@ def shard_local_row_offsets(row_ptr, first_row, num_rows, base=0):
     return out
 
 
+def coo_row_offsets(coo_rows, num_rows, base=0):
+    coo_rows = _np(coo_rows, np.int32)
+    out = np.empty(num_rows + 1, np.int32)
+    lib().oracle_coo_row_offsets(C.c_int64(num_rows), C.c_int64(coo_rows.size), C.c_int(base), _p(coo_rows), _p(out))
+    return out
+
+
 def csr_validate(rows, cols, row_ptr, col, base=0):
     row_ptr, col = _np(row_ptr, np.int32), _np(col, np.int32)
     return lib().oracle_csr_validate(C.c_int64(rows), C.c_int64(cols), C.c_int64(col.size), C.c_int(base),

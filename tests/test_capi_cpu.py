@@ -138,3 +138,22 @@ def test_mat_descr():
 def test_partition_view_needs_arguments():
     ipt, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
     assert lib.mcsparseB200SpMVPartitionView(None, FAKE, C.byref(ipt), C.byref(nt), C.byref(p)) == 3
+
+
+def test_coo_descriptor_roundtrip():
+    d = C.c_void_p()
+    assert lib.mcsparseCreateCoo(C.byref(d), 3, 4, 5, FAKE, C.c_void_p(0x2000), C.c_void_p(0x3000),
+                                 capi.MCSPARSE_INDEX_32I, 1, capi.MACA_R_32F) == 0
+    fmt = C.c_int()
+    assert lib.mcsparseSpMatGetFormat(d, C.byref(fmt)) == 0 and fmt.value == capi.MCSPARSE_FORMAT_COO
+    rows, cols, nnz = C.c_int64(), C.c_int64(), C.c_int64()
+    p0, p1, p2, it, b, vt = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_int(), C.c_int(), C.c_int()
+    assert lib.mcsparseCooGet(d, C.byref(rows), C.byref(cols), C.byref(nnz), C.byref(p0), C.byref(p1), C.byref(p2),
+                              C.byref(it), C.byref(b), C.byref(vt)) == 0
+    assert (rows.value, cols.value, nnz.value, p0.value, p1.value, p2.value, it.value, b.value, vt.value) == \
+        (3, 4, 5, 0x1000, 0x2000, 0x3000, 2, 1, 0)
+    assert lib.mcsparseCooSetPointers(d, C.c_void_p(0x10), C.c_void_p(0x20), C.c_void_p(0x30)) == 0
+    assert lib.mcsparseCooGet(d, C.byref(rows), C.byref(cols), C.byref(nnz), C.byref(p0), C.byref(p1), C.byref(p2),
+                              C.byref(it), C.byref(b), None) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert lib.mcsparseCreateCoo(C.byref(d), 3, 4, -5, FAKE, FAKE, FAKE, 2, 0, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    assert lib.mcsparseDestroySpMat(d) == 0

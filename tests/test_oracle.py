@@ -174,3 +174,12 @@ def test_csr_validate():
     assert oracle.csr_validate(3, 5, bad, col) == 2
     badc = col.copy(); badc[0] = 5
     assert oracle.csr_validate(3, 5, rp, badc) == 4
+
+
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
+def test_coo_row_offsets(name, base):
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    rp = (np.concatenate([[0], np.cumsum(lengths)]) + base).astype(np.int32)
+    coo_rows = (np.repeat(np.arange(lengths.size), lengths) + base).astype(np.int32)
+    np.testing.assert_array_equal(oracle.coo_row_offsets(coo_rows, lengths.size, base), rp)

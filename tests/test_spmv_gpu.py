@@ -241,3 +241,49 @@ def test_legacy_csrmv_and_csrmvex(handle, device, dtype, name):
     torch.cuda.synchronize()
     assert_close(y.cpu().numpy()[:m], ref, d, TOL[np.dtype(dtype)], "CsrmvEx")
     lib.mcsparseDestroyMatDescr(descr)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle"])
+def test_spmv_coo_input(handle, device, name, dtype, base):
+    """A row-sorted COO matrix goes through mcsparseSpMV: row offsets are derived on the device (bit-exact
+    against the CPU count) and the CSR kernels run on them."""
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    ncols = max(int(lengths.max()), 1) + 11
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=31, base=base)
+    coo_rows = (np.repeat(np.arange(lengths.size), lengths) + base).astype(np.int32)
+    rng = np.random.default_rng(6)
+    x, y0 = rng.uniform(-1, 1, ncols).astype(dtype), rng.uniform(-1, 1, lengths.size).astype(dtype)
+    pad = lambda a: np.concatenate([a, np.zeros(1, a.dtype)])
+    t = {k: torch.from_numpy(pad(v)).to(device) for k, v in dict(r=coo_rows, c=col, v=val, x=x, y=y0).items()}
+    m, nnz = lengths.size, col.size
+    d = C.c_void_p()
+    P = lambda k: C.c_void_p(t[k].data_ptr())
+    capi.check(lib.mcsparseCreateCoo(C.byref(d), m, ncols, nnz, P("r"), P("c"), P("v"), capi.MCSPARSE_INDEX_32I, base,
+                                     MACA[dtype]))
+    X, Y = mc.DnVec(t["x"][:ncols]), mc.DnVec(t["y"][:m])
+    ct = C.c_float if dtype == np.float32 else C.c_double
+    a, b = ct(-1.5), ct(0.25)
+    pa, pb = C.cast(C.pointer(a), C.c_void_p), C.cast(C.pointer(b), C.c_void_p)
+    sz = C.c_size_t()
+    capi.check(lib.mcsparseSpMV_bufferSize(handle.h, 0, pa, d, X.d, pb, Y.d, MACA[dtype], 0, C.byref(sz)))
+    buf = torch.empty(sz.value, dtype=torch.uint8, device=device)
+    capi.check(lib.mcsparseSpMV(handle.h, 0, pa, d, X.d, pb, Y.d, MACA[dtype], 0, C.c_void_p(buf.data_ptr())))
+    torch.cuda.synchronize()
+    ref, dd = oracle.spmv(rp, col, val, x, -1.5, 0.25, y0, base=base)
+    assert_close(t["y"].cpu().numpy()[:m], ref, dd, TOL[np.dtype(dtype)], "COO input")
+    # the derived row offsets sit behind the SpMV work area
+    items, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
+    capi.check(lib.mcsparseB200SpMVPartitionView(d, C.c_void_p(buf.data_ptr()), C.byref(items), C.byref(nt), C.byref(p)))
+    csr_sz = C.c_size_t()
+    A_csr = mc.CsrMatrix(m, ncols, torch.from_numpy(rp).to(device), t["c"][:max(nnz, 0)] if nnz else t["c"][:0],
+                         t["v"][:nnz] if nnz else t["v"][:0], base=base)
+    capi.check(lib.mcsparseSpMV_bufferSize(handle.h, 0, pa, A_csr.d, X.d, pb, Y.d, MACA[dtype], 0, C.byref(csr_sz)))
+    off = (p.value - buf.data_ptr()) + (csr_sz.value - 256)
+    got = buf[off:off + (m + 1) * 4].view(torch.int32).cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.coo_row_offsets(coo_rows, m, base))
+    # the entry points without a COO path refuse it
+    assert lib.mcsparseB200SpMVNoAlloc(handle.h, 0, pa, d, X.d, pb, Y.d, MACA[dtype], 0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    lib.mcsparseDestroySpMat(d)
