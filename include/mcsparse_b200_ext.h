@@ -11,9 +11,15 @@
 extern "C" {
 #endif
 
-/* Merge items (rows + nonzeros) one thread block of the tiled SpMV kernel consumes. */
+/* Merge items (rows + nonzeros) one thread block of the tiled SpMV kernel consumes. Two sizes exist
+ * per value type: the large one for matrices whose neighbouring nonzeros have neighbouring columns
+ * (stencils, banded matrices: x is reused through L1 and per-tile overhead matters), half of it for
+ * matrices with scattered columns (gather-latency bound: shorter tiles measured 20-40 % faster). The
+ * choice is made once per matrix from a 4096-sample probe of the column indices. */
 #define MCSPARSE_B200_SPMV_TILE_ITEMS_F32 4096
 #define MCSPARSE_B200_SPMV_TILE_ITEMS_F64 2048
+#define MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 2048
+#define MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 1024
 
 /*
  * mcsparseSpMV_preprocess: same argument list as mcsparseSpMV. Runs the merge-path
@@ -125,7 +131,7 @@ mcsparseStatus_t mcsparseB200PeerClose(void* mappedPtr);
  *     other's partition: run them one after the other.
  * Arguments and status codes are those of mcsparseSpMV without the buffer.
  */
-#define MCSPARSE_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
+#define MCSPARSE_B200_NOALLOC_SCRATCH_BYTES (16u << 20)
 mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
                                          mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
                                          mcsparseDnVecDescr_t vecY, macaDataType computeType,

@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libmcsparse.so")
+# MCSPARSE_B200_LIB points the binding at another build of the library (tuning experiments).
+LIB_PATH = os.environ.get("MCSPARSE_B200_LIB") or os.path.join(_HERE, "lib", "libmcsparse.so")
 
 # status codes
 MCSPARSE_STATUS_SUCCESS = 0
@@ -19,7 +20,7 @@ MCSPARSE_STATUS_EXECUTION_FAILED = 6
 MCSPARSE_STATUS_INTERNAL_ERROR = 7
 MCSPARSE_STATUS_NOT_SUPPORTED = 10
 MCSPARSE_STATUS_INSUFFICIENT_RESOURCES = 11
-NOALLOC_SCRATCH_BYTES = 8 << 20
+NOALLOC_SCRATCH_BYTES = 16 << 20
 # operations
 MCSPARSE_OPERATION_NON_TRANSPOSE = 0
 MCSPARSE_OPERATION_TRANSPOSE = 1
@@ -41,7 +42,7 @@ MCSPARSE_ALG_MERGE_PATH = 0
 MACA_R_32F, MACA_R_64F, MACA_R_16F, MACA_C_32F, MACA_R_32I = 0, 1, 2, 4, 10
 MAJOR_VERSION, MINOR_VERSION, PATCH_LEVEL = 0, 1, 2
 
-SPMV_TILE_ITEMS = {MACA_R_32F: 4096, MACA_R_64F: 2048}
+SPMV_TILE_ITEMS = {MACA_R_32F: (4096, 2048), MACA_R_64F: (2048, 1024)}  # (large, small) tile per value type
 
 _vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 _pvp = C.POINTER(C.c_void_p)

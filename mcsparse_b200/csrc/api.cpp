@@ -132,6 +132,39 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     return OK;
 }
 
+// Tile size for this matrix: small tiles when neighbouring nonzeros rarely have neighbouring columns
+// (fewer than a quarter of 4096 sampled pairs within 8 columns). Probed once per column array
+// (one small kernel and a 4-byte copy, which synchronises the stream) and remembered on the
+// descriptor; MCSPARSE_B200_SPMV_TILE=small|large overrides. `scratch` is device memory the
+// probe may overwrite (the start of the work buffer, before the analysis writes it).
+bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, void* scratch) {
+    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
+        if (e[0] == 's') return true;
+        if (e[0] == 'l') return false;
+    }
+    std::lock_guard<std::mutex> g(A->lock);
+    if (A->probed_cols == A->cols && A->probed_nnz == A->nnz) return A->small_tiles;
+    int near = 4096;
+    if (A->nnz >= 2 &&
+        spmv_locality_probe(h->stream, A->nnz, static_cast<const int32_t*>(A->cols), static_cast<int*>(scratch),
+                            &near) != cudaSuccess)
+        near = 4096;
+    A->small_tiles = near < 1024;
+    A->probed_cols = A->cols;
+    A->probed_nnz = A->nnz;
+    return A->small_tiles;
+}
+
+// The choice already made for this matrix, without probing (large tiles if none was made).
+bool known_small_tiles(mcsparseSpMatDescr* A) {
+    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
+        if (e[0] == 's') return true;
+        if (e[0] == 'l') return false;
+    }
+    std::lock_guard<std::mutex> g(A->lock);
+    return A->probed_cols == A->cols && A->probed_nnz == A->nnz && A->small_tiles;
+}
+
 struct PushArgs {
     int count = 0;
     void* const* y = nullptr;
@@ -140,9 +173,9 @@ struct PushArgs {
 
 template <typename T>
 St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
-            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute,
+            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, bool small_tiles,
             const PushArgs& push = PushArgs()) {
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T));
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), small_tiles);
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
@@ -182,7 +215,8 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
-    const int ipt = computeType == MACA_R_64F ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    const bool small = choose_small_tiles(h, A, align_up_256(buffer));
+    const int ipt = spmv_workspace(A->row_num, A->nnz, value_size(computeType), small).items_per_tile;
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
@@ -196,8 +230,8 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         }
     }
     if (computeType == MACA_R_64F)
-        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, push);
-    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, push);
+        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
 }
 
 // Legacy csrmv family: raw arrays plus a matrix descriptor
@@ -314,8 +348,8 @@ template <typename T>
 St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X,
                               mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer,
                               const PushArgs& push, int chunks) {
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T));
     void* buf = align_up_256(buffer);
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_small_tiles(h, A, buf));
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
     if (h->side_stream == nullptr) {
@@ -330,7 +364,8 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
     }
     {
         std::lock_guard<std::mutex> g(A->lock);
-        if (!(A->push_buffer == buffer && A->push_rows_ptr == A->rows && A->push_chunks == chunks)) {
+        if (!(A->push_buffer == buffer && A->push_rows_ptr == A->rows && A->push_chunks == chunks &&
+              A->analysed_items_per_tile == ws.items_per_tile)) {
             // First use with this buffer: analyse, then read back where each chunk of tiles starts.
             cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
             if (e != cudaSuccess) return from_cuda(e);
@@ -625,6 +660,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     std::lock_guard<std::mutex> g(d->lock);
     d->push_buffer = nullptr;
     d->spmm_buffer = nullptr;
+    d->probed_cols = nullptr;
     d->rows = csrRowOffsets;
     d->cols = csrColInd;
     d->vals = csrValues;
@@ -821,7 +857,8 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
         tileStarts == nullptr)
         return pub(BAD_POINTER);
     if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
-    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType));
+    const SpmvWorkspace ws =
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA));
     *itemsPerTile = ws.items_per_tile;
     *numTiles = ws.num_tiles;
     *tileStarts = static_cast<const int32_t*>(align_up_256(externalBuffer));
@@ -834,7 +871,8 @@ mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMa
     if (matA == nullptr || externalBuffer == nullptr || status == nullptr) return pub(BAD_POINTER);
     if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
-    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType));
+    const SpmvWorkspace ws =
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA));
     const char* word = static_cast<const char*>(align_up_256(externalBuffer)) + ws.off_status;
     cudaError_t e = cudaMemcpyAsync(status, word, sizeof(int), cudaMemcpyDeviceToHost, handle->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(handle->stream);
@@ -857,12 +895,12 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         return pub(BAD_POINTER);
     if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
-    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType));
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
     cudaError_t e = spmv_static_scratch(&scratch, &scratch_bytes);
     if (e != cudaSuccess) return pub(from_cuda(e));
-    if (ws.bytes > scratch_bytes) {
+    if (spmv_workspace(matA->row_num, matA->nnz, value_size(computeType)).bytes > scratch_bytes) {
+        const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType));
         char msg[200];
         std::snprintf(msg, sizeof msg,
                       "mcsparseB200SpMVNoAlloc: matrix needs %zu bytes of work area, the built-in one has %zu; "
@@ -871,6 +909,8 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         log_error(msg);
         return MCSPARSE_STATUS_INSUFFICIENT_RESOURCES;
     }
+    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType),
+                                            choose_small_tiles(handle, matA, scratch));
     const int base = matA->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(matA->rows);
     e = spmv_analysis(handle->stream, matA->row_num, matA->nnz, base, rows, ws, scratch);

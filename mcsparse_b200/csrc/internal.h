@@ -49,6 +49,10 @@ struct mcsparseSpMatDescr {
     void* analysed_buffer = nullptr;
     const void* analysed_rows = nullptr;
     int analysed_items_per_tile = 0;
+    // Tile size chosen by the locality probe for these column indices (probed once, then remembered).
+    const void* probed_cols = nullptr;
+    int64_t probed_nnz = -1;
+    bool small_tiles = false;
     // Chunk boundaries of the pipelined push (tiles and the rows they start at), read back once.
     void* push_buffer = nullptr;
     const void* push_rows_ptr = nullptr;
@@ -106,7 +110,12 @@ struct SpmvWorkspace {
     int64_t num_tiles = 0;
     size_t off_carry_row = 0, off_carry_val = 0, off_status = 0, bytes = 0;
 };
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size);
+// Layout for the chosen tile size; `bytes` is always the size the small tiles would need, so that
+// mcsparseSpMV_bufferSize does not depend on the choice.
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles = false);
+// Counts, over 4096 evenly spaced positions j, how often |col[j + 1] - col[j]| <= 8; the count is left
+// in *device_count and copied to *host_count (synchronises the stream).
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const int32_t* col, int* device_count, int* host_count);
 inline void* align_up_256(void* p) {
     return reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255));
 }

@@ -24,12 +24,32 @@ template <typename T>
 struct TileCfg;
 template <>
 struct TileCfg<float> {
-    static constexpr int kItemsPerThread = MCSPARSE_B200_SPMV_TILE_ITEMS_F32 / kThreads;
+    static constexpr int kLarge = MCSPARSE_B200_SPMV_TILE_ITEMS_F32 / kThreads;
+    static constexpr int kSmall = MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 / kThreads;
 };
 template <>
 struct TileCfg<double> {
-    static constexpr int kItemsPerThread = MCSPARSE_B200_SPMV_TILE_ITEMS_F64 / kThreads;
+    static constexpr int kLarge = MCSPARSE_B200_SPMV_TILE_ITEMS_F64 / kThreads;
+    static constexpr int kSmall = MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 / kThreads;
 };
+
+// Column locality probe: 1024 threads x 4 samples.
+__global__ void locality_probe_kernel(long long nnz, const int* __restrict__ col, int* __restrict__ count) {
+    __shared__ int s_count;
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    int local = 0;
+    for (int q = 0; q < 4; ++q) {
+        const long long j = ((long long)(threadIdx.x * 4 + q) * (nnz - 1)) / 4096;
+        if (j + 1 < nnz) {
+            const int d = __ldg(col + j + 1) - __ldg(col + j);
+            local += (d <= 8 && d >= -8);
+        }
+    }
+    atomicAdd(&s_count, local);
+    __syncthreads();
+    if (threadIdx.x == 0) *count = s_count;
+}
 
 // ---------------------------------------------------------------------------------------
 // K0: merge-path analysis. Thread t finds where diagonal min(t * items_per_tile, m + nnz)
@@ -541,9 +561,9 @@ __global__ void __launch_bounds__(kThreads)
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size) {
+static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int items_per_tile) {
     SpmvWorkspace ws;
-    ws.items_per_tile = value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    ws.items_per_tile = items_per_tile;
     const int64_t items = m + nnz;
     ws.num_tiles = (items + ws.items_per_tile - 1) / ws.items_per_tile;
     auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
@@ -552,6 +572,23 @@ SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size) {
     ws.off_status = ws.off_carry_val + up(size_t(ws.num_tiles) * value_size);
     ws.bytes = ws.off_status + 256;
     return ws;
+}
+
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles) {
+    const int large = value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    const int small = value_size == 8 ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32;
+    SpmvWorkspace ws = spmv_layout(m, nnz, value_size, small_tiles ? small : large);
+    ws.bytes = spmv_layout(m, nnz, value_size, small).bytes;
+    return ws;
+}
+
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const int32_t* col, int* device_count,
+                                int* host_count) {
+    locality_probe_kernel<<<1, 1024, 0, s>>>(nnz, col, device_count);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_count, device_count, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e;
 }
 
 cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
@@ -575,35 +612,48 @@ static size_t tuning_pad_smem() {
     return pad;
 }
 
+// One launch of the tile kernel over tiles [tile0, tile0 + count), for the tile size of `ws`.
+template <typename T, bool PUSH>
+static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, int64_t m, int64_t nnz, int base,
+                                const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
+                                ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
+                                const PeerList<T>& peers) {
+    char* base_ptr = static_cast<char*>(buf);
+    const int2* starts = reinterpret_cast<const int2*>(base_ptr);
+    int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
+    T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
+    int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
+    if (ws.items_per_tile == kThreads * TileCfg<T>::kLarge)
+        spmv_tile_kernel<T, kThreads, TileCfg<T>::kLarge, PUSH><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
+            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
+            (int)tile0);
+    else
+        spmv_tile_kernel<T, kThreads, TileCfg<T>::kSmall, PUSH><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
+            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
+            (int)tile0);
+    return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                        const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
                        const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers) {
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
-    const int2* starts = reinterpret_cast<const int2*>(base_ptr);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
-    constexpr int IPT = TileCfg<T>::kItemsPerThread;
-    int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
-    const unsigned grid = (unsigned)ws.num_tiles;
     const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
-    if (peers.count > 0) {
-        spmv_tile_kernel<T, kThreads, IPT, true><<<grid, kThreads, tuning_pad_smem(), s>>>(
-            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
-            0);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
+    cudaError_t e = peers.count > 0 ? launch_tiles<T, true>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y,
+                                                           alpha, beta, ws, buf, peers)
+                                    : launch_tiles<T, false>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y,
+                                                            alpha, beta, ws, buf, peers);
+    if (e != cudaSuccess) return e;
+    if (peers.count > 0)
         spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
                                                                   peers);
-        return cudaGetLastError();
-    }
-    spmv_tile_kernel<T, kThreads, IPT, false><<<grid, kThreads, tuning_pad_smem(), s>>>(
-        (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers, 0);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
-                                                               peers);
+    else
+        spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
+                                                                   peers);
     return cudaGetLastError();
 }
 
@@ -644,18 +694,12 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
-    int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
-    constexpr int IPT = TileCfg<T>::kItemsPerThread;
     const PeerList<T> none;
     cudaError_t e = cudaSuccess;
     for (int c = 0; c < chunks && e == cudaSuccess; ++c) {
         const int64_t t0 = chunk_tiles[c], t1 = chunk_tiles[c + 1];
-        if (t1 > t0) {
-            spmv_tile_kernel<T, kThreads, IPT, false><<<(unsigned)(t1 - t0), kThreads, tuning_pad_smem(), s>>>(
-                (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, none,
-                (int)t0);
-            e = cudaGetLastError();
-        }
+        if (t1 > t0)
+            e = launch_tiles<T, false>(s, t0, t1 - t0, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws, buf, none);
         if (e == cudaSuccess) e = cudaEventRecord(events[c], s);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(side, events[c], 0);
         if (e == cudaSuccess && t1 > t0) {

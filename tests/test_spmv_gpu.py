@@ -41,8 +41,11 @@ def run_spmv(handle, device, rp, col, val, x, y0, alpha, beta, base=0, preproces
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("base", [0, 1])
 @pytest.mark.parametrize("beta", [0.0, -0.75])
+@pytest.mark.parametrize("tile", ["auto", "small", "large"])
 @pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
-def test_spmv_adversarial_shapes(handle, device, name, dtype, base, beta):
+def test_spmv_adversarial_shapes(handle, device, name, dtype, base, beta, tile, monkeypatch):
+    if tile != "auto":
+        monkeypatch.setenv("MCSPARSE_B200_SPMV_TILE", tile)  # force one of the two tile sizes
     lengths = ADVERSARIAL_LENGTHS[name]
     ncols = max(max(lengths), 1) + 17
     rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=11, base=base)
@@ -54,12 +57,13 @@ def test_spmv_adversarial_shapes(handle, device, name, dtype, base, beta):
     assert_close(y, ref, d, TOL[np.dtype(dtype)], name)
     # the work partition in the buffer is bit-exact against the CPU partition
     nnz = col.size
-    ipt = capi.SPMV_TILE_ITEMS[MACA[dtype]]
-    part = oracle.merge_path_partition(rp, nnz, ipt, base)
     items, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
     capi.check(lib.mcsparseB200SpMVPartitionView(keep[0].d, C.c_void_p(buf.data_ptr()), C.byref(items), C.byref(nt),
                                                  C.byref(p)))
-    assert items.value == ipt and nt.value == part.shape[0] - 1
+    large, small = capi.SPMV_TILE_ITEMS[MACA[dtype]]  # the locality probe picks one of the two
+    assert items.value == {"auto": items.value, "small": small, "large": large}[tile] and items.value in (large, small)
+    part = oracle.merge_path_partition(rp, nnz, items.value, base)
+    assert nt.value == part.shape[0] - 1
     off = p.value - buf.data_ptr()
     got = buf[off:off + part.size * 4].view(torch.int32).cpu().numpy().reshape(-1, 2)
     np.testing.assert_array_equal(got, part)

@@ -72,7 +72,7 @@ def test_no_alloc_spmv_matches_spmv_on_two_calls_in_a_row(handle, device):
 
 
 def test_no_alloc_spmv_refuses_oversized_matrix(handle, device):
-    # 2.2e9 merge items of fp32 would need more than the fixed 8 MiB; no array is touched
+    # 2.2e9 merge items of fp32 would need more than the fixed 16 MiB; no array is touched
     # before the size check, so small placeholders stand in for the matrix.
     rows = 1 << 30
     nnz = (1 << 30) - 8
