@@ -467,27 +467,34 @@ template <typename T>
 __global__ void __launch_bounds__(512) push_rows_kernel(PeerList<T> peers, const T* __restrict__ y, long long r0,
                                                         long long r1) {
     constexpr int VW = 16 / (int)sizeof(T);
+    constexpr int UNROLL = 4;
+    const int p = blockIdx.y;  // one grid row of CTAs per destination: all peers are written concurrently
     const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     const long long nthreads = (long long)gridDim.x * blockDim.x;
+    T* const dst = peers.y[p] + peers.row_offset;
+    const long long mis = (long long)((reinterpret_cast<uintptr_t>(dst + r0) / sizeof(T)) & (VW - 1));
+    long long v0 = r0 + ((VW - mis) & (VW - 1));  // first row whose destination is 16-byte aligned
+    if (v0 > r1) v0 = r1;
+    const long long nvec = (r1 - v0) / VW;
+    for (long long c = tid; c < nvec; c += nthreads * UNROLL) {
+        T v[UNROLL][VW];
 #pragma unroll
-    for (int p = 0; p < PeerList<T>::kMax; ++p) {
-        if (p >= peers.count) break;
-        T* const dst = peers.y[p] + peers.row_offset;
-        const long long mis = (long long)((reinterpret_cast<uintptr_t>(dst + r0) / sizeof(T)) & (VW - 1));
-        long long v0 = r0 + ((VW - mis) & (VW - 1));  // first row whose destination is 16-byte aligned
-        if (v0 > r1) v0 = r1;
-        const long long nvec = (r1 - v0) / VW;
-        for (long long c = tid; c < nvec; c += nthreads) {
-            const long long i = v0 + c * VW;
-            T v[VW];
+        for (int u = 0; u < UNROLL; ++u) {
+            const long long cc = c + u * nthreads;
+            if (cc < nvec) {
 #pragma unroll
-            for (int e = 0; e < VW; ++e) v[e] = y[i + e];
-            store_vec16(dst + i, v);
+                for (int e = 0; e < VW; ++e) v[u][e] = y[v0 + cc * VW + e];
+            }
         }
-        const long long tail0 = v0 + nvec * VW;  // fewer than VW rows before v0 and after tail0
-        if (tid < VW && r0 + tid < v0) dst[r0 + tid] = y[r0 + tid];
-        if (tid >= 32 && tid < 32 + VW && tail0 + (tid - 32) < r1) dst[tail0 + (tid - 32)] = y[tail0 + (tid - 32)];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const long long cc = c + u * nthreads;
+            if (cc < nvec) store_vec16(dst + v0 + cc * VW, v[u]);
+        }
     }
+    const long long tail0 = v0 + nvec * VW;  // fewer than VW rows before v0 and after tail0
+    if (tid < VW && r0 + tid < v0) dst[r0 + tid] = y[r0 + tid];
+    if (tid >= 32 && tid < 32 + VW && tail0 + (tid - 32) < r1) dst[tail0 + (tid - 32)] = y[tail0 + (tid - 32)];
 }
 
 // Adds the carries of rows that cross tile boundaries. The first tile of each run of equal
@@ -657,11 +664,11 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const i
     return cudaGetLastError();
 }
 
-// CTAs (of 512 threads) of one row-copy kernel: MCSPARSE_B200_PUSH_CTAS, default 64. Enough to keep
-// NVLink busy, few enough to leave most SM slots to the tile kernel running beside it.
+// CTAs (of 512 threads, over all peers) of one row-copy kernel: MCSPARSE_B200_PUSH_CTAS, default 112.
+// Enough to keep NVLink busy, few enough to leave most SM slots to the tile kernel running beside it.
 static long long push_copy_ctas() {
     const char* e = std::getenv("MCSPARSE_B200_PUSH_CTAS");
-    const long long v = e ? std::atoll(e) : 64;
+    const long long v = e ? std::atoll(e) : 112;
     return v < 1 ? 1 : (v > 1184 ? 1184 : v);
 }
 
@@ -719,8 +726,9 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
                                         cudaMemcpyDeviceToDevice, side);
             } else {
                 const long long vecs = (r1 - r0) * (long long)sizeof(T) / 16 + 1;
-                const unsigned grid = (unsigned)std::min<long long>((vecs + 511) / 512, push_copy_ctas());
-                push_rows_kernel<T><<<grid, 512, 0, side>>>(peers, y, r0, r1);
+                const unsigned gx = (unsigned)std::max<long long>(
+                    1, std::min<long long>((vecs + 2047) / 2048, push_copy_ctas() / peers.count));
+                push_rows_kernel<T><<<dim3(gx, (unsigned)peers.count), 512, 0, side>>>(peers, y, r0, r1);
                 e = cudaGetLastError();
             }
         }
