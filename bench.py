@@ -158,7 +158,8 @@ class SpmvJob:
         self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta)
         self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta)
         self.flops = 2 * self.total_nnz
-        self.launches_per_step = 2  # tile kernel + carry fix-up
+        # tile kernel + carry fix-up; with one peer the step is pipelined: 4 tile launches + 4 fix-ups
+        self.launches_per_step = 8 if world == 2 else 2
 
     def compute(self):
         """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""

@@ -150,6 +150,9 @@ bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, void* scratch
                             &near) != cudaSuccess)
         near = 4096;
     A->small_tiles = near < 1024;
+    // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
+    const int64_t large = A->valueType == MACA_R_64F ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    if ((A->row_num + A->nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) A->small_tiles = true;
     A->probed_cols = A->cols;
     A->probed_nnz = A->nnz;
     return A->small_tiles;

@@ -46,4 +46,6 @@ ADVERSARIAL_LENGTHS = {
     "tile_straddle": [2047, 2049, 4095, 4097, 1, 2048, 4096],
     "many_short": [1, 2, 0, 3] * 4000,
     "uniform_27": [27] * 3000,
+    "mostly_empty": [0] * 5000 + [3] + [0] * 3000 + [1] * 10,  # whole tiles of row ends only
+    "mixed_medium_long": ([2] * 150 + [300] + [5] * 100 + [1500] + [9] * 50 + [40]) * 6 + [7000],
 }
