@@ -249,6 +249,18 @@ mcsparseStatus_t mcsparseDnMatGet(mcsparseDnMatDescr_t dnMatDescr, int64_t* rows
 mcsparseStatus_t mcsparseDnMatGetValues(mcsparseDnMatDescr_t dnMatDescr, void** values);
 mcsparseStatus_t mcsparseDnMatSetValues(mcsparseDnMatDescr_t dnMatDescr, void* values);
 
+/* ---- Strided batches for mcsparseSpMM: batchCount independent products whose operands lie batchStride
+ *      elements apart (A: row offsets offsetsBatchStride apart, columns and values
+ *      columnsValuesBatchStride apart; a stride of 0 shares the operand between the batches).
+ *      Reference: mcsparse/include/interface/mcsp_generic.h:180-185, setters
+ *      mcsparse/src/kernels/generic/mcsp_generic.cpp:701-743, batching in the kernel
+ *      mcsparse/src/kernels/level3/spmm/csr_spmm_device.hpp:102-108. A, B and C must carry the same
+ *      batch count (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:96-98). ---- */
+mcsparseStatus_t mcsparseCsrSetStridedBatch(mcsparseSpMatDescr_t spMatDescr, int batchCount, int64_t offsetsBatchStride,
+                                            int64_t columnsValuesBatchStride);
+mcsparseStatus_t mcsparseDnMatSetStridedBatch(mcsparseDnMatDescr_t dnMatDescr, int batchCount, int64_t batchStride);
+mcsparseStatus_t mcsparseDnMatGetStridedBatch(mcsparseDnMatDescr_t dnMatDescr, int* batchCount, int64_t* batchStride);
+
 /* ---- SpMV: y = alpha * A * x + beta * y.
  * Reference: mcsparse/include/interface/mcsp_generic.h:43-51; entry
  * mcsparse/src/wrapper/mcsp_interface_wrapper.cpp:1236-1249; validation order

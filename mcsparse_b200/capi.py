@@ -100,6 +100,9 @@ PROTOTYPES = {
     "mcsparseDnMatGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pi, _pi]),
     "mcsparseDnMatGetValues": (_i, [_vp, _pvp]),
     "mcsparseDnMatSetValues": (_i, [_vp, _vp]),
+    "mcsparseCsrSetStridedBatch": (_i, [_vp, _i, _i64, _i64]),
+    "mcsparseDnMatSetStridedBatch": (_i, [_vp, _i, _i64]),
+    "mcsparseDnMatGetStridedBatch": (_i, [_vp, _pi, _pi64]),
     "mcsparseSpMV_bufferSize": (_i, _SPMV_ARGS + [_psz]),
     "mcsparseSpMV_preprocess": (_i, _SPMV_ARGS + [_vp]),
     "mcsparseSpMV": (_i, _SPMV_ARGS + [_vp]),

@@ -287,6 +287,7 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
     const bool tB = opB == MCSPARSE_OPERATION_TRANSPOSE;
     const int64_t opb_rows = tB ? B->col_num : B->row_num, opb_cols = tB ? B->row_num : B->col_num;
     if (opb_rows != A->col_num || opb_cols != C->col_num || C->row_num != A->row_num) return BAD_SIZE;
+    if (!(C->batchCount == A->batchCount && C->batchCount == B->batchCount)) return BAD_SIZE;
     if (B->ld < (B->order == MCSPARSE_ORDER_ROW ? B->col_num : B->row_num)) return BAD_SIZE;
     if (C->ld < (C->order == MCSPARSE_ORDER_ROW ? C->col_num : C->row_num)) return BAD_SIZE;
     return OK;
@@ -310,11 +311,20 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
     int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
     if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
     const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
-    return from_cuda(spmm<T>(h->stream, A->row_num, C->col_num, A->mat_descr->base,
-                             static_cast<const int32_t*>(A->rows), static_cast<const int32_t*>(A->cols),
-                             static_cast<const T*>(A->vals), static_cast<const T*>(B->values), b_rs, b_cs,
-                             static_cast<T*>(C->values), c_rs, c_cs, scalar_arg<T>(h, alpha),
-                             scalar_arg<T>(h, beta), num_panels, panel_ptr));
+    // Strided batch: the same product on operands batchStride elements apart, one launch sequence per batch
+    // (the column panels, built for batch 0's structure, are used only for a single product).
+    for (int64_t b = 0; b < C->batchCount; ++b) {
+        const bool single = C->batchCount == 1;
+        cudaError_t e = spmm<T>(h->stream, A->row_num, C->col_num, A->mat_descr->base,
+                                static_cast<const int32_t*>(A->rows) + b * A->offsetsBatchStride,
+                                static_cast<const int32_t*>(A->cols) + b * A->batchStride,
+                                static_cast<const T*>(A->vals) + b * A->batchStride,
+                                static_cast<const T*>(B->values) + b * B->batchStride, b_rs, b_cs,
+                                static_cast<T*>(C->values) + b * C->batchStride, c_rs, c_cs, scalar_arg<T>(h, alpha),
+                                scalar_arg<T>(h, beta), single ? num_panels : 1, single ? panel_ptr : nullptr);
+        if (e != cudaSuccess) return from_cuda(e);
+    }
+    return OK;
 }
 
 // Legacy csrmm / csrmm2: column-major B and C (mcsparse/src/kernels/level3/spmm/mcsp_spmm_gpu.cpp:19-80).
@@ -819,6 +829,33 @@ mcsparseStatus_t mcsparseDnMatGetValues(mcsparseDnMatDescr_t d, void** values) {
 mcsparseStatus_t mcsparseDnMatSetValues(mcsparseDnMatDescr_t d, void* values) {
     if (d == nullptr) return pub(BAD_POINTER);
     d->values = values;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+// ----------------------------------------------------------------------------- strided batches
+
+mcsparseStatus_t mcsparseCsrSetStridedBatch(mcsparseSpMatDescr_t d, int batchCount, int64_t offsetsBatchStride,
+                                            int64_t columnsValuesBatchStride) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    if (batchCount <= 0 || offsetsBatchStride < 0 || columnsValuesBatchStride < 0) return pub(BAD_SIZE);
+    d->batchCount = batchCount;
+    d->offsetsBatchStride = offsetsBatchStride;
+    d->batchStride = columnsValuesBatchStride;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnMatSetStridedBatch(mcsparseDnMatDescr_t d, int batchCount, int64_t batchStride) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    if (batchCount <= 0 || batchStride < 0) return pub(BAD_SIZE);
+    d->batchCount = batchCount;
+    d->batchStride = batchStride;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseDnMatGetStridedBatch(mcsparseDnMatDescr_t d, int* batchCount, int64_t* batchStride) {
+    if (d == nullptr || batchCount == nullptr || batchStride == nullptr) return pub(BAD_POINTER);
+    *batchCount = (int)d->batchCount;
+    *batchStride = d->batchStride;
     return MCSPARSE_STATUS_SUCCESS;
 }
 

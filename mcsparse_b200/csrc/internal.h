@@ -43,6 +43,7 @@ struct mcsparseSpMatDescr {
     mcsparseIndexBase_t idxBase = MCSPARSE_INDEX_BASE_ZERO;
     macaDataType valueType = MACA_R_32F;
     mcsparseMatDescr* mat_descr = nullptr;
+    int64_t batchCount = 1, batchStride = 0, offsetsBatchStride = 0;  // strided batch (SpMM)
     // Analysis recorded by mcsparseSpMV_preprocess: which buffer holds the partition of
     // which row-offset array. Guarded by `lock`; cleared by mcsparseCsrSetPointers.
     std::mutex lock;
@@ -78,6 +79,7 @@ struct mcsparseDnMatDescr {
     void* values = nullptr;
     macaDataType valueType = MACA_R_32F;
     mcsparseOrder_t order = MCSPARSE_ORDER_COL;
+    int64_t batchCount = 1, batchStride = 0;
 };
 
 namespace mcsp_b200 {

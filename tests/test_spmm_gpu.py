@@ -213,3 +213,49 @@ def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, monkeypat
     mc.spmm(handle, A, Bm, Cm, other, alpha=1.25, beta=beta)
     torch.cuda.synchronize()
     assert_close(t[4].cpu().numpy().reshape(m, n), ref, d, TOL[np.dtype(dtype)], "single pass")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("shared_a", [False, True])
+def test_spmm_strided_batch(handle, device, dtype, shared_a):
+    """Three products in one call: operands a batch stride apart; a stride of 0 shares A between them."""
+    batches, k, n = 3, 60, 8
+    lengths = [4, 0, 9, 17, 1, 33]
+    m = len(lengths)
+    mats = [csr_from_lengths(lengths, k, dtype, seed=40 + (0 if shared_a else b)) for b in range(batches)]
+    nnz = mats[0][1].size  # same lengths, so every batch has the same nonzero count
+    rng = np.random.default_rng(40)
+    Bs = rng.uniform(-1, 1, (batches, k, n)).astype(dtype)
+    C0 = rng.uniform(-1, 1, (batches, m, n)).astype(dtype)
+    if shared_a:
+        rp, col, val = mats[0]
+        strides = (0, 0)
+    else:
+        rp = np.concatenate([mt[0] for mt in mats])
+        col = np.concatenate([mt[1] for mt in mats])
+        val = np.concatenate([mt[2] for mt in mats])
+        strides = (m + 1, nnz)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, Bs.ravel(), C0.ravel().copy())]
+    A = mc.CsrMatrix(m, k, t[0][:m + 1], t[1][:nnz], t[2][:nnz])
+    Bm, Cm = mc.DnMat(t[3], k, n, n), mc.DnMat(t[4], m, n, n)
+    capi.check(lib.mcsparseCsrSetStridedBatch(A.d, batches, strides[0], strides[1]))
+    capi.check(lib.mcsparseDnMatSetStridedBatch(Bm.d, batches, k * n))
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    one = (C.c_float if dtype == np.float32 else C.c_double)(1.0)
+    pa = C.cast(C.pointer(one), C.c_void_p)
+    dt = capi.MACA_R_32F if dtype == np.float32 else capi.MACA_R_64F
+    # C without a batch setting does not match A and B
+    assert lib.mcsparseSpMM(handle.h, 0, 0, pa, A.d, Bm.d, pa, Cm.d, dt, 0,
+                            C.c_void_p(buf.data_ptr())) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    capi.check(lib.mcsparseDnMatSetStridedBatch(Cm.d, batches, m * n))
+    bc, bs = C.c_int(), C.c_int64()
+    capi.check(lib.mcsparseDnMatGetStridedBatch(Cm.d, C.byref(bc), C.byref(bs)))
+    assert (bc.value, bs.value) == (batches, m * n)
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=0.5, beta=2.0)
+    torch.cuda.synchronize()
+    got = t[4].cpu().numpy().reshape(batches, m, n)
+    for b in range(batches):
+        rpb, colb, valb = mats[b]
+        ref, d = oracle.spmm(rpb, colb, valb, Bs[b], n, ROW, n, 0.5, 2.0, C0[b], n, ROW)
+        assert_close(got[b], ref, d, TOL[np.dtype(dtype)], f"batch {b}")
+    assert lib.mcsparseCsrSetStridedBatch(A.d, 0, 0, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
