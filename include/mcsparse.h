@@ -8,7 +8,8 @@
  *
  * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO as an input of
  * mcsparseSpMV), MCSPARSE_OPERATION_NON_TRANSPOSE,
- * MACA_R_32F / MACA_R_64F, MCSPARSE_INDEX_32I offsets and columns, index base 0 or 1.
+ * MACA_R_32F / MACA_R_64F, offsets and columns both MCSPARSE_INDEX_32I or (CSR only) both
+ * MCSPARSE_INDEX_64I with extents below 2^31, index base 0 or 1.
  * Everything else that the reference accepts on these entry points returns
  * MCSPARSE_STATUS_NOT_SUPPORTED here.
  */

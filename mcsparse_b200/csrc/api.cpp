@@ -111,11 +111,15 @@ struct DeviceGuard {
 St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
               bool need_buffer, const void* buffer, bool need_size_out, const void* size_out,
-              bool allow_coo = false) {
+              bool allow_coo = false, bool allow_wide_indices = false) {
     if (h == nullptr) return BAD_HANDLE;
     if (alpha == nullptr || beta == nullptr || A == nullptr || X == nullptr || Y == nullptr) return BAD_POINTER;
     if (need_size_out && size_out == nullptr) return BAD_POINTER;
-    if (!(A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I)) return NOT_IMPL;
+    // Index types come in matched pairs (mcsp_spmv_gpu.cpp:1112-1118); 64-bit indices run on CSR only,
+    // and the extents must still fit 31 bits.
+    const bool narrow = A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I;
+    const bool wide = A->rowIdxType == MCSPARSE_INDEX_64I && A->colIdxType == MCSPARSE_INDEX_64I;
+    if (!(narrow || (wide && allow_wide_indices && A->format == MCSPARSE_FORMAT_CSR))) return NOT_IMPL;
     if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(X->size) || too_big(Y->size) ||
         too_big(A->row_num + A->nnz))
         return NOT_IMPL;
@@ -138,6 +142,7 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
 // descriptor; MCSPARSE_B200_SPMV_TILE=small|large overrides. `scratch` is device memory the
 // probe may overwrite (the start of the work buffer, before the analysis writes it).
 bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, void* scratch) {
+    if (A->colIdxType == MCSPARSE_INDEX_64I) return true;  // one tile size for 64-bit indices
     if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
         if (e[0] == 's') return true;
         if (e[0] == 'l') return false;
@@ -174,22 +179,26 @@ struct PushArgs {
     int64_t row_offset = 0;
 };
 
-template <typename T>
+size_t index_size(const mcsparseSpMatDescr* A) { return A->rowIdxType == MCSPARSE_INDEX_64I ? 8 : 4; }
+
+template <typename T, typename I>
 St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
             const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, bool small_tiles,
             const PushArgs& push = PushArgs()) {
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), small_tiles);
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), small_tiles, sizeof(I));
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
-    const int32_t* rows = static_cast<const int32_t*>(A->rows);
+    const I* rows = static_cast<const I*>(A->rows);
     if (A->format == MCSPARSE_FORMAT_COO) {
-        // Row offsets derived from the sorted row indices live behind the SpMV work area.
+        // Row offsets derived from the sorted row indices live behind the SpMV work area
+        // (32-bit indices only: the argument check admits no 64-bit COO).
         int32_t* offsets = reinterpret_cast<int32_t*>(static_cast<char*>(buf) + ws.bytes);
         if (analyse) {
-            cudaError_t e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, rows, offsets);
+            cudaError_t e = coo_row_offsets(h->stream, A->row_num, A->nnz, base,
+                                            static_cast<const int32_t*>(A->rows), offsets);
             if (e != cudaSuccess) return from_cuda(e);
         }
-        rows = offsets;
+        rows = reinterpret_cast<const I*>(offsets);
     }
     if (analyse) {
         cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
@@ -200,17 +209,18 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mc
     peers.count = push.count;
     peers.row_offset = push.row_offset;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
-    cudaError_t e = spmv_tiled<T>(h->stream, A->row_num, A->nnz, base, rows, static_cast<const int32_t*>(A->cols),
-                                  static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
-                                  static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
-                                  buf, peers);
+    cudaError_t e = spmv_tiled<T, I>(h->stream, A->row_num, A->nnz, base, rows, static_cast<const I*>(A->cols),
+                                     static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
+                                     static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
+                                     buf, peers);
     return from_cuda(e);
 }
 
 St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
               void* buffer, bool preprocess_only, const PushArgs& push = PushArgs()) {
-    St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr, push.count == 0);
+    St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr, push.count == 0,
+                       push.count == 0);
     if (st != OK) return st;
     // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
     if (A->rows == nullptr || A->cols == nullptr || A->vals == nullptr || X->values == nullptr ||
@@ -219,7 +229,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
     const bool small = choose_small_tiles(h, A, align_up_256(buffer));
-    const int ipt = spmv_workspace(A->row_num, A->nnz, value_size(computeType), small).items_per_tile;
+    const int ipt = spmv_workspace(A->row_num, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
@@ -232,9 +242,12 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
             analyse = false;
         }
     }
+    const bool wide = index_size(A) == 8;
     if (computeType == MACA_R_64F)
-        return spmv_run<double>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
-    return spmv_run<float>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+        return wide ? spmv_run<double, int64_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                    : spmv_run<double, int32_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+    return wide ? spmv_run<float, int64_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                : spmv_run<float, int32_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
 }
 
 // Legacy csrmv family: raw arrays plus a matrix descriptor
@@ -259,7 +272,7 @@ St csrmv_entry(mcsparseHandle_t h, mcsparseOperation_t transA, int m, int n, int
         void* buf = align_up_256(buffer);
         cudaError_t e = spmv_analysis(h->stream, m, nnz, descr->base, rows, ws, buf);
         if (e != cudaSuccess) return from_cuda(e);
-        return from_cuda(spmv_tiled<T>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b, ws, buf));
+        return from_cuda(spmv_tiled<T, int32_t>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b, ws, buf));
     }
     return from_cuda(spmv_rowgroup<T>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b));
 }
@@ -273,7 +286,10 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
     if (h == nullptr) return BAD_HANDLE;
     if (A == nullptr || B == nullptr || C == nullptr || alpha == nullptr || beta == nullptr) return BAD_POINTER;
     if (need_buffer && buffer == nullptr) return BAD_POINTER;
-    if (!(A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I)) return NOT_IMPL;
+    // Matched index pairs only (mcsp_spmm_gpu.cpp:954-960); extents must fit 31 bits either way.
+    if (!((A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I) ||
+          (A->rowIdxType == MCSPARSE_INDEX_64I && A->colIdxType == MCSPARSE_INDEX_64I)))
+        return NOT_IMPL;
     if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(B->row_num) ||
         too_big(B->col_num) || too_big(B->ld) || too_big(C->row_num) || too_big(C->col_num) || too_big(C->ld))
         return NOT_IMPL;
@@ -305,7 +321,7 @@ SpmmPlan spmm_plan_for(mcsparseOperation_t opB, const mcsparseSpMatDescr* A, con
     return spmm_plan(A->row_num, A->col_num, C->col_num, A->nnz, value_size(computeType), spmm_row_major(opB, B, C));
 }
 
-template <typename T>
+template <typename T, typename I>
 St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, mcsparseDnMatDescr* B,
             mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr) {
     int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
@@ -315,9 +331,9 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
     // (the column panels, built for batch 0's structure, are used only for a single product).
     for (int64_t b = 0; b < C->batchCount; ++b) {
         const bool single = C->batchCount == 1;
-        cudaError_t e = spmm<T>(h->stream, A->row_num, C->col_num, A->mat_descr->base,
-                                static_cast<const int32_t*>(A->rows) + b * A->offsetsBatchStride,
-                                static_cast<const int32_t*>(A->cols) + b * A->batchStride,
+        cudaError_t e = spmm<T, I>(h->stream, A->row_num, C->col_num, A->mat_descr->base,
+                                static_cast<const I*>(A->rows) + b * A->offsetsBatchStride,
+                                static_cast<const I*>(A->cols) + b * A->batchStride,
                                 static_cast<const T*>(A->vals) + b * A->batchStride,
                                 static_cast<const T*>(B->values) + b * B->batchStride, b_rs, b_cs,
                                 static_cast<T*>(C->values) + b * C->batchStride, c_rs, c_cs, scalar_arg<T>(h, alpha),
@@ -342,7 +358,7 @@ St csrmm_entry(mcsparseHandle_t h, mcsparseOperation_t transA, mcsparseOperation
     DeviceGuard guard(h->device);
     int64_t b_rs = 1, b_cs = ldb;
     if (transB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
-    return from_cuda(spmm<T>(h->stream, m, n, descr->base, rows, cols, vals, B, b_rs, b_cs, C, 1, ldc,
+    return from_cuda(spmm<T, int32_t>(h->stream, m, n, descr->base, rows, cols, vals, B, b_rs, b_cs, C, 1, ldc,
                              scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
 }
 
@@ -866,11 +882,12 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
                                          mcsparseDnVecDescr_t vecY, macaDataType computeType,
                                          mcsparseSpMVAlg_t alg, size_t* bufferSize) {
     (void)alg;
-    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize, true);
+    St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize, true,
+                       true);
     if (st != OK) return pub(st);
     // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
     // also needs room for the row offsets derived from its row indices.
-    *bufferSize = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType)).bytes + 256;
+    *bufferSize = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType), false, index_size(matA)).bytes + 256;
     if (matA->format == MCSPARSE_FORMAT_COO) *bufferSize += ((size_t(matA->row_num) + 1) * 4 + 255) & ~size_t(255);
     return MCSPARSE_STATUS_SUCCESS;
 }
@@ -898,7 +915,7 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
         return pub(BAD_POINTER);
     if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
     const SpmvWorkspace ws =
-        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA));
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
     *itemsPerTile = ws.items_per_tile;
     *numTiles = ws.num_tiles;
     *tileStarts = static_cast<const int32_t*>(align_up_256(externalBuffer));
@@ -912,7 +929,7 @@ mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMa
     if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
     const SpmvWorkspace ws =
-        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA));
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
     const char* word = static_cast<const char*>(align_up_256(externalBuffer)) + ws.off_status;
     cudaError_t e = cudaMemcpyAsync(status, word, sizeof(int), cudaMemcpyDeviceToHost, handle->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(handle->stream);
@@ -956,12 +973,12 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
     e = spmv_analysis(handle->stream, matA->row_num, matA->nnz, base, rows, ws, scratch);
     if (e != cudaSuccess) return pub(from_cuda(e));
     if (computeType == MACA_R_64F)
-        e = spmv_tiled<double>(handle->stream, matA->row_num, matA->nnz, base, rows,
+        e = spmv_tiled<double, int32_t>(handle->stream, matA->row_num, matA->nnz, base, rows,
                                static_cast<const int32_t*>(matA->cols), static_cast<const double*>(matA->vals),
                                static_cast<const double*>(vecX->values), static_cast<double*>(vecY->values),
                                scalar_arg<double>(handle, alpha), scalar_arg<double>(handle, beta), ws, scratch);
     else
-        e = spmv_tiled<float>(handle->stream, matA->row_num, matA->nnz, base, rows,
+        e = spmv_tiled<float, int32_t>(handle->stream, matA->row_num, matA->nnz, base, rows,
                               static_cast<const int32_t*>(matA->cols), static_cast<const float*>(matA->vals),
                               static_cast<const float*>(vecX->values), static_cast<float*>(vecY->values),
                               scalar_arg<float>(handle, alpha), scalar_arg<float>(handle, beta), ws, scratch);
@@ -1001,9 +1018,15 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
     matA->spmm_buffer = nullptr;
     if (plan.num_panels <= 1) return MCSPARSE_STATUS_SUCCESS;
     DeviceGuard guard(handle->device);
-    if (spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base, static_cast<const int32_t*>(matA->rows),
-                        static_cast<const int32_t*>(matA->cols), plan, align_up_256(externalBuffer)) != cudaSuccess)
-        return MCSPARSE_STATUS_SUCCESS;
+    const cudaError_t e =
+        matA->rowIdxType == MCSPARSE_INDEX_64I
+            ? spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base,
+                              static_cast<const int64_t*>(matA->rows), static_cast<const int64_t*>(matA->cols), plan,
+                              align_up_256(externalBuffer))
+            : spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base,
+                              static_cast<const int32_t*>(matA->rows), static_cast<const int32_t*>(matA->cols), plan,
+                              align_up_256(externalBuffer));
+    if (e != cudaSuccess) return MCSPARSE_STATUS_SUCCESS;
     matA->spmm_buffer = externalBuffer;
     matA->spmm_rows = matA->rows;
     matA->spmm_cols = matA->cols;
@@ -1035,9 +1058,12 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
             panel_ptr = static_cast<const int*>(align_up_256(externalBuffer));
         }
     }
+    const bool wide = index_size(matA) == 8;
     if (computeType == MACA_R_64F)
-        return pub(spmm_run<double>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
-    return pub(spmm_run<float>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+        return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr)
+                        : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+    return pub(wide ? spmm_run<float, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr)
+                    : spmm_run<float, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
 }
 
 // ----------------------------------------------------------------------------- legacy entry points

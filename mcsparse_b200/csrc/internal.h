@@ -114,20 +114,24 @@ struct SpmvWorkspace {
 };
 // Layout for the chosen tile size; `bytes` is always the size the small tiles would need, so that
 // mcsparseSpMV_bufferSize does not depend on the choice.
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles = false);
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles = false,
+                             size_t index_size = 4);
 // Counts, over 4096 evenly spaced positions j, how often |col[j + 1] - col[j]| <= 8; the count is left
 // in *device_count and copied to *host_count (synchronises the stream).
-cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const int32_t* col, int* device_count, int* host_count);
+template <typename I>
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const I* col, int* device_count, int* host_count);
 inline void* align_up_256(void* p) {
     return reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255));
 }
 
-cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
-                          const SpmvWorkspace& ws, void* buf);
-template <typename T>
-cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
-                       const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
-                       const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers = PeerList<T>());
+// I: type of the row offsets and column indices (int32_t or int64_t; extents must fit 31 bits either way).
+template <typename I>
+cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const SpmvWorkspace& ws,
+                          void* buf);
+template <typename T, typename I>
+cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col, const T* val,
+                       const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
+                       const PeerList<T>& peers = PeerList<T>());
 // Rows at which the given tiles start, copied to the host (synchronises the stream).
 cudaError_t spmv_read_tile_rows(cudaStream_t s, const void* buf, int count, const int64_t* tiles, int64_t* rows);
 // The tiles in `chunks` launches; after each, a copy kernel on `side` pushes the rows that ended in
@@ -154,13 +158,14 @@ struct SpmmPlan {
     size_t bytes = 128;
 };
 SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_size, bool row_major_operands);
-cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
-                            const SpmmPlan& plan, void* buf);
+template <typename I>
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const I* row_ptr, const I* col, const SpmmPlan& plan,
+                            void* buf);
 
 // Dense operand addressed as element(r, c) = ptr[r * row_stride + c * col_stride].
-template <typename T>
-cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
-                 const T* val, const T* B, int64_t b_row_stride, int64_t b_col_stride, T* C, int64_t c_row_stride,
+template <typename T, typename I>
+cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val,
+                 const T* B, int64_t b_row_stride, int64_t b_col_stride, T* C, int64_t c_row_stride,
                  int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels = 1,
                  const int* panel_ptr = nullptr);
 

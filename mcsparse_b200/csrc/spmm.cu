@@ -79,9 +79,9 @@ __device__ __forceinline__ double2 zero_vec<double2>() {
 // C. Successive rows hit the same L2-resident slice of B instead of all of B, which trades the
 // random re-reads of B from HBM for streaming re-reads of C. Rows with nothing in a later panel
 // are skipped entirely.
-template <typename T, int G, bool PANEL>
+template <typename T, int G, bool PANEL, typename I>
 __global__ void __launch_bounds__(kThreads)
-    spmm_rowmajor_kernel(int m, int n, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+    spmm_rowmajor_kernel(int m, int n, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                          const T* __restrict__ val, const T* __restrict__ B, long long ldb, T* __restrict__ C,
                          long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg,
                          const int* __restrict__ panel_lo, const int* __restrict__ panel_hi, int first_panel) {
@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(kThreads)
             j0 = __ldg(panel_lo + row);
             j1 = __ldg(panel_hi + row);
         } else {
-            j0 = __ldg(row_ptr + row) - base;
-            j1 = __ldg(row_ptr + row + 1) - base;
+            j0 = (int)__ldg(row_ptr + row) - base;
+            j1 = (int)__ldg(row_ptr + row + 1) - base;
         }
     }
     V acc = zero_vec<V>();
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kThreads)
         int cj = 0;
         T vj = T(0);
         if (j + lane < j1) {
-            cj = __ldcs(col + j + lane);
+            cj = (int)__ldcs(col + j + lane);
             vj = __ldcs(val + j + lane);
         }
         const int cnt = min(G, j1 - j);
@@ -139,11 +139,12 @@ __global__ void __launch_bounds__(kThreads)
 
 // One thread per row: where each column panel starts inside the row (lower bound of the panel's first
 // column among the row's sorted columns). A row whose columns are not sorted is given to panel 0 whole.
-__global__ void spmm_panel_ptr_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+template <typename I>
+__global__ void spmm_panel_ptr_kernel(int m, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                                       int num_panels, int panel_cols, int* __restrict__ panel_ptr) {
     const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (r >= m) return;
-    const int j0 = row_ptr[r] - base, j1 = row_ptr[r + 1] - base;
+    const int j0 = (int)row_ptr[r] - base, j1 = (int)row_ptr[r + 1] - base;
     bool sorted = true;
     for (int j = j0 + 1; j < j1; ++j) sorted &= col[j - 1] <= col[j];
     panel_ptr[r] = j0;
@@ -168,10 +169,10 @@ __global__ void spmm_panel_ptr_kernel(int m, int base, const int* __restrict__ r
 
 // Any layout, any n: one thread per C element, addressed through (row, col) strides.
 // Consecutive threads run along C's contiguous dimension.
-template <typename T>
+template <typename T, typename I>
 __global__ void __launch_bounds__(kThreads)
-    spmm_strided_kernel(long long m, long long n, int base, const int* __restrict__ row_ptr,
-                        const int* __restrict__ col, const T* __restrict__ val, const T* __restrict__ B,
+    spmm_strided_kernel(long long m, long long n, int base, const I* __restrict__ row_ptr,
+                        const I* __restrict__ col, const T* __restrict__ val, const T* __restrict__ B,
                         long long b_rs, long long b_cs, T* __restrict__ C, long long c_rs, long long c_cs,
                         ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
     const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -184,9 +185,10 @@ __global__ void __launch_bounds__(kThreads)
         c = idx / m;
         r = idx - c * m;
     }
-    const int j0 = __ldg(row_ptr + r) - base, j1 = __ldg(row_ptr + r + 1) - base;
+    const int j0 = (int)__ldg(row_ptr + r) - base, j1 = (int)__ldg(row_ptr + r + 1) - base;
     T sum = T(0);
-    for (int j = j0; j < j1; ++j) sum += __ldg(val + j) * __ldg(B + (long long)(__ldg(col + j) - base) * b_rs + c * b_cs);
+    for (int j = j0; j < j1; ++j)
+        sum += __ldg(val + j) * __ldg(B + ((long long)__ldg(col + j) - base) * b_rs + c * b_cs);
     const T alpha = alpha_arg.get(), beta = beta_arg.get();
     T* out = C + r * c_rs + c * c_cs;
     T v = alpha * sum;
@@ -194,20 +196,19 @@ __global__ void __launch_bounds__(kThreads)
     *out = v;
 }
 
-template <typename T, int G>
-cudaError_t launch_rowmajor(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr,
-                            const int32_t* col, const T* val, const T* B, int64_t ldb, T* C, int64_t ldc,
+template <typename T, int G, typename I>
+cudaError_t launch_rowmajor(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val, const T* B, int64_t ldb, T* C, int64_t ldc,
                             ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
     constexpr int W = VecOf<T>::W;
     const long long threads_total = m * G;
     dim3 grid((unsigned)((threads_total + kThreads - 1) / kThreads), (unsigned)((n + G * W - 1) / (G * W)));
     if (num_panels <= 1 || panel_ptr == nullptr) {
-        spmm_rowmajor_kernel<T, G, false><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C,
+        spmm_rowmajor_kernel<T, G, false, I><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C,
                                                                     ldc, alpha, beta, nullptr, nullptr, 1);
         return cudaGetLastError();
     }
     for (int p = 0; p < num_panels; ++p) {
-        spmm_rowmajor_kernel<T, G, true><<<grid, kThreads, 0, s>>>(
+        spmm_rowmajor_kernel<T, G, true, I><<<grid, kThreads, 0, s>>>(
             (int)m, (int)n, base, row_ptr, col, val, B, ldb, C, ldc, alpha, beta, panel_ptr + (size_t)p * m,
             panel_ptr + (size_t)(p + 1) * m, p == 0);
         cudaError_t e = cudaGetLastError();
@@ -244,17 +245,17 @@ SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_si
     return plan;
 }
 
-cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
-                            const SpmmPlan& plan, void* buf) {
+template <typename I>
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const I* row_ptr, const I* col, const SpmmPlan& plan,
+                            void* buf) {
     if (plan.num_panels <= 1) return cudaSuccess;
-    spmm_panel_ptr_kernel<<<(unsigned)((m + 127) / 128), 128, 0, s>>>((int)m, base, row_ptr, col, plan.num_panels,
+    spmm_panel_ptr_kernel<I><<<(unsigned)((m + 127) / 128), 128, 0, s>>>((int)m, base, row_ptr, col, plan.num_panels,
                                                                     plan.panel_cols, static_cast<int*>(buf));
     return cudaGetLastError();
 }
 
-template <typename T>
-cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col,
-                 const T* val, const T* B, int64_t b_rs, int64_t b_cs, T* C, int64_t c_rs, int64_t c_cs,
+template <typename T, typename I>
+cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val, const T* B, int64_t b_rs, int64_t b_cs, T* C, int64_t c_rs, int64_t c_cs,
                  ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
     if (m == 0 || n == 0) return cudaSuccess;
     constexpr int W = VecOf<T>::W;
@@ -262,24 +263,31 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const int32_t* 
                         ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
     if (vec_ok) {
         const int64_t lanes = n / W;
-        if (lanes <= 2) return launch_rowmajor<T, 2>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        if (lanes <= 4) return launch_rowmajor<T, 4>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        if (lanes <= 8) return launch_rowmajor<T, 8>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 2) return launch_rowmajor<T, 2, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 4) return launch_rowmajor<T, 4, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 8) return launch_rowmajor<T, 8, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
         if (lanes <= 16)
-            return launch_rowmajor<T, 16>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        return launch_rowmajor<T, 32>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+            return launch_rowmajor<T, 16, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        return launch_rowmajor<T, 32, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
     }
     const long long total = m * n;
-    spmm_strided_kernel<T><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, s>>>(
+    spmm_strided_kernel<T, I><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, s>>>(
         m, n, base, row_ptr, col, val, B, b_rs, b_cs, C, c_rs, c_cs, alpha, beta);
     return cudaGetLastError();
 }
 
-template cudaError_t spmm<float>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, const float*,
-                                 const float*, int64_t, int64_t, float*, int64_t, int64_t, ScalarArg<float>,
-                                 ScalarArg<float>, int, const int*);
-template cudaError_t spmm<double>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
-                                  const double*, const double*, int64_t, int64_t, double*, int64_t, int64_t,
-                                  ScalarArg<double>, ScalarArg<double>, int, const int*);
+#define INSTANTIATE(T, I)                                                                                     \
+    template cudaError_t spmm<T, I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*, const T*, const T*, \
+                                    int64_t, int64_t, T*, int64_t, int64_t, ScalarArg<T>, ScalarArg<T>, int,   \
+                                    const int*);
+INSTANTIATE(float, int32_t)
+INSTANTIATE(double, int32_t)
+INSTANTIATE(float, int64_t)
+INSTANTIATE(double, int64_t)
+#undef INSTANTIATE
+template cudaError_t spmm_preprocess<int32_t>(cudaStream_t, int64_t, int, const int32_t*, const int32_t*,
+                                              const SpmmPlan&, void*);
+template cudaError_t spmm_preprocess<int64_t>(cudaStream_t, int64_t, int, const int64_t*, const int64_t*,
+                                              const SpmmPlan&, void*);
 
 }  // namespace mcsp_b200

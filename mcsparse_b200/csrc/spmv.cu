@@ -20,21 +20,20 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <typename T>
-struct TileCfg;
-template <>
-struct TileCfg<float> {
-    static constexpr int kLarge = MCSPARSE_B200_SPMV_TILE_ITEMS_F32 / kThreads;
-    static constexpr int kSmall = MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 / kThreads;
-};
-template <>
-struct TileCfg<double> {
-    static constexpr int kLarge = MCSPARSE_B200_SPMV_TILE_ITEMS_F64 / kThreads;
-    static constexpr int kSmall = MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 / kThreads;
+// Items per thread of the two tile sizes. With 64-bit column indices the staged columns take twice
+// the shared memory, so only the small tile is used.
+template <typename T, typename I>
+struct TileCfg {
+    static constexpr int kSmall =
+        (sizeof(T) == 8 ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32) / kThreads;
+    static constexpr int kLarge =
+        sizeof(I) == 8 ? kSmall
+                       : (sizeof(T) == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32) / kThreads;
 };
 
 // Column locality probe: 1024 threads x 4 samples.
-__global__ void locality_probe_kernel(long long nnz, const int* __restrict__ col, int* __restrict__ count) {
+template <typename I>
+__global__ void locality_probe_kernel(long long nnz, const I* __restrict__ col, int* __restrict__ count) {
     __shared__ int s_count;
     if (threadIdx.x == 0) s_count = 0;
     __syncthreads();
@@ -42,7 +41,7 @@ __global__ void locality_probe_kernel(long long nnz, const int* __restrict__ col
     for (int q = 0; q < 4; ++q) {
         const long long j = ((long long)(threadIdx.x * 4 + q) * (nnz - 1)) / 4096;
         if (j + 1 < nnz) {
-            const int d = __ldg(col + j + 1) - __ldg(col + j);
+            const long long d = (long long)__ldg(col + j + 1) - (long long)__ldg(col + j);
             local += (d <= 8 && d >= -8);
         }
     }
@@ -56,7 +55,8 @@ __global__ void locality_probe_kernel(long long nnz, const int* __restrict__ col
 // crosses the merge of row ends and nonzero indices. Same search, same tie-break (a row end
 // equal to a nonzero index is taken first) as the CPU partition it is checked against.
 // ---------------------------------------------------------------------------------------
-__global__ void merge_path_partition_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr,
+template <typename I>
+__global__ void merge_path_partition_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr,
                                             int items_per_tile, long long num_tiles, int2* __restrict__ starts,
                                             int* __restrict__ status) {
     long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -202,9 +202,9 @@ __device__ __forceinline__ void push_tile_rows(const PeerList<T>& peers, const T
 // before HBM does, so the kernel is organised to spend few L1 wavefronts per nonzero.
 // No atomics on the data path: every addition has a fixed place, so results are reproducible.
 // ---------------------------------------------------------------------------------------
-template <typename T, int THREADS, int IPT, bool PUSH>
+template <typename T, int THREADS, int IPT, bool PUSH, typename I>
 __global__ void __launch_bounds__(THREADS)
-    spmv_tile_kernel(int m, int nnz, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+    spmv_tile_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
                      T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset) {
@@ -213,9 +213,10 @@ __global__ void __launch_bounds__(THREADS)
     constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
                                    // stride-WALK shared reads of a warp fall in distinct banks
     constexpr int GV = 16 / (int)sizeof(T);  // values per 16 bytes
+    constexpr int GC = 16 / (int)sizeof(I);  // column indices per 16 bytes
 
     __shared__ __align__(128) T s_val[TILE + 16];   // values (then products); long-row path: row sums behind them
-    __shared__ __align__(128) int s_col[TILE + 16];  // column indices, then the tile's row ends behind them
+    __shared__ __align__(128) I s_col[TILE + 16];  // column indices, then the tile's row ends (int) behind them
     __shared__ __align__(8) unsigned long long s_mbar;
     __shared__ int s_warp_row[NWARPS];  // long-row path: last carry of each warp
     __shared__ T s_warp_sum[NWARPS];
@@ -236,17 +237,17 @@ __global__ void __launch_bounds__(THREADS)
 
     // Element nz_s + k of col is staged at s_col[head_c + k]; head_c is chosen so that the element
     // at index 0 of s_col sits on a 16-byte boundary in global memory. Likewise for val.
-    const int head_c = (int)((reinterpret_cast<uintptr_t>(col) >> 2) + (unsigned)nz_s) & 3;
+    const int head_c = (int)((reinterpret_cast<uintptr_t>(col) / sizeof(I)) + (unsigned)nz_s) & (GC - 1);
     const int head_v = (int)((reinterpret_cast<uintptr_t>(val) / sizeof(T)) + (unsigned)nz_s) & (GV - 1);
-    const int* const colv = s_col + head_c;  // colv[k], valv[k]: k-th nonzero of the tile
+    const I* const colv = s_col + head_c;  // colv[k], valv[k]: k-th nonzero of the tile
     T* const valv = s_val + head_v;
-    const int span_c = (head_c + nnz_tile + 3) & ~3;  // staged extent of s_col, in elements
-    int* const s_row_end = s_col + span_c;            // nrows + 1 entries; nrows + nnz_tile <= TILE
+    const int span_c = (head_c + nnz_tile + GC - 1) & ~(GC - 1);  // staged extent of s_col, in elements
+    int* const s_row_end = reinterpret_cast<int*>(s_col + span_c);  // nrows + 1 ints; nrows + nnz_tile <= TILE
 
     // ---- phase 1: bulk copies of the 16-byte aligned part that lies inside the arrays
     int lo_c = nz_s - head_c, hi_c = lo_c + span_c;  // global element range of the col copy
-    if (lo_c < 0) lo_c += 4;
-    if (hi_c > nnz) hi_c -= 4;
+    if (lo_c < 0) lo_c += GC;
+    if (hi_c > nnz) hi_c -= GC;
     int lo_v = nz_s - head_v, hi_v = lo_v + ((head_v + nnz_tile + GV - 1) & ~(GV - 1));
     if (lo_v < 0) lo_v += GV;
     if (hi_v > nnz) hi_v -= GV;
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
     if (tid == 0 && (copy_c || copy_v)) {
         const unsigned long long policy = l2_evict_first_policy();
-        const uint32_t bytes_c = copy_c ? (uint32_t)(hi_c - lo_c) * 4u : 0u;
+        const uint32_t bytes_c = copy_c ? (uint32_t)(hi_c - lo_c) * (uint32_t)sizeof(I) : 0u;
         const uint32_t bytes_v = copy_v ? (uint32_t)(hi_v - lo_v) * (uint32_t)sizeof(T) : 0u;
         mbar_expect_tx(&s_mbar, bytes_c + bytes_v);
         if (copy_c) bulk_copy_g2s(s_col + (lo_c - (nz_s - head_c)), col + lo_c, bytes_c, &s_mbar, policy);
@@ -286,9 +287,9 @@ __global__ void __launch_bounds__(THREADS)
     int maxlen = 0;
     for (int i = tid; i <= nrows; i += THREADS) {
         const int r = row_s + i;
-        int e = (r < m) ? __ldg(row_ptr + r + 1) - base : nz_e;
+        int e = (r < m) ? (int)__ldg(row_ptr + r + 1) - base : nz_e;
         e = min(e, nz_e);
-        const int b = (r < m) ? max(__ldg(row_ptr + r) - base, nz_s) : nz_e;
+        const int b = (r < m) ? max((int)__ldg(row_ptr + r) - base, nz_s) : nz_e;
         maxlen = max(maxlen, e - b);
         s_row_end[i] = e - nz_s;
     }
@@ -539,9 +540,9 @@ __global__ void spmv_carry_fixup_range_kernel(long long t0, long long t1, const 
 // loads, xor-shuffle reduction. Needs no analysis and no work buffer: the kernel behind the
 // legacy csrmv calls, which have neither.
 // ---------------------------------------------------------------------------------------
-template <typename T, int G>
+template <typename T, int G, typename I>
 __global__ void __launch_bounds__(kThreads)
-    spmv_rowgroup_kernel(int m, int base, const int* __restrict__ row_ptr, const int* __restrict__ col,
+    spmv_rowgroup_kernel(int m, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                          const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y,
                          ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg) {
     const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / G;
@@ -549,7 +550,7 @@ __global__ void __launch_bounds__(kThreads)
     const bool active = gid < m;
     T sum = T(0);
     if (active) {
-        const int j0 = __ldg(row_ptr + gid) - base, j1 = __ldg(row_ptr + gid + 1) - base;
+        const int j0 = (int)__ldg(row_ptr + gid) - base, j1 = (int)__ldg(row_ptr + gid + 1) - base;
         const T* xb = x - base;
         for (int j = j0 + lane; j < j1; j += G) sum = mad(__ldcs(val + j), __ldg(xb + __ldcs(col + j)), sum);
     }
@@ -581,29 +582,32 @@ static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int 
     return ws;
 }
 
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles) {
-    const int large = value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles, size_t index_size) {
     const int small = value_size == 8 ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32;
+    const int large = index_size == 8 ? small  // 64-bit indices: one tile size (see TileCfg)
+                      : value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64
+                                        : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
     SpmvWorkspace ws = spmv_layout(m, nnz, value_size, small_tiles ? small : large);
     ws.bytes = spmv_layout(m, nnz, value_size, small).bytes;
     return ws;
 }
 
-cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const int32_t* col, int* device_count,
-                                int* host_count) {
-    locality_probe_kernel<<<1, 1024, 0, s>>>(nnz, col, device_count);
+template <typename I>
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const I* col, int* device_count, int* host_count) {
+    locality_probe_kernel<I><<<1, 1024, 0, s>>>(nnz, col, device_count);
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_count, device_count, sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return e;
 }
 
-cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
-                          const SpmvWorkspace& ws, void* buf) {
+template <typename I>
+cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const SpmvWorkspace& ws,
+                          void* buf) {
     const long long n = ws.num_tiles + 1;
     const int threads = 128;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
-    merge_path_partition_kernel<<<blocks, threads, 0, s>>>(
+    merge_path_partition_kernel<I><<<blocks, threads, 0, s>>>(
         (int)m, (int)nnz, base, row_ptr, ws.items_per_tile, ws.num_tiles, reinterpret_cast<int2*>(buf),
         reinterpret_cast<int*>(static_cast<char*>(buf) + ws.off_status));
     return cudaGetLastError();
@@ -620,9 +624,9 @@ static size_t tuning_pad_smem() {
 }
 
 // One launch of the tile kernel over tiles [tile0, tile0 + count), for the tile size of `ws`.
-template <typename T, bool PUSH>
+template <typename T, bool PUSH, typename I>
 static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, int64_t m, int64_t nnz, int base,
-                                const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
+                                const I* row_ptr, const I* col, const T* val, const T* x, T* y,
                                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
                                 const PeerList<T>& peers) {
     char* base_ptr = static_cast<char*>(buf);
@@ -630,30 +634,30 @@ static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, in
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
-    if (ws.items_per_tile == kThreads * TileCfg<T>::kLarge)
-        spmv_tile_kernel<T, kThreads, TileCfg<T>::kLarge, PUSH><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
+    if (ws.items_per_tile == kThreads * TileCfg<T, I>::kLarge)
+        spmv_tile_kernel<T, kThreads, TileCfg<T, I>::kLarge, PUSH, I><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
             (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
             (int)tile0);
     else
-        spmv_tile_kernel<T, kThreads, TileCfg<T>::kSmall, PUSH><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
+        spmv_tile_kernel<T, kThreads, TileCfg<T, I>::kSmall, PUSH, I><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
             (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
             (int)tile0);
     return cudaGetLastError();
 }
 
-template <typename T>
-cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
-                       const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta,
-                       const SpmvWorkspace& ws, void* buf, const PeerList<T>& peers) {
+template <typename T, typename I>
+cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col, const T* val,
+                       const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
+                       const PeerList<T>& peers) {
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
-    cudaError_t e = peers.count > 0 ? launch_tiles<T, true>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y,
-                                                           alpha, beta, ws, buf, peers)
-                                    : launch_tiles<T, false>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y,
-                                                            alpha, beta, ws, buf, peers);
+    cudaError_t e = peers.count > 0 ? launch_tiles<T, true, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x,
+                                                              y, alpha, beta, ws, buf, peers)
+                                    : launch_tiles<T, false, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x,
+                                                               y, alpha, beta, ws, buf, peers);
     if (e != cudaSuccess) return e;
     if (peers.count > 0)
         spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
@@ -706,7 +710,8 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
     for (int c = 0; c < chunks && e == cudaSuccess; ++c) {
         const int64_t t0 = chunk_tiles[c], t1 = chunk_tiles[c + 1];
         if (t1 > t0)
-            e = launch_tiles<T, false>(s, t0, t1 - t0, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws, buf, none);
+            e = launch_tiles<T, false, int32_t>(s, t0, t1 - t0, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws, buf,
+                                                none);
         if (e == cudaSuccess) e = cudaEventRecord(events[c], s);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(side, events[c], 0);
         if (e == cudaSuccess && t1 > t0) {
@@ -744,7 +749,7 @@ static cudaError_t launch_rowgroup(cudaStream_t s, int64_t m, int base, const in
                                    const T* val, const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta) {
     const long long threads_total = m * G;
     const unsigned grid = (unsigned)((threads_total + kThreads - 1) / kThreads);
-    spmv_rowgroup_kernel<T, G><<<grid, kThreads, 0, s>>>((int)m, base, row_ptr, col, val, x, y, alpha, beta);
+    spmv_rowgroup_kernel<T, G, int32_t><<<grid, kThreads, 0, s>>>((int)m, base, row_ptr, col, val, x, y, alpha, beta);
     return cudaGetLastError();
 }
 
@@ -792,10 +797,13 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
     return cudaSuccess;
 }
 
+#define INSTANTIATE_TI(T, I)                                                                                  \
+    template cudaError_t spmv_tiled<T, I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*, const T*,    \
+                                          const T*, T*, ScalarArg<T>, ScalarArg<T>, const SpmvWorkspace&,      \
+                                          void*, const PeerList<T>&);
 #define INSTANTIATE(T)                                                                                         \
-    template cudaError_t spmv_tiled<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,    \
-                                       const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>,                     \
-                                       const SpmvWorkspace&, void*, const PeerList<T>&);                       \
+    INSTANTIATE_TI(T, int32_t)                                                                                 \
+    INSTANTIATE_TI(T, int64_t)                                                                                 \
     template cudaError_t spmv_rowgroup<T>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*, \
                                           const T*, const T*, T*, ScalarArg<T>, ScalarArg<T>);                 \
     template cudaError_t spmv_tiled_pipelined<T>(cudaStream_t, cudaStream_t, cudaEvent_t*, int, const int64_t*, \
@@ -804,6 +812,13 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
                                                  ScalarArg<T>, const SpmvWorkspace&, void*, const PeerList<T>&);
 INSTANTIATE(float)
 INSTANTIATE(double)
+template cudaError_t spmv_analysis<int32_t>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const SpmvWorkspace&,
+                                            void*);
+template cudaError_t spmv_analysis<int64_t>(cudaStream_t, int64_t, int64_t, int, const int64_t*, const SpmvWorkspace&,
+                                            void*);
+template cudaError_t spmv_locality_probe<int32_t>(cudaStream_t, int64_t, const int32_t*, int*, int*);
+template cudaError_t spmv_locality_probe<int64_t>(cudaStream_t, int64_t, const int64_t*, int*, int*);
 #undef INSTANTIATE
+#undef INSTANTIATE_TI
 
 }  // namespace mcsp_b200

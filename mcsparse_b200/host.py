@@ -62,13 +62,15 @@ class CsrMatrix:
     """mcsparseSpMatDescr_t over three device tensors (borrowed by the C side, owned here)."""
 
     def __init__(self, rows, cols, row_offsets, col_ind, values, base=0):
-        assert row_offsets.dtype == torch.int32 and col_ind.dtype == torch.int32
+        # Index types come in matched pairs: both 32-bit or both 64-bit.
+        assert row_offsets.dtype == col_ind.dtype and row_offsets.dtype in (torch.int32, torch.int64)
+        index_type = capi.MCSPARSE_INDEX_64I if row_offsets.dtype == torch.int64 else capi.MCSPARSE_INDEX_32I
         self.rows, self.cols, self.base = int(rows), int(cols), int(base)
         self.nnz = int(col_ind.numel())
         self.row_offsets, self.col_ind, self.values = row_offsets, col_ind, values
         d = C.c_void_p()
         check(lib.mcsparseCreateCsr(C.byref(d), self.rows, self.cols, self.nnz, _ptr(row_offsets), _ptr(col_ind),
-                                    _ptr(values), capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, self.base,
+                                    _ptr(values), index_type, index_type, self.base,
                                     _DTYPE[values.dtype]), "mcsparseCreateCsr")
         self.d = d
 

@@ -73,6 +73,33 @@ def test_spmm_other_layouts(handle, device, dtype, order_b, order_c):
     assert_close(got, ref, d, TOL[np.dtype(dtype)], "layouts")
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n,order", [(64, ROW), (12, ROW), (5, COL)])
+def test_spmm_64bit_indices(handle, device, dtype, n, order):
+    """MCSPARSE_INDEX_64I row offsets and column indices give the 32-bit result bit for bit."""
+    lengths = ADVERSARIAL_LENGTHS["lengths_1_to_33"] + ADVERSARIAL_LENGTHS["empty_start_mid_end"] + [300]
+    k, m, base = 400, None, 1
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=9, base=base)
+    m = len(lengths)
+    rng = np.random.default_rng(9)
+    ldb = n if order == ROW else k
+    ldc = n if order == ROW else m
+    B, C0 = dense(rng, k, n, ldb, order, dtype), dense(rng, m, n, ldc, order, dtype)
+    out = []
+    for idx in (np.int32, np.int64):
+        t = [torch.from_numpy(a).to(device) for a in (rp.astype(idx), col.astype(idx), val, B, C0.copy())]
+        A = mc.CsrMatrix(m, k, t[0], t[1], t[2], base=base)
+        Bm, Cm = mc.DnMat(t[3], k, n, ldb, order), mc.DnMat(t[4], m, n, ldc, order)
+        buf = torch.empty(256, dtype=torch.uint8, device=device)
+        mc.spmm(handle, A, Bm, Cm, buf, alpha=0.75, beta=-0.5)
+        torch.cuda.synchronize()
+        out.append(t[4].cpu().numpy())
+    np.testing.assert_array_equal(out[0], out[1])
+    ref, d = oracle.spmm(rp, col, val, B, ldb, order, n, 0.75, -0.5, C0, ldc, order, base=base)
+    got = out[1].reshape(m, ldc) if order == ROW else out[1].reshape(n, ldc).T
+    assert_close(got, ref, d, TOL[np.dtype(dtype)], f"64-bit indices, n={n}")
+
+
 def test_spmm_op_b_transpose(handle, device):
     """op(B) = B^T with B stored n x k column-major is the same memory as k x n row-major."""
     dtype = np.float32

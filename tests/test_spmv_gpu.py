@@ -17,9 +17,12 @@ DT = {np.float32: torch.float32, np.float64: torch.float64}
 MACA = {np.float32: capi.MACA_R_32F, np.float64: capi.MACA_R_64F}
 
 
-def run_spmv(handle, device, rp, col, val, x, y0, alpha, beta, base=0, preprocess=False, offset_elems=0):
+def run_spmv(handle, device, rp, col, val, x, y0, alpha, beta, base=0, preprocess=False, offset_elems=0,
+             index_dtype=np.int32):
     """Uploads, runs mcsparseSpMV, returns (y, buffer, descriptor holder). offset_elems > 0 puts col/val at a
-    misaligned address to reach the scalar-load variant."""
+    misaligned address to reach the scalar-load variant; index_dtype=np.int64 passes 64-bit indices."""
+    rp, col = rp.astype(index_dtype), col.astype(index_dtype)
+
     def up(a, off=0):
         t = torch.empty(a.size + off + 1, dtype=torch.from_numpy(a[:0]).dtype, device=device)
         t[off:off + a.size] = torch.from_numpy(a).to(device)
@@ -105,6 +108,55 @@ def test_spmv_unaligned_arrays(handle, device, dtype, offset):
     y, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 1.0, 1.0, offset_elems=offset)
     ref, d = oracle.spmv(rp, col, val, x, 1.0, 1.0, y0)
     assert_close(y, ref, d, TOL[np.dtype(dtype)], f"offset {offset}")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("offset", [0, 1])
+@pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
+def test_spmv_64bit_indices(handle, device, name, dtype, base, offset, monkeypatch):
+    """MCSPARSE_INDEX_64I row offsets and column indices: same result, bit for bit, as the 32-bit
+    run with the same (small) tile size, and the same work partition."""
+    lengths = ADVERSARIAL_LENGTHS[name]
+    ncols = max(max(lengths), 1) + 17
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=13, base=base)
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, ncols).astype(dtype)
+    y0 = rng.uniform(-1, 1, len(lengths)).astype(dtype)
+    y64, buf, keep = run_spmv(handle, device, rp, col, val, x, y0, 0.5, 1.5, base, offset_elems=offset,
+                              index_dtype=np.int64)
+    ref, d = oracle.spmv(rp, col, val, x, 0.5, 1.5, y0, base=base)
+    assert_close(y64, ref, d, TOL[np.dtype(dtype)], name)
+    items, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
+    capi.check(lib.mcsparseB200SpMVPartitionView(keep[0].d, C.c_void_p(buf.data_ptr()), C.byref(items), C.byref(nt),
+                                                 C.byref(p)))
+    small = capi.SPMV_TILE_ITEMS[MACA[dtype]][1]
+    assert items.value == small
+    part = oracle.merge_path_partition(rp, col.size, small, base)
+    off = p.value - buf.data_ptr()
+    got = buf[off:off + part.size * 4].view(torch.int32).cpu().numpy().reshape(-1, 2)
+    np.testing.assert_array_equal(got, part)
+    monkeypatch.setenv("MCSPARSE_B200_SPMV_TILE", "small")
+    y32, _, _ = run_spmv(handle, device, rp, col, val, x, y0, 0.5, 1.5, base, offset_elems=offset)
+    np.testing.assert_array_equal(y64, y32)
+
+
+def test_spmv_64bit_indices_scaled_config(handle, device):
+    cfg = workloads.scaled("C3", 64)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr.long(), w.col.long(), w.val)
+    y = w.y0.clone()
+    X, Y = mc.DnVec(w.x), mc.DnVec(y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+    mc.spmv_preprocess(handle, A, X, Y, buf)
+    mc.spmv(handle, A, X, Y, buf, alpha=w.alpha, beta=w.beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(w.row_ptr, w.col, w.val, w.x, w.alpha, w.beta, w.y0)
+    assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], "C3 with 64-bit indices")
+    # Mixed widths, 64-bit COO and the entry points that stay 32-bit only are refused, not misread.
+    st = lib.mcsparseB200SpMVNoAlloc(handle.h, 0, C.byref(C.c_float(1)), A.d, X.d, C.byref(C.c_float(0)), Y.d,
+                                     capi.MACA_R_32F, 0)
+    assert st == capi.MCSPARSE_STATUS_NOT_SUPPORTED
 
 
 @pytest.mark.parametrize("name,factor", [("C1", 16), ("C2", 64), ("C3", 64), ("C5", 64)])
