@@ -18,6 +18,7 @@ from .host import (  # noqa: F401
     DnMat,
     DnVec,
     Handle,
+    HostSpmvPipeline,
     spmm,
     spmm_buffer_size,
     spmm_preprocess,
@@ -28,5 +29,6 @@ from .host import (  # noqa: F401
 
 __all__ = [
     "capi", "lib", "load_library", "check", "McsparseError", "Handle", "CsrMatrix", "DnVec", "DnMat",
+    "HostSpmvPipeline",
     "spmv", "spmv_buffer_size", "spmv_preprocess", "spmm", "spmm_buffer_size", "spmm_preprocess",
 ]

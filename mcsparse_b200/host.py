@@ -172,3 +172,86 @@ def spmm(handle, A, B, Cmat, buffer, alpha=1.0, beta=0.0, op_b=capi.MCSPARSE_OPE
     check(lib.mcsparseSpMM(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, op_b, pa, A.d, B.d, pb, Cmat.d,
                            _DTYPE[A.dtype], capi.MCSPARSE_SPMM_ALG_DEFAULT, _ptr(buffer)), "mcsparseSpMM")
     del keep
+
+
+class HostSpmvPipeline:
+    """y_host = alpha * A @ x_host + beta * y_host for vectors that live in pinned host memory.
+
+    The matrix stays resident on the GPU. Each `submit` runs on one of `depth` slots (own stream,
+    own device x / y, own work buffer and matrix descriptor over the same three arrays), so the
+    host-to-device copy of one product overlaps the device-to-host copy of the previous one: the
+    two directions use different copy engines. Products submitted back to back must therefore be
+    independent of one another; `wait()` returns when all submitted results are in host memory.
+
+    With `shard=(row_offset, total_rows, group)` the matrix is this rank's row block of a
+    row-sharded matrix (see sharding.ShardedSpmv): every slot then owns a peer-visible y, the
+    kernel pushes finished rows to the other GPUs, and `y_host` receives this rank's rows.
+    """
+
+    def __init__(self, handle, rows, cols, row_offsets, col_ind, values, base=0, depth=2, shard=None):
+        self.h, self.depth, self.dtype = handle, int(depth), values.dtype
+        self.main = handle.stream
+        device = values.device
+        self.slots = []
+        self.submitted = 0
+        for _ in range(self.depth):
+            s = {"stream": torch.cuda.Stream(device=device), "done": torch.cuda.Event(),
+                 "A": CsrMatrix(rows, cols, row_offsets, col_ind, values, base=base),
+                 "x": torch.zeros(cols, dtype=values.dtype, device=device)}
+            if shard is None:
+                s["y"] = torch.zeros(rows, dtype=values.dtype, device=device)
+                s["X"], s["Y"] = DnVec(s["x"]), DnVec(s["y"])
+                s["buf"] = torch.empty(spmv_buffer_size(handle, s["A"], s["X"], s["Y"]), dtype=torch.uint8,
+                                       device=device)
+                spmv_preprocess(handle, s["A"], s["X"], s["Y"], s["buf"])
+                s["sharded"] = None
+            else:
+                from . import sharding
+
+                row_offset, total_rows, group = shard
+                s["sharded"] = sharding.ShardedSpmv(handle, s["A"], s["x"], row_offset, total_rows, group)
+                s["y"] = s["sharded"].y_local
+            self.slots.append(s)
+        torch.cuda.synchronize(device)
+
+    def submit(self, x_host, y_host, alpha=1.0, beta=0.0):
+        """Queues one product; returns at once. x_host / y_host must stay untouched until wait()."""
+        s = self.slots[self.submitted % self.depth]
+        self.submitted += 1
+        with torch.cuda.stream(s["stream"]):
+            s["x"].copy_(x_host, non_blocking=True)
+            if beta != 0:
+                s["y"].copy_(y_host, non_blocking=True)
+            self.h.set_stream(s["stream"])
+            try:
+                if s["sharded"] is None:
+                    spmv(self.h, s["A"], s["X"], s["Y"], s["buf"], alpha=alpha, beta=beta)
+                else:
+                    s["sharded"].step(alpha, beta)
+            finally:
+                self.h.set_stream(self.main)
+            y_host.copy_(s["y"], non_blocking=True)
+            s["done"].record(s["stream"])
+
+    def start_after(self, stream):
+        """Makes every slot's stream wait for the work queued so far on `stream`."""
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        for s in self.slots:
+            s["stream"].wait_event(ev)
+
+    def join(self, stream):
+        """Makes `stream` wait for every product submitted so far (no host synchronisation)."""
+        for s in self.slots:
+            stream.wait_event(s["done"])
+
+    def wait(self):
+        for s in self.slots:
+            s["done"].synchronize()
+
+    def close(self):
+        self.wait()
+        for s in self.slots:
+            if s["sharded"] is not None:
+                s["sharded"].close()
+        self.slots = []

@@ -343,3 +343,25 @@ def test_spmv_coo_input(handle, device, name, dtype, base):
     # the entry points without a COO path refuse it
     assert lib.mcsparseB200SpMVNoAlloc(handle.h, 0, pa, d, X.d, pb, Y.d, MACA[dtype], 0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
     lib.mcsparseDestroySpMat(d)
+
+
+@pytest.mark.parametrize("beta", [0.0, 0.5])
+def test_host_pipeline_matches_oracle(handle, device, beta):
+    """HostSpmvPipeline: five products with different host vectors through two slots."""
+    dtype = np.float64
+    lengths = ADVERSARIAL_LENGTHS["tile_straddle"] + ADVERSARIAL_LENGTHS["lengths_1_to_33"]
+    ncols = 5000
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=21)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val)]
+    pipe = mc.HostSpmvPipeline(handle, len(lengths), ncols, t[0], t[1], t[2], depth=2)
+    rng = np.random.default_rng(8)
+    xs = [torch.from_numpy(rng.uniform(-1, 1, ncols)).pin_memory() for _ in range(5)]
+    y0 = [rng.uniform(-1, 1, len(lengths)) for _ in range(5)]
+    ys = [torch.from_numpy(v.copy()).pin_memory() for v in y0]
+    for x, y in zip(xs, ys):
+        pipe.submit(x, y, alpha=2.0, beta=beta)
+    pipe.wait()
+    for x, y, v in zip(xs, ys, y0):
+        ref, d = oracle.spmv(rp, col, val, x.numpy(), 2.0, beta, v)
+        assert_close(y.numpy(), ref, d, TOL[np.dtype(dtype)], "host pipeline")
+    pipe.close()
