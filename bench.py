@@ -381,64 +381,61 @@ def run_gpu(args, rank, world, local_rank):
     ms_per_step = total_ms / args.steps
     value = job.bytes / (ms_per_step * 1e-3) / 1e9
 
-    # end to end: x from pinned host memory every step, y back to pinned host memory. Measured twice:
-    # one product at a time on the compute stream (latency), and through HostSpmvPipeline, which keeps
-    # two independent products in flight so that one product's upload overlaps the previous download
-    # (throughput; this is the e2e value, the metric being a throughput).
+    # end to end: x from pinned host memory every step, y back to pinned host memory, through
+    # HostSpmvPipeline. Measured twice: one product at a time (depth 1: latency), and with several
+    # independent products in flight so that one product's upload overlaps the previous download
+    # (throughput; this is the e2e value, the metric being a throughput). At N > 1 every rank uploads
+    # its 1/N slice of x and the GPUs all-gather the slices; every rank downloads its rows of y.
+    y_device = job.y.cpu()  # result of the device-resident steps above (same x, beta == 0: same y)
     x_host = job.w.x.cpu().pin_memory()
-    y_host = torch.empty(job.y.numel(), dtype=job.cfg.dtype).pin_memory()
-    if job.cfg.beta != 0:
-        y_host.copy_(job.w.y0)
-
-    def e2e_step():
-        job.w.x.copy_(x_host, non_blocking=True)
-        if job.cfg.beta != 0:
-            job.y.copy_(y_host, non_blocking=True)
-        job.step()
-        y_host.copy_(job.y, non_blocking=True)
-
     e2e_steps = 4 if args.quick else max(6, min(args.steps, 50))
-    serial_total, _ = time_steps(torch, e2e_step, e2e_steps, 3, None, barrier)
-    y_serial = y_host.clone()
-
-    depth = args.e2e_depth
-    shard = None if world == 1 else (job.bounds[rank], job.cfg.rows, None)
-    pipe = mc.HostSpmvPipeline(h, job.w.rows, job.w.cols, job.w.row_ptr, job.w.col, job.w.val, depth=depth, shard=shard)
-    xs = [x_host] + [x_host.clone().pin_memory() for _ in range(depth - 1)]
-    ys = [torch.empty_like(y_host).pin_memory() for _ in range(depth)]
-    if job.cfg.beta != 0:
-        for y in ys:
-            y.copy_(job.w.y0)
     main = torch.cuda.current_stream()
+    shard = None if world == 1 else (job.bounds[rank], job.cfg.rows, None)
 
-    def run_pipe(count):
-        pipe.start_after(main)
-        for i in range(count):
-            pipe.submit(xs[i % depth], ys[i % depth], job.cfg.alpha, job.cfg.beta)
-        pipe.join(main)
+    def time_pipeline(depth):
+        pipe = mc.HostSpmvPipeline(h, job.w.rows, job.w.cols, job.w.row_ptr, job.w.col, job.w.val, depth=depth,
+                                   shard=shard)
+        xs = [x_host] + [x_host.clone().pin_memory() for _ in range(depth - 1)]
+        ys = [torch.empty(job.y.numel(), dtype=job.cfg.dtype).pin_memory() for _ in range(depth)]
+        if job.cfg.beta != 0:
+            for y in ys:
+                y.copy_(job.w.y0)
 
-    run_pipe(depth)  # warm-up
-    torch.cuda.synchronize()
-    pipe_ok = bool(torch.equal(ys[0], y_serial)) if job.cfg.beta == 0 else None
-    run_pipe(depth)
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
+        def run(count):
+            pipe.start_after(main)
+            for i in range(count):
+                pipe.submit(xs[i % depth], ys[i % depth], job.cfg.alpha, job.cfg.beta)
+                if depth == 1:
+                    pipe.wait()  # one product at a time: the host has y before it sends the next x
+            pipe.join(main)
+
+        run(max(3, depth))  # warm-up
         torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    run_pipe(e2e_steps)
-    t1.record()
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
+        same = bool(torch.equal(ys[0], y_device)) if job.cfg.beta == 0 else None
+        if barrier:
+            barrier()
+            torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        run(e2e_steps)
+        t1.record()
         torch.cuda.synchronize()
-    t = torch.tensor([t0.elapsed_time(t1), serial_total], dtype=torch.float64, device=device)
+        if barrier:
+            barrier()
+            torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1)
+        pipe.close()
+        return ms, same
+
+    depth = max(2, args.e2e_depth)
+    serial_total, serial_same = time_pipeline(1)
+    piped_total, piped_same = time_pipeline(depth)
+    pipe_ok = None if piped_same is None else (piped_same and serial_same)
+    t = torch.tensor([piped_total, serial_total], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms, e2e_serial_ms = (v / e2e_steps for v in t.tolist())
-    pipe.close()
-    del pipe
+    x_up = x_host.numel() + (job.cfg.rows if job.cfg.beta != 0 else 0)  # elements uploaded per step, all ranks
 
     if rank == 0:
         local_gbs = job.local_bytes / (compute_ms * 1e-3) / 1e9
@@ -463,13 +460,13 @@ def run_gpu(args, rank, world, local_rank):
                          "frac_of_nominal_8tbs": round(local_gbs / 8000.0, 4),
                          "kernel": "spmv_tile_kernel (+ carry fix-up) per rank", "ms": round(compute_ms, 5)},
             "e2e": {"value": round(job.bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": UNIT,
-                    "h2d_bytes_per_step": (x_host.numel() + (y_host.numel() if job.cfg.beta != 0 else 0)) * job.vsize, "d2h_bytes_per_step": y_host.numel() * job.vsize,
+                    "h2d_bytes_per_step": x_up * job.vsize, "d2h_bytes_per_step": job.cfg.rows * job.vsize,
                     "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
                     "mode": f"{depth} independent products in flight (HostSpmvPipeline): upload of one overlaps "
-                            "download of the previous",
+                            "download of the previous; bytes are totals over all ranks",
                     "serial_ms_per_step": round(e2e_serial_ms, 4),
                     "serial_value": round(job.bytes / (e2e_serial_ms * 1e-3) / 1e9, 1),
-                    "pipelined_equals_serial_bitwise": pipe_ok},
+                    "equals_device_resident_result_bitwise": pipe_ok},
             "gpu_launches": job.launches_per_step * args.steps,
             "multi_gpu": None if world == 1 else {
                 "kernel_only_ms": round(compute_ms, 5), "push_kernels_ms": round(push_ms, 5),

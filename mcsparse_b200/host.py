@@ -185,7 +185,10 @@ class HostSpmvPipeline:
 
     With `shard=(row_offset, total_rows, group)` the matrix is this rank's row block of a
     row-sharded matrix (see sharding.ShardedSpmv): every slot then owns a peer-visible y, the
-    kernel pushes finished rows to the other GPUs, and `y_host` receives this rank's rows.
+    kernel pushes finished rows to the other GPUs, and `y_host` receives this rank's rows. Each
+    rank uploads only its 1/world slice of `x_host` (every rank is given the same full-length
+    vector); the slices are exchanged between the GPUs by an all-gather, so the bytes crossing
+    PCIe per product do not grow with the number of GPUs.
     """
 
     def __init__(self, handle, rows, cols, row_offsets, col_ind, values, base=0, depth=2, shard=None):
@@ -208,9 +211,16 @@ class HostSpmvPipeline:
             else:
                 from . import sharding
 
+                import torch.distributed as dist
+
                 row_offset, total_rows, group = shard
                 s["sharded"] = sharding.ShardedSpmv(handle, s["A"], s["x"], row_offset, total_rows, group)
                 s["y"] = s["sharded"].y_local
+                world, rank = dist.get_world_size(group), dist.get_rank(group)
+                cut = [cols * g // world for g in range(world + 1)]
+                s["x_parts"] = [s["x"][cut[g]:cut[g + 1]] for g in range(world)]
+                s["x_slice"] = slice(cut[rank], cut[rank + 1])
+                s["group"] = group
             self.slots.append(s)
         torch.cuda.synchronize(device)
 
@@ -219,7 +229,14 @@ class HostSpmvPipeline:
         s = self.slots[self.submitted % self.depth]
         self.submitted += 1
         with torch.cuda.stream(s["stream"]):
-            s["x"].copy_(x_host, non_blocking=True)
+            if s["sharded"] is None:
+                s["x"].copy_(x_host, non_blocking=True)
+            else:
+                from . import sharding
+
+                mine = s["x_slice"]
+                s["x"][mine].copy_(x_host[mine], non_blocking=True)
+                sharding.all_gather_ragged(s["x_parts"], s["x"][mine], s["group"])
             if beta != 0:
                 s["y"].copy_(y_host, non_blocking=True)
             self.h.set_stream(s["stream"])
