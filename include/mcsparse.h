@@ -6,8 +6,9 @@
  * changes. Each group cites the reference declaration it replaces (path inside the
  * mcSparse source tree : line).
  *
- * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO as an input of
- * mcsparseSpMV), MCSPARSE_OPERATION_NON_TRANSPOSE,
+ * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO or MCSPARSE_FORMAT_CSC
+ * as an input of mcsparseSpMV), MCSPARSE_OPERATION_NON_TRANSPOSE (mcsparseSpMV: also
+ * MCSPARSE_OPERATION_TRANSPOSE, through a conversion into the external buffer),
  * MACA_R_32F / MACA_R_64F, offsets and columns both MCSPARSE_INDEX_32I or (CSR only) both
  * MCSPARSE_INDEX_64I with extents below 2^31, index base 0 or 1.
  * Everything else that the reference accepts on these entry points returns
@@ -240,6 +241,17 @@ mcsparseStatus_t mcsparseCooGet(mcsparseSpMatDescr_t spMatDescr, int64_t* rows, 
                                 mcsparseIndexBase_t* idxBase, macaDataType* valueType);
 mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t spMatDescr, void* cooRows, void* cooColumns,
                                         void* cooValues);
+
+/* ---- CSC sparse matrix descriptor, accepted by mcsparseSpMV (32-bit indices).
+ *      Reference: mcsp_helper.h.in:69-72, mcsparse/src/common/mcsp_helper.cpp:447-452,607-615.
+ *      The CSC arrays are the CSR arrays of the transposed matrix: op(A) = A^T on a CSC matrix runs the CSR
+ *      kernels directly, op(A) = A goes through the same conversion as op(A) = A^T on a CSR matrix. ---- */
+mcsparseStatus_t mcsparseCreateCsc(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                   void* cscColOffsets, void* cscRowInd, void* cscValues,
+                                   mcsparseIndexType_t cscColOffsetsType, mcsparseIndexType_t cscRowIndType,
+                                   mcsparseIndexBase_t idxBase, macaDataType valueType);
+mcsparseStatus_t mcsparseCscSetPointers(mcsparseSpMatDescr_t spMatDescr, void* cscColOffsets, void* cscRowInd,
+                                        void* cscValues);
 
 /* ---- Dense matrix descriptor. Reference: mcsp_helper.h.in:92-98, mcsp_helper.cpp:715-795. ---- */
 mcsparseStatus_t mcsparseCreateDnMat(mcsparseDnMatDescr_t* dnMatDescr, int64_t rows, int64_t cols, int64_t ld,

@@ -47,6 +47,17 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
                                                const int32_t** tileStarts);
 
 /*
+ * View of the converted matrix that a transposed product (op(A) = A^T on CSR, op(A) = A on CSC)
+ * left in externalBuffer: the CSR arrays of the transposed matrix, 0-based, `rows` row offsets + 1
+ * entries, nonzeros of a row in the order of the source (stable), values as of the last product.
+ * Used to check the device conversion bit for bit against a CPU one. Returns INVALID_VALUE when
+ * (matA, opA) is not a transposed product. No reference counterpart.
+ */
+mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcsparseOperation_t opA,
+                                                void* externalBuffer, int64_t* rows, const int32_t** rowOffsets,
+                                                const int32_t** colInd, const void** values);
+
+/*
  * Device-side status of the SpMV calls that used externalBuffer since its last analysis: 0, or 1
  * if a thread block gave up its bounded wait (about a second of SM clocks) for the bulk copies
  * of its tile and left its rows unwritten. Synchronises the handle's stream. The reference has

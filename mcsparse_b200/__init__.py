@@ -14,6 +14,7 @@ from .capi import (  # noqa: F401
     load_library,
 )
 from .host import (  # noqa: F401
+    CscMatrix,
     CsrMatrix,
     DnMat,
     DnVec,
@@ -28,7 +29,7 @@ from .host import (  # noqa: F401
 )
 
 __all__ = [
-    "capi", "lib", "load_library", "check", "McsparseError", "Handle", "CsrMatrix", "DnVec", "DnMat",
+    "capi", "lib", "load_library", "check", "McsparseError", "Handle", "CsrMatrix", "CscMatrix", "DnVec", "DnMat",
     "HostSpmvPipeline",
     "spmv", "spmv_buffer_size", "spmv_preprocess", "spmm", "spmm_buffer_size", "spmm_preprocess",
 ]

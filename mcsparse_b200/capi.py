@@ -87,6 +87,8 @@ PROTOTYPES = {
     "mcsparseCreateCoo": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i]),
     "mcsparseCooGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pvp, _pvp, _pi, _pi, _pi]),
     "mcsparseCooSetPointers": (_i, [_vp, _vp, _vp, _vp]),
+    "mcsparseCreateCsc": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "mcsparseCscSetPointers": (_i, [_vp, _vp, _vp, _vp]),
     "mcsparseDestroySpMat": (_i, [_vp]),
     "mcsparseSpMatGetSize": (_i, [_vp, _pi64, _pi64, _pi64]),
     "mcsparseSpMatGetFormat": (_i, [_vp, _pi]),
@@ -126,6 +128,7 @@ PROTOTYPES = {
     "mcsparseB200PeerClose": (_i, [_vp]),
     "mcsparseB200SpMVGetStatus": (_i, [_vp, _vp, _vp, _pi]),
     "mcsparseB200SpMVPartitionView": (_i, [_vp, _vp, _pi, _pi64, _pvp]),
+    "mcsparseB200SpMVTransposedView": (_i, [_vp, _i, _vp, _pi64, _pvp, _pvp, _pvp]),
     "mcsparseB200ShardRowBounds": (_i, [_vp, _i64, _i64, _i, _vp, _i, _pi64]),
     "mcsparseB200ShardLocalRowOffsets": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),
 }

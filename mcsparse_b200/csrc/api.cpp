@@ -111,7 +111,7 @@ struct DeviceGuard {
 St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mcsparseSpMatDescr_t A,
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
               bool need_buffer, const void* buffer, bool need_size_out, const void* size_out,
-              bool allow_coo = false, bool allow_wide_indices = false) {
+              bool allow_coo = false, bool allow_wide_indices = false, bool allow_transposed = false) {
     if (h == nullptr) return BAD_HANDLE;
     if (alpha == nullptr || beta == nullptr || A == nullptr || X == nullptr || Y == nullptr) return BAD_POINTER;
     if (need_size_out && size_out == nullptr) return BAD_POINTER;
@@ -121,16 +121,22 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     const bool wide = A->rowIdxType == MCSPARSE_INDEX_64I && A->colIdxType == MCSPARSE_INDEX_64I;
     if (!(narrow || (wide && allow_wide_indices && A->format == MCSPARSE_FORMAT_CSR))) return NOT_IMPL;
     if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(X->size) || too_big(Y->size) ||
-        too_big(A->row_num + A->nnz))
+        too_big(A->row_num + A->nnz) || too_big(A->col_num + A->nnz))
         return NOT_IMPL;
     if (need_buffer && buffer == nullptr) return BAD_POINTER;
-    if (!(A->format == MCSPARSE_FORMAT_CSR || (allow_coo && A->format == MCSPARSE_FORMAT_COO))) return NOT_IMPL;
+    if (!(A->format == MCSPARSE_FORMAT_CSR || (allow_coo && A->format == MCSPARSE_FORMAT_COO) ||
+          (allow_transposed && A->format == MCSPARSE_FORMAT_CSC)))
+        return NOT_IMPL;
     const bool n_op = opA == MCSPARSE_OPERATION_NON_TRANSPOSE;
     if (!((n_op && X->size == A->col_num && Y->size == A->row_num) ||
           (!n_op && X->size == A->row_num && Y->size == A->col_num)))
         return BAD_SIZE;
     if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
-    if (!n_op) return NOT_IMPL;
+    // op(A) = A^T and CSC inputs run through a conversion into the buffer (32-bit CSR / CSC only).
+    if (!n_op && !(allow_transposed && opA == MCSPARSE_OPERATION_TRANSPOSE && narrow &&
+                   (A->format == MCSPARSE_FORMAT_CSR || A->format == MCSPARSE_FORMAT_CSC)))
+        return NOT_IMPL;
+    if (A->format == MCSPARSE_FORMAT_CSC && !narrow) return NOT_IMPL;
     if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType)) return NOT_IMPL;
     if (!is_real_fp(computeType)) return NOT_IMPL;
     return OK;
@@ -141,24 +147,34 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
 // (one small kernel and a 4-byte copy, which synchronises the stream) and remembered on the
 // descriptor; MCSPARSE_B200_SPMV_TILE=small|large overrides. `scratch` is device memory the
 // probe may overwrite (the start of the work buffer, before the analysis writes it).
-bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, void* scratch) {
+bool probe_small_tiles(mcsparseContext* h, const int32_t* idx, int64_t nnz, int64_t rows, size_t vsize, void* scratch) {
+    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
+        if (e[0] == 's') return true;
+        if (e[0] == 'l') return false;
+    }
+    int near = 4096;
+    if (nnz >= 2 && spmv_locality_probe(h->stream, nnz, idx, static_cast<int*>(scratch), &near) != cudaSuccess)
+        near = 4096;
+    bool small = near < 1024;
+    // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
+    const int64_t large = vsize == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    if ((rows + nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) small = true;
+    return small;
+}
+
+// `idx` / `rows`: the index array and the row count the kernels will run on (for a CSC input these
+// are the row indices and the column count).
+bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, const void* idx, int64_t rows, void* scratch) {
     if (A->colIdxType == MCSPARSE_INDEX_64I) return true;  // one tile size for 64-bit indices
     if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
         if (e[0] == 's') return true;
         if (e[0] == 'l') return false;
     }
     std::lock_guard<std::mutex> g(A->lock);
-    if (A->probed_cols == A->cols && A->probed_nnz == A->nnz) return A->small_tiles;
-    int near = 4096;
-    if (A->nnz >= 2 &&
-        spmv_locality_probe(h->stream, A->nnz, static_cast<const int32_t*>(A->cols), static_cast<int*>(scratch),
-                            &near) != cudaSuccess)
-        near = 4096;
-    A->small_tiles = near < 1024;
-    // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
-    const int64_t large = A->valueType == MACA_R_64F ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
-    if ((A->row_num + A->nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) A->small_tiles = true;
-    A->probed_cols = A->cols;
+    if (A->probed_cols == idx && A->probed_nnz == A->nnz) return A->small_tiles;
+    A->small_tiles = probe_small_tiles(h, static_cast<const int32_t*>(idx), A->nnz, rows,
+                                       A->valueType == MACA_R_64F ? 8 : 4, scratch);
+    A->probed_cols = idx;
     A->probed_nnz = A->nnz;
     return A->small_tiles;
 }
@@ -181,27 +197,47 @@ struct PushArgs {
 
 size_t index_size(const mcsparseSpMatDescr* A) { return A->rowIdxType == MCSPARSE_INDEX_64I ? 8 : 4; }
 
+// A product as the CSR kernels see it: an m x n CSR matrix (offsets `ptr`, indices `idx`) applied as
+// it is or transposed. CSC arrays are the CSR arrays of the transposed matrix, so a CSC input swaps
+// the roles (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:734-739 does the same swap).
+struct CsrView {
+    int64_t m = 0, n = 0;
+    const void* ptr = nullptr;
+    const void* idx = nullptr;
+    bool transposed = false;
+};
+
+CsrView csr_view(const mcsparseSpMatDescr* A, mcsparseOperation_t opA) {
+    CsrView v;
+    const bool t_op = opA != MCSPARSE_OPERATION_NON_TRANSPOSE;
+    if (A->format == MCSPARSE_FORMAT_CSC) {
+        v.m = A->col_num, v.n = A->row_num, v.ptr = A->cols, v.idx = A->rows, v.transposed = !t_op;
+    } else {
+        v.m = A->row_num, v.n = A->col_num, v.ptr = A->rows, v.idx = A->cols, v.transposed = t_op;
+    }
+    return v;
+}
+
 template <typename T, typename I>
-St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
+St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
             const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, bool small_tiles,
             const PushArgs& push = PushArgs()) {
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), small_tiles, sizeof(I));
+    const SpmvWorkspace ws = spmv_workspace(v.m, A->nnz, sizeof(T), small_tiles, sizeof(I));
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
-    const I* rows = static_cast<const I*>(A->rows);
+    const I* rows = static_cast<const I*>(v.ptr);
     if (A->format == MCSPARSE_FORMAT_COO) {
         // Row offsets derived from the sorted row indices live behind the SpMV work area
         // (32-bit indices only: the argument check admits no 64-bit COO).
         int32_t* offsets = reinterpret_cast<int32_t*>(static_cast<char*>(buf) + ws.bytes);
         if (analyse) {
-            cudaError_t e = coo_row_offsets(h->stream, A->row_num, A->nnz, base,
-                                            static_cast<const int32_t*>(A->rows), offsets);
+            cudaError_t e = coo_row_offsets(h->stream, v.m, A->nnz, base, static_cast<const int32_t*>(v.ptr), offsets);
             if (e != cudaSuccess) return from_cuda(e);
         }
         rows = reinterpret_cast<const I*>(offsets);
     }
     if (analyse) {
-        cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, base, rows, ws, buf);
+        cudaError_t e = spmv_analysis(h->stream, v.m, A->nnz, base, rows, ws, buf);
         if (e != cudaSuccess) return from_cuda(e);
     }
     if (!compute) return OK;
@@ -209,10 +245,81 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecDescr* X, mc
     peers.count = push.count;
     peers.row_offset = push.row_offset;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
-    cudaError_t e = spmv_tiled<T, I>(h->stream, A->row_num, A->nnz, base, rows, static_cast<const I*>(A->cols),
+    cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
                                      static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
                                      buf, peers);
+    return from_cuda(e);
+}
+
+// Layout of the external buffer of a transposed product: the SpMV work area of the n x m transposed
+// matrix, then (256-byte aligned) the conversion area described by TransposePlan.
+struct TransposedLayout {
+    void* work = nullptr;
+    void* area = nullptr;
+    TransposePlan plan;
+};
+
+TransposedLayout transposed_layout(const CsrView& v, int64_t nnz, size_t vsize, void* buffer) {
+    TransposedLayout L;
+    L.plan = transpose_plan(v.m, v.n, nnz, vsize);
+    L.work = align_up_256(buffer);
+    if (buffer != nullptr) L.area = align_up_256(static_cast<char*>(L.work) + spmv_workspace(v.n, nnz, vsize).bytes);
+    return L;
+}
+
+size_t transposed_buffer_bytes(const CsrView& v, int64_t nnz, size_t vsize) {
+    return spmv_workspace(v.n, nnz, vsize).bytes + 256 + transpose_plan(v.m, v.n, nnz, vsize).bytes + 256;
+}
+
+// y = alpha * V^T * x + beta * y for the CSR view V: convert (structure once per preprocess, or on
+// every call without one; values on every call), then the ordinary tile kernels on the result.
+template <typename T>
+St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X,
+                       mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer, bool preprocess_only) {
+    const int64_t nnz = A->nnz;
+    const int base = A->mat_descr->base;
+    const TransposedLayout L = transposed_layout(v, nnz, sizeof(T), buffer);
+    char* area = static_cast<char*>(L.area);
+    const int32_t* t_ptr = reinterpret_cast<const int32_t*>(area + L.plan.off_ptr);
+    const int32_t* t_idx = reinterpret_cast<const int32_t*>(area + L.plan.off_keys[L.plan.col_slot()]);
+    const T* t_val = reinterpret_cast<const T*>(area + L.plan.off_val);
+    bool cached = false, small = false, probed = false;
+    {
+        std::lock_guard<std::mutex> g(A->lock);
+        cached = A->trans_buffer == buffer && A->trans_ptr_src == v.ptr && A->trans_idx_src == v.idx && A->trans_nnz == nnz;
+        probed = A->trans_probed_idx == v.idx && A->trans_probed_nnz == nnz;
+        small = A->trans_small_tiles;
+    }
+    if (!cached) {
+        cudaError_t e = transpose_structure(h->stream, v.m, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
+                                            static_cast<const int32_t*>(v.idx), L.plan, L.area);
+        if (e != cudaSuccess) return from_cuda(e);
+        if (!probed) {  // tile size for the transposed matrix: probed once (synchronises), then remembered
+            small = probe_small_tiles(h, t_idx, nnz, v.n, sizeof(T), L.work);
+            std::lock_guard<std::mutex> g(A->lock);
+            A->trans_probed_idx = v.idx;
+            A->trans_probed_nnz = nnz;
+            A->trans_small_tiles = small;
+        }
+    }
+    const SpmvWorkspace ws = spmv_workspace(v.n, nnz, sizeof(T), small);
+    if (!cached) {
+        cudaError_t e = spmv_analysis(h->stream, v.n, nnz, 0, t_ptr, ws, L.work);
+        if (e != cudaSuccess) return from_cuda(e);
+        if (preprocess_only) {
+            std::lock_guard<std::mutex> g(A->lock);
+            A->trans_buffer = buffer;
+            A->trans_ptr_src = v.ptr;
+            A->trans_idx_src = v.idx;
+            A->trans_nnz = nnz;
+        }
+    }
+    if (preprocess_only) return OK;
+    cudaError_t e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area);
+    if (e != cudaSuccess) return from_cuda(e);
+    e = spmv_tiled<T, int32_t>(h->stream, v.n, nnz, 0, t_ptr, t_idx, t_val, static_cast<const T*>(X->values),
+                               static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, L.work);
     return from_cuda(e);
 }
 
@@ -220,7 +327,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
               mcsparseDnVecDescr_t X, const void* beta, mcsparseDnVecDescr_t Y, macaDataType computeType,
               void* buffer, bool preprocess_only, const PushArgs& push = PushArgs()) {
     St st = spmv_check(h, opA, alpha, A, X, beta, Y, computeType, true, buffer, false, nullptr, push.count == 0,
-                       push.count == 0);
+                       push.count == 0, push.count == 0);
     if (st != OK) return st;
     // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
     if (A->rows == nullptr || A->cols == nullptr || A->vals == nullptr || X->values == nullptr ||
@@ -228,26 +335,32 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
-    const bool small = choose_small_tiles(h, A, align_up_256(buffer));
-    const int ipt = spmv_workspace(A->row_num, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
+    const CsrView view = csr_view(A, opA);
+    if (view.transposed) {
+        if (computeType == MACA_R_64F)
+            return spmv_transposed_run<double>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+        return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+    }
+    const bool small = choose_small_tiles(h, A, view.idx, view.m, align_up_256(buffer));
+    const int ipt = spmv_workspace(view.m, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
         if (preprocess_only) {
             A->analysed_buffer = buffer;
-            A->analysed_rows = A->rows;
+            A->analysed_rows = view.ptr;
             A->analysed_items_per_tile = ipt;
-        } else if (A->analysed_buffer == buffer && A->analysed_rows == A->rows &&
+        } else if (A->analysed_buffer == buffer && A->analysed_rows == view.ptr &&
                    A->analysed_items_per_tile == ipt) {
             analyse = false;
         }
     }
     const bool wide = index_size(A) == 8;
     if (computeType == MACA_R_64F)
-        return wide ? spmv_run<double, int64_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
-                    : spmv_run<double, int32_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
-    return wide ? spmv_run<float, int64_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
-                : spmv_run<float, int32_t>(h, A, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+        return wide ? spmv_run<double, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                    : spmv_run<double, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+    return wide ? spmv_run<float, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                : spmv_run<float, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
 }
 
 // Legacy csrmv family: raw arrays plus a matrix descriptor
@@ -378,7 +491,7 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
                               mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer,
                               const PushArgs& push, int chunks) {
     void* buf = align_up_256(buffer);
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_small_tiles(h, A, buf));
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_small_tiles(h, A, A->cols, A->row_num, buf));
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
     if (h->side_stream == nullptr) {
@@ -695,6 +808,8 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     d->vals = csrValues;
     d->analysed_buffer = nullptr;
     d->analysed_rows = nullptr;
+    d->trans_buffer = nullptr;
+    d->trans_probed_idx = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -728,6 +843,22 @@ mcsparseStatus_t mcsparseCooGet(mcsparseSpMatDescr_t d, int64_t* rows, int64_t* 
 
 mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t d, void* cooRows, void* cooColumns, void* cooValues) {
     return mcsparseCsrSetPointers(d, cooRows, cooColumns, cooValues);
+}
+
+// CSC: the descriptor keeps the row indices in `rows` and the column offsets in `cols`, as the
+// reference does (mcsparse/src/common/mcsp_helper.cpp:447-452, :607-615).
+mcsparseStatus_t mcsparseCreateCsc(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                   void* cscColOffsets, void* cscRowInd, void* cscValues,
+                                   mcsparseIndexType_t cscColOffsetsType, mcsparseIndexType_t cscRowIndType,
+                                   mcsparseIndexBase_t idxBase, macaDataType valueType) {
+    mcsparseStatus_t st = mcsparseCreateCsr(spMatDescr, rows, cols, nnz, cscRowInd, cscColOffsets, cscValues,
+                                            cscRowIndType, cscColOffsetsType, idxBase, valueType);
+    if (st == MCSPARSE_STATUS_SUCCESS) (*spMatDescr)->format = MCSPARSE_FORMAT_CSC;
+    return st;
+}
+
+mcsparseStatus_t mcsparseCscSetPointers(mcsparseSpMatDescr_t d, void* cscColOffsets, void* cscRowInd, void* cscValues) {
+    return mcsparseCsrSetPointers(d, cscRowInd, cscColOffsets, cscValues);
 }
 
 mcsparseStatus_t mcsparseDestroySpMat(mcsparseSpMatDescr_t d) {
@@ -883,11 +1014,16 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
                                          mcsparseSpMVAlg_t alg, size_t* bufferSize) {
     (void)alg;
     St st = spmv_check(handle, opA, alpha, matA, vecX, beta, vecY, computeType, false, nullptr, true, bufferSize, true,
-                       true);
+                       true, true);
     if (st != OK) return pub(st);
     // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
     // also needs room for the row offsets derived from its row indices.
-    *bufferSize = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType), false, index_size(matA)).bytes + 256;
+    const CsrView view = csr_view(matA, opA);
+    if (view.transposed) {  // work area of the transposed matrix + the conversion area
+        *bufferSize = transposed_buffer_bytes(view, matA->nnz, value_size(computeType));
+        return MCSPARSE_STATUS_SUCCESS;
+    }
+    *bufferSize = spmv_workspace(view.m, matA->nnz, value_size(computeType), false, index_size(matA)).bytes + 256;
     if (matA->format == MCSPARSE_FORMAT_COO) *bufferSize += ((size_t(matA->row_num) + 1) * 4 + 255) & ~size_t(255);
     return MCSPARSE_STATUS_SUCCESS;
 }
@@ -936,6 +1072,24 @@ mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMa
     return pub(from_cuda(e));
 }
 
+mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcsparseOperation_t opA,
+                                                void* externalBuffer, int64_t* rows, const int32_t** rowOffsets,
+                                                const int32_t** colInd, const void** values) {
+    if (matA == nullptr || externalBuffer == nullptr || rows == nullptr || rowOffsets == nullptr || colInd == nullptr ||
+        values == nullptr)
+        return pub(BAD_POINTER);
+    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    const CsrView view = csr_view(matA, opA);
+    if (!view.transposed) return pub(BAD_VALUE);
+    const TransposedLayout L = transposed_layout(view, matA->nnz, value_size(matA->valueType), externalBuffer);
+    const char* area = static_cast<const char*>(L.area);
+    *rows = view.n;
+    *rowOffsets = reinterpret_cast<const int32_t*>(area + L.plan.off_ptr);
+    *colInd = reinterpret_cast<const int32_t*>(area + L.plan.off_keys[L.plan.col_slot()]);
+    *values = area + L.plan.off_val;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
 // SpMV for callers that may not allocate device memory: same arithmetic and kernels as
 // mcsparseSpMV, with the work area taken from the fixed array inside the library instead of an
 // external buffer. Nothing here (or below it) allocates. The analysis is redone on every call
@@ -967,7 +1121,7 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         return MCSPARSE_STATUS_INSUFFICIENT_RESOURCES;
     }
     const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType),
-                                            choose_small_tiles(handle, matA, scratch));
+                                            choose_small_tiles(handle, matA, matA->cols, matA->row_num, scratch));
     const int base = matA->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(matA->rows);
     e = spmv_analysis(handle->stream, matA->row_num, matA->nnz, base, rows, ws, scratch);

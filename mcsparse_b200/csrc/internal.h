@@ -60,6 +60,15 @@ struct mcsparseSpMatDescr {
     int push_chunks = 0;
     int64_t push_chunk_tiles[kMaxPushChunks + 1] = {};
     int64_t push_chunk_rows[kMaxPushChunks + 1] = {};
+    // Transposed products: which buffer holds the converted structure of which arrays (recorded by
+    // mcsparseSpMV_preprocess), and the tile size probed for the converted matrix.
+    void* trans_buffer = nullptr;
+    const void* trans_ptr_src = nullptr;
+    const void* trans_idx_src = nullptr;
+    int64_t trans_nnz = -1;
+    const void* trans_probed_idx = nullptr;
+    int64_t trans_probed_nnz = -1;
+    bool trans_small_tiles = false;
     // Column panels recorded by mcsparseSpMM_preprocess: buffer, arrays and shape they were built for.
     void* spmm_buffer = nullptr;
     const void* spmm_rows = nullptr;
@@ -171,6 +180,27 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_pt
 
 cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
                             int32_t* offsets);
+
+// Where the CSR arrays of the transposed matrix and the scratch of the conversion live inside a
+// buffer (byte offsets from a 256-byte aligned start). The transposed matrix is n x m, 0-based:
+// row offsets at off_ptr, column indices in keys[col_slot()], values at off_val.
+struct TransposePlan {
+    int passes = 1;          // radix-sort passes (8 bits of the column index each)
+    int64_t tiles = 0;       // thread blocks of one pass
+    int64_t hist_count = 0;  // 256 digit counts per tile
+    int64_t scan_chunks = 0;
+    size_t off_ptr = 0, off_keys[2] = {0, 0}, off_perm[2] = {0, 0}, off_val = 0, off_hist = 0, off_sums = 0;
+    size_t bytes = 0;
+    int final_slot() const { return (passes - 1) & 1; }  // where the last pass leaves sorted keys and permutation
+    int col_slot() const { return final_slot() ^ 1; }
+};
+TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_size);
+// Structure of the transposed matrix (row offsets, column indices, permutation) of an m x n CSR matrix.
+cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
+                                const int32_t* col, const TransposePlan& plan, void* buf);
+// Values of the transposed matrix, gathered through the permutation left by transpose_structure.
+template <typename T>
+cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& plan, void* buf);
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host);
 cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,

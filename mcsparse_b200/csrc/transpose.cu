@@ -1,0 +1,290 @@
+// CSR of the transposed matrix (equivalently: CSC of the matrix), built on the device so that
+// y = alpha * A^T * x + beta * y and products with CSC inputs run on the same CSR kernels.
+//
+// The reference reaches its CSR kernel the same way: it converts with csr2csc into the external
+// buffer and multiplies with the converted arrays (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:797-846,
+// mcsparse/src/common/mcsp_internal_transpose_sparse.hpp:237-341).
+//
+// The conversion is a stable sort of the nonzeros by column:
+//   1. least-significant-digit radix sort (8-bit digits, as many passes as the column count needs)
+//      of the pairs (column, position), each pass = tile histograms -> exclusive scan -> stable
+//      scatter; stable means that within a column the nonzeros keep their order (ascending rows),
+//      so the transposed matrix, and with it every later product, is the same on every run;
+//   2. row offsets of the transposed matrix = lower bounds of 0 .. cols in the sorted columns;
+//   3. column indices of the transposed matrix = the row that owns each source position (upper
+//      bound in the source row offsets);
+//   4. values gathered through the permutation (repeated on every product: values may have changed).
+#include <cstdint>
+
+#include "internal.h"
+
+namespace mcsp_b200 {
+namespace {
+
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortItemsPerWarp = 1024;                         // 32 rounds of one item per lane
+constexpr int kSortTile = kSortWarps * kSortItemsPerWarp;       // items per thread block
+constexpr int kScanThreads = 1024;
+constexpr int kScanItems = 8;                                   // consecutive items per thread
+constexpr int kScanChunk = kScanThreads * kScanItems;
+
+__device__ __forceinline__ unsigned sort_key(const int* __restrict__ keys, long long i, int sub) {
+    return (unsigned)(__ldg(keys + i) - sub);
+}
+
+// hist[d * tiles + t] = number of items of tile t whose digit is d.
+__global__ void __launch_bounds__(kSortThreads)
+    radix_hist_kernel(const int* __restrict__ keys, int sub, long long count, int shift, unsigned* __restrict__ hist,
+                      long long tiles) {
+    __shared__ unsigned s_cnt[256];
+    const long long t = blockIdx.x;
+    s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const long long begin = t * kSortTile;
+    const int lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < kSortTile; i += kSortThreads) {  // block-uniform trip count
+        const long long idx = begin + i;
+        const unsigned d = idx < count ? (sort_key(keys, idx, sub) >> shift) & 255u : 256u;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (d < 256u && lane == __ffs(peers) - 1) atomicAdd(&s_cnt[d], __popc(peers));
+    }
+    __syncthreads();
+    hist[(long long)threadIdx.x * tiles + t] = s_cnt[threadIdx.x];
+}
+
+// Stable scatter of one tile: item idx goes to offsets[digit][tile] + (number of earlier items of
+// the tile with the same digit). Warps own consecutive 1024-item pieces of the tile and walk them
+// 32 items at a time, so "earlier" is decided by (warp, round, lane) = ascending idx.
+__global__ void __launch_bounds__(kSortThreads)
+    radix_scatter_kernel(const int* __restrict__ keys_in, int sub, const unsigned* __restrict__ perm_in,
+                         int* __restrict__ keys_out, unsigned* __restrict__ perm_out, long long count, int shift,
+                         const unsigned* __restrict__ offsets, long long tiles) {
+    __shared__ unsigned s_cnt[kSortWarps][256];
+    const long long t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long begin = t * kSortTile + (long long)warp * kSortItemsPerWarp;
+    for (int w = 0; w < kSortWarps; ++w) s_cnt[w][threadIdx.x] = 0;
+    __syncthreads();
+    // pass 1: digit counts of each warp's piece
+    for (int r = 0; r < kSortItemsPerWarp / 32; ++r) {
+        const long long idx = begin + r * 32 + lane;
+        const unsigned d = idx < count ? (sort_key(keys_in, idx, sub) >> shift) & 255u : 256u;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (d < 256u && lane == __ffs(peers) - 1) s_cnt[warp][d] += __popc(peers);  // one writer per digit and round
+        __syncwarp();
+    }
+    __syncthreads();
+    // counts -> first output position of every (warp, digit)
+    {
+        const int d = threadIdx.x;
+        unsigned running = offsets[(long long)d * tiles + t];
+        for (int w = 0; w < kSortWarps; ++w) {
+            const unsigned c = s_cnt[w][d];
+            s_cnt[w][d] = running;
+            running += c;
+        }
+    }
+    __syncthreads();
+    // pass 2: positions, in the same order as pass 1 counted
+    for (int r = 0; r < kSortItemsPerWarp / 32; ++r) {
+        const long long idx = begin + r * 32 + lane;
+        const bool live = idx < count;
+        const unsigned key = live ? sort_key(keys_in, idx, sub) : 0u;
+        const unsigned d = live ? (key >> shift) & 255u : 256u;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const int leader = __ffs(peers) - 1;
+        unsigned base = 0;
+        if (live && lane == leader) {
+            base = s_cnt[warp][d];
+            s_cnt[warp][d] = base + __popc(peers);
+        }
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (live) {
+            const unsigned pos = base + __popc(peers & ((1u << lane) - 1u));
+            keys_out[pos] = (int)key;
+            perm_out[pos] = perm_in ? __ldg(perm_in + idx) : (unsigned)idx;
+        }
+        __syncwarp();
+    }
+}
+
+// ---- exclusive scan of a long array of counts, in place (three kernels)
+
+__device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned* s_warp, unsigned* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned inc = v;
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned w = s_warp[lane];  // kScanThreads / 32 == 32 warps
+        unsigned winc = w;
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned o = __shfl_up_sync(0xffffffffu, winc, d);
+            if (lane >= d) winc += o;
+        }
+        s_warp[lane] = winc - w;  // exclusive prefix of the warp totals
+        if (lane == 31) *total = winc;
+    }
+    __syncthreads();
+    return s_warp[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    scan_chunk_sums_kernel(const unsigned* __restrict__ data, long long count, unsigned* __restrict__ sums) {
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_total;
+    const long long first = (long long)blockIdx.x * kScanChunk + (long long)threadIdx.x * kScanItems;
+    unsigned v = 0;
+    for (int i = 0; i < kScanItems; ++i)
+        if (first + i < count) v += data[first + i];
+    block_exclusive_scan(v, s_warp, &s_total);
+    if (threadIdx.x == 0) sums[blockIdx.x] = s_total;
+}
+
+// One thread block: exclusive scan of the chunk sums, 1024 at a time with a running carry.
+__global__ void __launch_bounds__(kScanThreads) scan_sums_kernel(unsigned* __restrict__ sums, long long chunks) {
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_total;
+    unsigned carry = 0;
+    for (long long first = 0; first < chunks; first += kScanThreads) {  // block-uniform trip count
+        const long long i = first + threadIdx.x;
+        const unsigned v = i < chunks ? sums[i] : 0u;
+        const unsigned ex = block_exclusive_scan(v, s_warp, &s_total);
+        if (i < chunks) sums[i] = carry + ex;
+        carry += s_total;
+        __syncthreads();  // s_warp / s_total are reused by the next round
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    scan_apply_kernel(unsigned* __restrict__ data, long long count, const unsigned* __restrict__ sums) {
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_total;
+    const long long first = (long long)blockIdx.x * kScanChunk + (long long)threadIdx.x * kScanItems;
+    unsigned item[kScanItems];
+    unsigned v = 0;
+    for (int i = 0; i < kScanItems; ++i) {
+        item[i] = first + i < count ? data[first + i] : 0u;
+        v += item[i];
+    }
+    unsigned run = sums[blockIdx.x] + block_exclusive_scan(v, s_warp, &s_total);
+    for (int i = 0; i < kScanItems; ++i) {
+        if (first + i < count) data[first + i] = run;
+        run += item[i];
+    }
+}
+
+// out[k] = the row whose range of source positions contains perm[k] (0-based), i.e. the column
+// index of the k-th nonzero of the transposed matrix.
+__global__ void owner_row_kernel(long long m, long long nnz, int base, const int* __restrict__ row_ptr,
+                                 const unsigned* __restrict__ perm, int* __restrict__ out) {
+    const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (k >= nnz) return;
+    const long long target = (long long)perm[k] + base;
+    long long lo = 0, hi = m - 1;  // last r in [0, m) with row_ptr[r] <= target: upper bound minus one
+    while (lo < hi) {
+        const long long mid = (lo + hi + 1) >> 1;
+        if ((long long)__ldg(row_ptr + mid) <= target)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    out[k] = (int)lo;
+}
+
+template <typename T>
+__global__ void permute_values_kernel(long long nnz, const T* __restrict__ val, const unsigned* __restrict__ perm,
+                                      T* __restrict__ out) {
+    const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (k < nnz) out[k] = __ldg(val + __ldcs(perm + k));
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_size) {
+    (void)m;
+    TransposePlan p;
+    int bits = 1;
+    while (bits < 31 && (int64_t(1) << bits) < n) ++bits;
+    p.passes = (bits + 7) / 8;
+    p.tiles = (nnz + kSortTile - 1) / kSortTile;
+    p.hist_count = 256 * p.tiles;
+    p.scan_chunks = (p.hist_count + kScanChunk - 1) / kScanChunk;
+    size_t off = 0;
+    p.off_ptr = off;
+    off += align256(size_t(n + 1) * 4);
+    for (int i = 0; i < 2; ++i) {
+        p.off_keys[i] = off;
+        off += align256(size_t(nnz) * 4);
+    }
+    for (int i = 0; i < 2; ++i) {
+        p.off_perm[i] = off;
+        off += align256(size_t(nnz) * 4);
+    }
+    p.off_val = off;
+    off += align256(size_t(nnz) * value_size);
+    p.off_hist = off;
+    off += align256(size_t(p.hist_count) * 4);
+    p.off_sums = off;
+    off += align256(size_t(p.scan_chunks) * 4);
+    p.bytes = off;
+    return p;
+}
+
+cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
+                                const int32_t* col, const TransposePlan& p, void* buf) {
+    char* b = static_cast<char*>(buf);
+    int32_t* ptr = reinterpret_cast<int32_t*>(b + p.off_ptr);
+    int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
+    unsigned* perm[2] = {reinterpret_cast<unsigned*>(b + p.off_perm[0]), reinterpret_cast<unsigned*>(b + p.off_perm[1])};
+    unsigned* hist = reinterpret_cast<unsigned*>(b + p.off_hist);
+    unsigned* sums = reinterpret_cast<unsigned*>(b + p.off_sums);
+    cudaError_t e = cudaSuccess;
+    if (nnz > 0) {
+        const int* src_keys = col;
+        const unsigned* src_perm = nullptr;
+        int sub = base;
+        for (int pass = 0; pass < p.passes; ++pass) {
+            const int dst = pass & 1;
+            radix_hist_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, nnz, 8 * pass, hist, p.tiles);
+            scan_chunk_sums_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
+            scan_sums_kernel<<<1, kScanThreads, 0, s>>>(sums, p.scan_chunks);
+            scan_apply_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
+            radix_scatter_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, src_perm, keys[dst],
+                                                                             perm[dst], nnz, 8 * pass, hist, p.tiles);
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+            src_keys = keys[dst];
+            src_perm = perm[dst];
+            sub = 0;
+        }
+    }
+    const int fin = p.final_slot();
+    // Row offsets of the transposed matrix from the sorted (0-based) columns; with no nonzeros they are all zero.
+    if ((e = coo_row_offsets(s, n, nnz, 0, keys[fin], ptr)) != cudaSuccess) return e;
+    if (nnz > 0) {
+        owner_row_kernel<<<(unsigned)((nnz + 255) / 256), 256, 0, s>>>(m, nnz, base, row_ptr, perm[fin], keys[fin ^ 1]);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+template <typename T>
+cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& p, void* buf) {
+    if (nnz == 0) return cudaSuccess;
+    char* b = static_cast<char*>(buf);
+    permute_values_kernel<T><<<(unsigned)((nnz + 255) / 256), 256, 0, s>>>(
+        nnz, val, reinterpret_cast<const unsigned*>(b + p.off_perm[p.final_slot()]), reinterpret_cast<T*>(b + p.off_val));
+    return cudaGetLastError();
+}
+
+template cudaError_t transpose_values<float>(cudaStream_t, int64_t, const float*, const TransposePlan&, void*);
+template cudaError_t transpose_values<double>(cudaStream_t, int64_t, const double*, const TransposePlan&, void*);
+
+}  // namespace mcsp_b200

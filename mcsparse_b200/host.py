@@ -84,6 +84,30 @@ class CsrMatrix:
             self.d = None
 
 
+class CscMatrix:
+    """mcsparseSpMatDescr_t in CSC form over three device tensors (column offsets, row indices, values)."""
+
+    def __init__(self, rows, cols, col_offsets, row_ind, values, base=0):
+        assert col_offsets.dtype == torch.int32 and row_ind.dtype == torch.int32
+        self.rows, self.cols, self.base = int(rows), int(cols), int(base)
+        self.nnz = int(row_ind.numel())
+        self.col_offsets, self.row_ind, self.values = col_offsets, row_ind, values
+        d = C.c_void_p()
+        check(lib.mcsparseCreateCsc(C.byref(d), self.rows, self.cols, self.nnz, _ptr(col_offsets), _ptr(row_ind),
+                                    _ptr(values), capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, self.base,
+                                    _DTYPE[values.dtype]), "mcsparseCreateCsc")
+        self.d = d
+
+    @property
+    def dtype(self):
+        return self.values.dtype
+
+    def __del__(self):
+        if getattr(self, "d", None) is not None and lib is not None:
+            lib.mcsparseDestroySpMat(self.d)
+            self.d = None
+
+
 class DnVec:
     def __init__(self, values):
         self.values = values
@@ -122,28 +146,28 @@ def _scalars(handle, alpha, beta, dtype):
     return C.cast(C.pointer(a), C.c_void_p), C.cast(C.pointer(b), C.c_void_p), (a, b)
 
 
-def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0):
+def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
     pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
     size = C.c_size_t()
-    check(lib.mcsparseSpMV_bufferSize(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d,
+    check(lib.mcsparseSpMV_bufferSize(handle.h, op, pa, A.d, x.d, pb, y.d,
                                       _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, C.byref(size)),
           "mcsparseSpMV_bufferSize")
     del keep
     return size.value
 
 
-def spmv_preprocess(handle, A, x, y, buffer, alpha=1.0, beta=0.0):
+def spmv_preprocess(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
     pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
-    check(lib.mcsparseSpMV_preprocess(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d,
+    check(lib.mcsparseSpMV_preprocess(handle.h, op, pa, A.d, x.d, pb, y.d,
                                       _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)),
           "mcsparseSpMV_preprocess")
     del keep
 
 
-def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0):
-    """y = alpha * A @ x + beta * y through mcsparseSpMV (asynchronous on the handle's stream)."""
+def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
+    """y = alpha * op(A) @ x + beta * y through mcsparseSpMV (asynchronous on the handle's stream)."""
     pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
-    check(lib.mcsparseSpMV(handle.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, A.d, x.d, pb, y.d, _DTYPE[A.dtype],
+    check(lib.mcsparseSpMV(handle.h, op, pa, A.d, x.d, pb, y.d, _DTYPE[A.dtype],
                            capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)), "mcsparseSpMV")
     del keep
 

@@ -166,6 +166,30 @@ void oracle_coo_row_offsets(int64_t m, int64_t nnz, int base, const int32_t* coo
     for (int64_t r = 0; r < m; ++r) offsets[r + 1] += offsets[r];
 }
 
+/* CSR arrays of the transposed matrix (equivalently the CSC arrays of the matrix), 0-based, by a
+ * stable counting sort on the column: within a row of the transpose the nonzeros keep the order of
+ * the source, i.e. ascending source rows. The reference reaches its transposed products through the
+ * same conversion (csr2csc, mcsparse/src/common/mcsp_internal_transpose_sparse.hpp:237-341, called from
+ * mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:797-846); the order inside a row is this build's
+ * choice and is what the device conversion is checked against bit for bit.
+ * t_ptr: n + 1 entries; t_idx, perm: nnz entries; perm[k] = source position of transposed nonzero k. */
+void oracle_csr_transpose(int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr, const int32_t* col,
+                          int32_t* t_ptr, int32_t* t_idx, int32_t* perm) {
+    for (int64_t c = 0; c <= n; ++c) t_ptr[c] = 0;
+    for (int64_t j = 0; j < nnz; ++j) t_ptr[(int64_t)col[j] - base + 1] += 1;
+    for (int64_t c = 0; c < n; ++c) t_ptr[c + 1] += t_ptr[c];
+    int32_t* next = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n > 0 ? n : 1));
+    for (int64_t c = 0; c < n; ++c) next[c] = t_ptr[c];
+    for (int64_t r = 0; r < m; ++r) {
+        for (int64_t j = (int64_t)row_ptr[r] - base; j < (int64_t)row_ptr[r + 1] - base; ++j) {
+            const int32_t k = next[(int64_t)col[j] - base]++;
+            t_idx[k] = (int32_t)r;
+            perm[k] = (int32_t)j;
+        }
+    }
+    free(next);
+}
+
 /* Host-side structural check of a CSR matrix: 0 when valid, else the number of the first
  * rule broken (1 first offset, 2 monotone offsets, 3 last offset, 4 column range). */
 int oracle_csr_validate(int64_t m, int64_t cols, int64_t nnz, int base, const int32_t* row_ptr,

@@ -119,6 +119,17 @@ def coo_row_offsets(coo_rows, num_rows, base=0):
     return out
 
 
+def csr_transpose(row_ptr, col, num_cols, base=0):
+    """(t_ptr, t_idx, perm) of the transposed matrix: 0-based CSR arrays and, for every transposed nonzero,
+    its position in the source arrays (stable: ascending source rows inside a row of the transpose)."""
+    row_ptr, col = _np(row_ptr, np.int32), _np(col, np.int32)
+    m, nnz = row_ptr.size - 1, col.size
+    t_ptr, t_idx, perm = np.empty(num_cols + 1, np.int32), np.empty(nnz, np.int32), np.empty(nnz, np.int32)
+    lib().oracle_csr_transpose(C.c_int64(m), C.c_int64(num_cols), C.c_int64(nnz), C.c_int(base), _p(row_ptr), _p(col),
+                               _p(t_ptr), _p(t_idx), _p(perm))
+    return t_ptr, t_idx, perm
+
+
 def csr_validate(rows, cols, row_ptr, col, base=0):
     row_ptr, col = _np(row_ptr, np.int32), _np(col, np.int32)
     return lib().oracle_csr_validate(C.c_int64(rows), C.c_int64(cols), C.c_int64(col.size), C.c_int(base),

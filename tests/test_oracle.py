@@ -183,3 +183,21 @@ def test_coo_row_offsets(name, base):
     rp = (np.concatenate([[0], np.cumsum(lengths)]) + base).astype(np.int32)
     coo_rows = (np.repeat(np.arange(lengths.size), lengths) + base).astype(np.int32)
     np.testing.assert_array_equal(oracle.coo_row_offsets(coo_rows, lengths.size, base), rp)
+
+
+def test_csr_transpose_matches_scipy():
+    sp = pytest.importorskip("scipy.sparse")
+    from tests.util import ADVERSARIAL_LENGTHS, csr_from_lengths
+
+    for name in ("lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty", "one_row"):
+        for base in (0, 1):
+            lengths = ADVERSARIAL_LENGTHS[name]
+            n = max(max(lengths), 1) + 3
+            rp, col, val = csr_from_lengths(lengths, n, np.float64, seed=5, base=base)
+            t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+            ref = sp.csr_matrix((val, col - base, rp - base), shape=(len(lengths), n)).T.tocsr()
+            ref.sort_indices()
+            np.testing.assert_array_equal(t_ptr, ref.indptr)
+            np.testing.assert_array_equal(t_idx, ref.indices)
+            np.testing.assert_array_equal(val[perm], ref.data)
+            assert sorted(perm.tolist()) == list(range(col.size))

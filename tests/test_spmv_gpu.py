@@ -240,7 +240,7 @@ def test_spmv_status_codes(handle, device):
     assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, f32, 0, None) == capi.MCSPARSE_STATUS_INVALID_VALUE
     assert call(handle.h, N, pa, A.d, X.d, pa, Ywrong.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
     assert call(handle.h, H, pa, A.d, Y.d, pa, X.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE
-    assert call(handle.h, T, pa, A.d, Y.d, pa, X.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert call(handle.h, T, pa, A.d, X.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_INVALID_VALUE  # sizes not swapped
     assert call(handle.h, N, pa, A.d, X.d, pa, Y.d, capi.MACA_R_64F, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
     assert call(handle.h, N, pa, A.d, X64.d, pa, Y.d, f32, 0, pb) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
     mode = C.c_int(capi.MCSPARSE_FILL_MODE_LOWER)

@@ -1,0 +1,148 @@
+"""GPU parity tests of the transposed products of mcsparseSpMV: op(A) = A^T on CSR and CSC inputs,
+both through the device conversion that is checked bit for bit against the CPU one."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import mcsparse_b200 as mc
+from mcsparse_b200 import capi, workloads
+from mcsparse_b200.capi import lib
+from oracle import oracle
+from tests.util import ADVERSARIAL_LENGTHS, TOL, assert_close, csr_from_lengths
+
+pytestmark = pytest.mark.gpu
+N, T = capi.MCSPARSE_OPERATION_NON_TRANSPOSE, capi.MCSPARSE_OPERATION_TRANSPOSE
+
+
+def device_view(A, op, buf, nnz, dtype):
+    """(row offsets, column indices, values) of the converted matrix inside the buffer, as numpy arrays."""
+    rows, p_ptr, p_idx, p_val = C.c_int64(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+    capi.check(lib.mcsparseB200SpMVTransposedView(A.d, op, C.c_void_p(buf.data_ptr()), C.byref(rows), C.byref(p_ptr),
+                                                  C.byref(p_idx), C.byref(p_val)))
+
+    def grab(p, count, tdtype):
+        off = p.value - buf.data_ptr()
+        size = count * torch.empty(0, dtype=tdtype).element_size()
+        return buf[off:off + size].view(tdtype).cpu().numpy()
+
+    return (rows.value, grab(p_ptr, rows.value + 1, torch.int32), grab(p_idx, nnz, torch.int32),
+            grab(p_val, nnz, torch.from_numpy(np.zeros(0, dtype)).dtype))
+
+
+def up(a, device):
+    """Device copy with a non-null address even when the array is empty (the C API rejects null arrays)."""
+    t = torch.empty(a.size + 1, dtype=torch.from_numpy(a[:0]).dtype, device=device)
+    t[:a.size] = torch.from_numpy(a).to(device)
+    return t[:a.size]
+
+
+def run(handle, device, A, op, x, y0, alpha, beta, preprocess=False):
+    d_x, d_y = torch.from_numpy(x).to(device), torch.from_numpy(y0.copy()).to(device)
+    X, Y = mc.DnVec(d_x), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=op), dtype=torch.uint8, device=device)
+    if preprocess:
+        mc.spmv_preprocess(handle, A, X, Y, buf, op=op)
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=beta, op=op)
+    torch.cuda.synchronize()
+    return d_y, buf, (X, Y)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("beta", [0.0, -0.75])
+@pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
+def test_spmv_transpose_csr(handle, device, name, dtype, base, beta):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, n = len(lengths), max(max(lengths), 1) + 17
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=17, base=base)
+    rng = np.random.default_rng(4)
+    x, y0 = rng.uniform(-1, 1, m).astype(dtype), rng.uniform(-1, 1, n).astype(dtype)
+    t = [up(a, device) for a in (rp, col, val)]
+    A = mc.CsrMatrix(m, n, *t, base=base)
+    d_y, buf, _ = run(handle, device, A, T, x, y0, 1.25, beta)
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+    ref, d = oracle.spmv(t_ptr, t_idx, val[perm], x, 1.25, beta, y0)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], name)
+    rows, g_ptr, g_idx, g_val = device_view(A, T, buf, col.size, dtype)
+    assert rows == n
+    np.testing.assert_array_equal(g_ptr, t_ptr)
+    np.testing.assert_array_equal(g_idx, t_idx)
+    np.testing.assert_array_equal(g_val, val[perm])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle", "mostly_empty"])
+def test_spmv_csc_input(handle, device, name, dtype, base):
+    """A given in CSC form: A @ x goes through the conversion, A^T @ x runs the CSR kernels directly."""
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, n = len(lengths), max(max(lengths), 1) + 5
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=23, base=base)
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+    csc = [up(a, device) for a in ((t_ptr + base).astype(np.int32), (t_idx + base).astype(np.int32), val[perm])]
+    A = mc.CscMatrix(m, n, *csc, base=base)
+    rng = np.random.default_rng(6)
+    xn, ym = rng.uniform(-1, 1, n).astype(dtype), rng.uniform(-1, 1, m).astype(dtype)
+    d_y, _, _ = run(handle, device, A, N, xn, ym, 0.5, 2.0, preprocess=True)
+    ref, d = oracle.spmv(rp, col, val, xn, 0.5, 2.0, ym, base=base)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], f"{name} CSC, A @ x")
+    d_y, _, _ = run(handle, device, A, T, ym, xn, 0.5, 2.0)
+    ref, d = oracle.spmv(t_ptr, t_idx, val[perm], ym, 0.5, 2.0, xn)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], f"{name} CSC, A^T @ x")
+
+
+@pytest.mark.parametrize("name,factor", [("C2", 64), ("C3", 64), ("C5", 64)])
+def test_spmv_transpose_scaled_configs(handle, device, name, factor):
+    """Three radix passes (more than 65536 columns), recorded conversion reused, values updated in place."""
+    cfg = workloads.scaled(name, factor)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    x = workloads.dense_values(cfg, device, w.rows, 77)
+    y = torch.zeros(w.cols, dtype=cfg.dtype, device=device)
+    X, Y = mc.DnVec(x), mc.DnVec(y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=T), dtype=torch.uint8, device=device)
+    mc.spmv_preprocess(handle, A, X, Y, buf, op=T)
+    rp, col = w.row_ptr.cpu().numpy(), w.col.cpu().numpy()
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, w.cols)
+    results = []
+    for scale in (1.0, -2.0, -2.0):
+        w.val.mul_(scale)  # in place: the recorded structure stays valid, the values must be re-read
+        mc.spmv(handle, A, X, Y, buf, alpha=1.0, beta=0.0, op=T)
+        torch.cuda.synchronize()
+        val = w.val.cpu().numpy()
+        ref, d = oracle.spmv(t_ptr, t_idx, val[perm], x.cpu().numpy(), 1.0, 0.0)
+        assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], f"{name} transposed, values x{scale}")
+        results.append(y.clone())
+    _, g_ptr, g_idx, _ = device_view(A, T, buf, col.size, val.dtype)
+    np.testing.assert_array_equal(g_ptr, t_ptr)
+    np.testing.assert_array_equal(g_idx, t_idx)
+    # same inputs (values x4 of the first call), same conversion, same order of summation
+    mc.spmv(handle, A, X, Y, buf, alpha=1.0, beta=0.0, op=T)
+    torch.cuda.synchronize()
+    assert torch.equal(y, results[-1])
+
+
+def test_spmv_transpose_refusals(handle, device):
+    rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.float32)
+    t64 = [torch.from_numpy(a).to(device) for a in (rp.astype(np.int64), col.astype(np.int64), val)]
+    A64 = mc.CsrMatrix(4, 5, *t64)
+    X, Y = mc.DnVec(torch.ones(4, device=device)), mc.DnVec(torch.zeros(5, device=device))
+    one = C.c_float(1.0)
+    pa = C.cast(C.pointer(one), C.c_void_p)
+    size = C.c_size_t()
+    # 64-bit indices are not converted; the peer-push and built-in-buffer entry points take op(A) = A only
+    assert lib.mcsparseSpMV_bufferSize(handle.h, T, pa, A64.d, X.d, pa, Y.d, capi.MACA_R_32F, 0,
+                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    t32 = [torch.from_numpy(a).to(device) for a in (rp, col, val)]
+    A = mc.CsrMatrix(4, 5, *t32)
+    assert lib.mcsparseB200SpMVNoAlloc(handle.h, T, pa, A.d, X.d, pa, Y.d, capi.MACA_R_32F,
+                                       0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert lib.mcsparseSpMV_bufferSize(handle.h, T, pa, A.d, X.d, pa, Y.d, capi.MACA_R_32F, 0, C.byref(size)) == 0
+    plain = C.c_size_t()
+    Xn, Yn = mc.DnVec(torch.ones(5, device=device)), mc.DnVec(torch.zeros(4, device=device))
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, Xn.d, pa, Yn.d, capi.MACA_R_32F, 0, C.byref(plain)) == 0
+    assert size.value > plain.value  # the conversion area is part of the reported size
