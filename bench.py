@@ -180,6 +180,45 @@ class SpmvJob:
         sharding.all_gather_ragged(self.parts, self.y)
 
 
+class TransposedSpmvJob:
+    """y = A^T x through mcsparseSpMV with op(A) = A^T: conversion recorded once by the preprocess call
+    (timed separately), every step re-gathers the values and runs the tile kernels on the converted matrix."""
+
+    def __init__(self, name, device, handle, scale=1):
+        import torch
+
+        import mcsparse_b200 as mc
+        from mcsparse_b200 import capi, workloads
+
+        self.torch, self.mc, self.h, self.op = torch, mc, handle, capi.MCSPARSE_OPERATION_TRANSPOSE
+        cfg = workloads.CONFIGS[name] if scale == 1 else workloads.scaled(name, scale)
+        self.cfg = cfg
+        w = workloads.generate(cfg, device)
+        self.w, self.total_nnz = w, w.nnz
+        self.vsize = 8 if cfg.dtype == torch.float64 else 4
+        self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+        self.x = workloads.dense_values(cfg, device, w.rows, 77)
+        self.y = torch.zeros(w.cols, dtype=cfg.dtype, device=device)
+        self.X, self.Y = mc.DnVec(self.x), mc.DnVec(self.y)
+        self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y, op=self.op), dtype=torch.uint8,
+                               device=device)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record()
+        mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf, op=self.op)
+        t1.record()
+        torch.cuda.synchronize()
+        self.preprocess_ms = t0.elapsed_time(t1)
+        self.bytes = workloads.algorithmic_bytes(w.cols, w.rows, w.nnz, self.vsize, 0.0)
+        self.flops = 2 * w.nnz
+        self.launches_per_step = 3
+
+    def step(self):
+        self.mc.spmv(self.h, self.A, self.X, self.Y, self.buf, alpha=1.0, beta=0.0, op=self.op)
+
+    compute = step
+
+
 class SpmmJob:
     def __init__(self, name, n, device, handle, scale=1):
         import torch
@@ -485,6 +524,13 @@ def run_gpu(args, rank, world, local_rank):
             for name in ("C1", "C2", "C3"):
                 j = SpmvJob(name, device, 0, 1, h)
                 extra[name] = measure_job(torch, j, 100, 5, peak, flush_buf)
+                del j
+                torch.cuda.empty_cache()
+            for name in ("C2", "C5"):
+                j = TransposedSpmvJob(name, device, h)
+                extra[f"{name}_transposed"] = measure_job(torch, j, 30, 3, peak, flush_buf)
+                extra[f"{name}_transposed"].update({"conversion_ms_once": round(j.preprocess_ms, 3),
+                                                    "buffer_bytes": j.buf.numel()})
                 del j
                 torch.cuda.empty_cache()
             for n in (64, 128):
