@@ -108,6 +108,22 @@ mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation
                                       void* externalBuffer, int numPeers, void* const* peerY, int64_t rowOffset);
 
 /*
+ * Same product as mcsparseB200SpMVPush, with the finished rows stored once into an NVSwitch
+ * multicast mapping instead of once per peer: multicastY is the address of the full-length y in a
+ * multicast address range bound to the same-sized, same-offset allocation on every GPU of the run
+ * (this one included), 16-byte aligned; the kernels use multimem.st, the switch replicates the
+ * store to all GPUs. vecY must be this GPU's rows inside its own unicast mapping of that
+ * allocation. Creating the mapping is the caller's job (CUDA virtual-memory multicast objects;
+ * the Python harness takes it from torch's symmetric-memory allocator). As with the peer-store
+ * variant, order the GPUs with any collective before y is read. No reference counterpart.
+ */
+mcsparseStatus_t mcsparseB200SpMVPushMulticast(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                               mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                               mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                               mcsparseSpMVAlg_t alg, void* externalBuffer, void* multicastY,
+                                               int64_t rowOffset);
+
+/*
  * Device buffers that other processes on the same node can map (one process per GPU):
  * PeerAlloc/PeerFree allocate with the plain CUDA allocator; PeerExport fills a 64-byte
  * handle that another process passes to PeerOpen to obtain an address valid on its current

@@ -121,6 +121,7 @@ PROTOTYPES = {
     "mcsparseDcsrmm": (_i, _CSRMM),
     "mcsparseB200SpMVNoAlloc": (_i, _SPMV_ARGS),
     "mcsparseB200SpMVPush": (_i, _SPMV_ARGS + [_vp, _i, _pvp, _i64]),
+    "mcsparseB200SpMVPushMulticast": (_i, _SPMV_ARGS + [_vp, _vp, _i64]),
     "mcsparseB200PeerAlloc": (_i, [_pvp, _sz]),
     "mcsparseB200PeerFree": (_i, [_vp]),
     "mcsparseB200PeerExport": (_i, [_vp, _vp]),

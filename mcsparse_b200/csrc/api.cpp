@@ -193,6 +193,7 @@ struct PushArgs {
     int count = 0;
     void* const* y = nullptr;
     int64_t row_offset = 0;
+    bool multicast = false;  // y[0] is a multicast address reaching every GPU
 };
 
 size_t index_size(const mcsparseSpMatDescr* A) { return A->rowIdxType == MCSPARSE_INDEX_64I ? 8 : 4; }
@@ -244,6 +245,7 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
     PeerList<T> peers;
     peers.count = push.count;
     peers.row_offset = push.row_offset;
+    peers.multicast = push.multicast;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
     cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
@@ -1342,6 +1344,24 @@ mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation
     if (computeType == MACA_R_64F)
         return pub(spmv_push_pipelined<double>(handle, matA, vecX, vecY, alpha, beta, externalBuffer, push, chunks));
     return pub(spmv_push_pipelined<float>(handle, matA, vecX, vecY, alpha, beta, externalBuffer, push, chunks));
+}
+
+mcsparseStatus_t mcsparseB200SpMVPushMulticast(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
+                                               mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,
+                                               mcsparseDnVecDescr_t vecY, macaDataType computeType,
+                                               mcsparseSpMVAlg_t alg, void* externalBuffer, void* multicastY,
+                                               int64_t rowOffset) {
+    (void)alg;
+    if (rowOffset < 0) return pub(BAD_SIZE);
+    if (multicastY == nullptr) return pub(BAD_POINTER);
+    if ((reinterpret_cast<uintptr_t>(multicastY) & 15) != 0) return pub(BAD_VALUE);
+    void* const dst[1] = {multicastY};
+    PushArgs push;
+    push.count = 1;
+    push.y = dst;
+    push.row_offset = rowOffset;
+    push.multicast = true;
+    return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
 }
 
 mcsparseStatus_t mcsparseB200PeerAlloc(void** devPtr, size_t bytes) {

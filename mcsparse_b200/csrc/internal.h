@@ -105,10 +105,13 @@ struct ScalarArg {
 
 // Destinations of the fused row push of a row-sharded SpMV: the full-length y vectors of the
 // other GPUs (addresses valid on this device) and the global index of this shard's first row.
+// With `multicast`, count is 1 and y[0] is the vector's address in an NVSwitch multicast mapping
+// that covers every GPU of the run; the kernels then store with multimem.st.
 template <typename T>
 struct PeerList {
     static constexpr int kMax = 7;
     int count = 0;
+    bool multicast = false;
     long long row_offset = 0;
     T* y[kMax] = {};
 };

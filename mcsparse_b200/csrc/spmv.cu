@@ -134,8 +134,36 @@ __device__ __forceinline__ double mad(double a, double b, double c) { return fma
 // the row's global position. The NVLink traffic thus overlaps the kernel instead of
 // following it as a separate all-gather. A row that continues from an earlier tile is the
 // exception: its value is final only after the carry fix-up, which pushes it then.
+//
+// Multicast mode (peers.multicast): y[0] is the address of the full-length y inside an NVSwitch
+// multicast mapping that spans all GPUs of the run; one multimem.st then reaches every GPU's copy
+// (this one included), so a row costs one store instruction instead of one per peer and the
+// replication happens in the switch.
+__device__ __forceinline__ void multicast_store(float* p, float v) {
+    asm volatile("multimem.st.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void multicast_store(double* p, double v) {
+    asm volatile("multimem.st.global.f64 [%0], %1;" ::"l"(p), "d"(v) : "memory");
+}
+// 16 bytes at a 16-byte aligned multicast address (the bit patterns travel unchanged).
+__device__ __forceinline__ void multicast_store_vec16(float* dst, const float* v) {
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+                 "f"(v[3])
+                 : "memory");
+}
+__device__ __forceinline__ void multicast_store_vec16(double* dst, const double* v) {
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__int_as_float(__double2loint(v[0]))),
+                 "f"(__int_as_float(__double2hiint(v[0]))), "f"(__int_as_float(__double2loint(v[1]))),
+                 "f"(__int_as_float(__double2hiint(v[1])))
+                 : "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ void push_to_peers(const PeerList<T>& peers, long long row, T v) {
+    if (peers.multicast) {
+        multicast_store(peers.y[0] + peers.row_offset + row, v);
+        return;
+    }
 #pragma unroll
     for (int p = 0; p < PeerList<T>::kMax; ++p)
         if (p < peers.count) peers.y[p][peers.row_offset + row] = v;
@@ -166,12 +194,20 @@ __device__ __forceinline__ void push_tile_rows(const PeerList<T>& peers, const T
                 T v[VW];
 #pragma unroll
                 for (int e = 0; e < VW; ++e) v[e] = vals[head + c * VW + e];
-                store_vec16(dst + head + c * VW, v);
+                if (peers.multicast)
+                    multicast_store_vec16(dst + head + c * VW, v);
+                else
+                    store_vec16(dst + head + c * VW, v);
             }
             const int tail0 = head + nvec * VW;
             const int u = THREADS - 1 - tid;  // the scalar edges go to the last threads, idle above
-            if (u < head) dst[u] = vals[u];
-            if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
+            if (peers.multicast) {
+                if (u < head) multicast_store(dst + u, vals[u]);
+                if (u >= VW && u - VW < n - tail0) multicast_store(dst + tail0 + (u - VW), vals[tail0 + (u - VW)]);
+            } else {
+                if (u < head) dst[u] = vals[u];
+                if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
+            }
         }
     }
 }

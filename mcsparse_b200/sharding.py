@@ -97,6 +97,47 @@ class PeerVector:
             self.ptr = 0
 
 
+class MulticastVector:
+    """A full-length device vector allocated on every rank by torch's symmetric-memory allocator and
+    bound to one NVSwitch multicast mapping: a multimem store to `multicast_ptr + offset` lands at
+    `offset` in every rank's copy. Raises RuntimeError when the GPUs offer no multicast mapping."""
+
+    def __init__(self, numel, dtype, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.numel, self.dtype = numel, dtype
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.tensor = symm.empty(max(numel, 1), dtype=dtype, device=device)[:numel]
+        self.handle = symm.rendezvous(self.tensor, group=self.group)
+        base = int(self.handle.multicast_ptr)
+        if base == 0:
+            raise RuntimeError("no NVSwitch multicast mapping available for symmetric memory on this system")
+        # The multicast range mirrors this rank's allocation: same offset, same bytes.
+        delta = self.tensor.data_ptr() - int(self.handle.buffer_ptrs[self.handle.rank])
+        if not 0 <= delta < int(self.handle.buffer_size):
+            raise RuntimeError("symmetric-memory tensor lies outside its allocation")
+        self.multicast_ptr = base + delta
+        self.tensor.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def close(self):
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)  # nobody frees while a peer's kernel may still store
+        self.handle = None
+        self.tensor = None
+        dist.barrier(group=self.group)
+
+
+def push_mode(world):
+    """How ShardedSpmv assembles y: MCSPARSE_B200_PUSH_MODE=peer|multicast, default peer stores."""
+    import os
+
+    mode = os.environ.get("MCSPARSE_B200_PUSH_MODE", "peer")
+    return mode if mode in ("peer", "multicast") and world > 1 else "peer"
+
+
 class ShardedSpmv:
     """y = alpha * A @ x + beta * y for a row-sharded A with the full y left on every GPU.
 
@@ -109,13 +150,17 @@ class ShardedSpmv:
         self.h, self.A, self.group = handle, A_local, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.row_offset = int(row_offset)
-        self.y = PeerVector(total_rows, A_local.dtype, group)
+        self.mode = push_mode(self.world)
+        if self.mode == "multicast":
+            self.y = MulticastVector(total_rows, A_local.dtype, group)
+        else:
+            self.y = PeerVector(total_rows, A_local.dtype, group)
         self.y_local = self.y.tensor[self.row_offset:self.row_offset + A_local.rows]
         self.X, self.Y = host.DnVec(x), host.DnVec(self.y_local)
         self.buffer = torch.empty(host.spmv_buffer_size(handle, A_local, self.X, self.Y), dtype=torch.uint8,
                                   device=x.device)
         host.spmv_preprocess(handle, A_local, self.X, self.Y, self.buffer)
-        ptrs = [self.y.peer_ptrs[g] for g in sorted(self.y.peer_ptrs)]
+        ptrs = [] if self.mode == "multicast" else [self.y.peer_ptrs[g] for g in sorted(self.y.peer_ptrs)]
         self.n_peers = len(ptrs)
         self.peer_array = (C.c_void_p * max(self.n_peers, 1))(*ptrs)
         self.token = torch.zeros(1, dtype=torch.int32, device=x.device)
@@ -125,6 +170,14 @@ class ShardedSpmv:
         from . import host
 
         pa, pb, keep = host._scalars(self.h, alpha, beta, self.A.dtype)
+        if self.mode == "multicast":
+            check(lib.mcsparseB200SpMVPushMulticast(self.h.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, self.A.d,
+                                                    self.X.d, pb, self.Y.d, host._DTYPE[self.A.dtype],
+                                                    capi.MCSPARSE_SPMV_ALG_DEFAULT, host._ptr(self.buffer),
+                                                    C.c_void_p(self.y.multicast_ptr), self.row_offset),
+                  "mcsparseB200SpMVPushMulticast")
+            del keep
+            return
         check(lib.mcsparseB200SpMVPush(self.h.h, capi.MCSPARSE_OPERATION_NON_TRANSPOSE, pa, self.A.d, self.X.d, pb,
                                        self.Y.d, host._DTYPE[self.A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT,
                                        host._ptr(self.buffer), self.n_peers, self.peer_array, self.row_offset),
