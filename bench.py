@@ -159,7 +159,7 @@ class SpmvJob:
         self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta)
         self.flops = 2 * self.total_nnz
         # tile kernel + carry fix-up; with one peer the step is pipelined: 4 tile launches + 4 fix-ups
-        self.launches_per_step = 8 if world == 2 else 2
+        self.launches_per_step = 8 if 2 <= world <= 4 else 2
 
     def compute(self):
         """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""

@@ -478,13 +478,16 @@ St csrmm_entry(mcsparseHandle_t h, mcsparseOperation_t transA, mcsparseOperation
 }
 
 // How mcsparseB200SpMVPush moves finished rows to the peers. Measured on B200 / NVSwitch with the
-// 27-point stencil: with one peer, computing the tiles in 4 launches and copying each chunk's rows
-// with the copy engines while the next chunk computes is fastest; with more peers the serial copies
-// lose to the variant whose tile kernel stores every finished row to all peers itself (0 chunks).
+// 27-point stencil: with up to three peers, computing the tiles in 4 launches and copying each
+// chunk's rows with the copy engines (one stream per destination) while the next chunk computes is
+// fastest (two GPUs 0.573 against 0.656 ms, four GPUs 0.370 against 0.405 ms); with seven peers the
+// variant whose tile kernel stores every finished row to all peers itself (0 chunks) was the faster
+// one when the copies still shared one stream, and stays the default there until the
+// per-destination streams are measured at that size.
 // MCSPARSE_B200_PUSH_CHUNKS overrides the choice (0 ... 8), read on every call.
 int push_chunks_setting(int num_peers) {
     const char* e = std::getenv("MCSPARSE_B200_PUSH_CHUNKS");
-    const int c = e ? std::atoi(e) : (num_peers <= 1 ? 4 : 0);
+    const int c = e ? std::atoi(e) : (num_peers <= 3 ? 4 : 0);
     return c < 0 ? 0 : (c > kMaxPushChunks ? kMaxPushChunks : c);
 }
 
@@ -505,6 +508,13 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
             return INTERNAL;
         for (auto& ev : h->events)
             if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL;
+        for (auto& ev : h->fix_events)
+            if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL;
+        for (auto& ev : h->peer_events)
+            if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL;
+        for (auto& st : h->peer_streams)
+            if (cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, greatest) != cudaSuccess) return INTERNAL;
+        if (cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking) != cudaSuccess) return INTERNAL;
     }
     {
         std::lock_guard<std::mutex> g(A->lock);
@@ -528,10 +538,72 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
     peers.count = push.count;
     peers.row_offset = push.row_offset;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
-    return from_cuda(spmv_tiled_pipelined<T>(
-        h->stream, h->side_stream, h->events, chunks, A->push_chunk_tiles, A->push_chunk_rows, A->row_num, A->nnz, base,
-        rows, static_cast<const int32_t*>(A->cols), static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
-        static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, buf, peers));
+    PushStreams ps;
+    ps.peer_streams = h->peer_streams;
+    ps.fix_events = h->fix_events;
+    ps.peer_events = h->peer_events;
+    const ScalarArg<T> a = scalar_arg<T>(h, alpha), b = scalar_arg<T>(h, beta);
+    auto enqueue = [&](cudaStream_t origin) {
+        return spmv_tiled_pipelined<T>(origin, h->side_stream, h->events, ps, chunks, A->push_chunk_tiles,
+                                       A->push_chunk_rows, A->row_num, A->nnz, base, rows,
+                                       static_cast<const int32_t*>(A->cols), static_cast<const T*>(A->vals),
+                                       static_cast<const T*>(X->values), static_cast<T*>(Y->values), a, b, ws, buf, peers);
+    };
+    // A step is some forty stream operations (launches, copies, event records and waits); issued one
+    // by one they cost more host time than the step takes on the GPUs. So the sequence is captured as
+    // a graph the first time and replayed with one call while nothing it depends on has changed
+    // (MCSPARSE_B200_PUSH_GRAPH=0 issues it directly; so does a stream that is itself being captured).
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(h->stream, &capturing);
+    const char* genv = std::getenv("MCSPARSE_B200_PUSH_GRAPH");
+    if (capturing != cudaStreamCaptureStatusNone || (genv != nullptr && genv[0] == '0'))
+        return from_cuda(enqueue(h->stream));
+
+    struct Key {
+        const void *rows, *cols, *vals, *x, *y, *buf, *stream;
+        void* peers[PeerList<T>::kMax];
+        long long row_offset, m, nnz;
+        double alpha_host, beta_host;
+        const void *alpha_dev, *beta_dev;
+        int chunks, count, items_per_tile, base, value_bytes;
+    } key;
+    static_assert(sizeof(Key) <= sizeof(A->push_graph_key), "key buffer too small");
+    std::memset(&key, 0, sizeof key);
+    key.rows = rows, key.cols = A->cols, key.vals = A->vals, key.x = X->values, key.y = Y->values, key.buf = buf;
+    key.stream = h->stream;
+    for (int p = 0; p < push.count; ++p) key.peers[p] = push.y[p];
+    key.row_offset = push.row_offset, key.m = A->row_num, key.nnz = A->nnz;
+    key.alpha_host = (double)a.host, key.beta_host = (double)b.host, key.alpha_dev = a.dev, key.beta_dev = b.dev;
+    key.chunks = chunks, key.count = push.count, key.items_per_tile = ws.items_per_tile, key.base = base;
+    key.value_bytes = (int)sizeof(T);
+    std::lock_guard<std::mutex> g(A->lock);
+    if (!(A->push_graph != nullptr && A->push_graph_key_bytes == sizeof key &&
+          std::memcmp(A->push_graph_key, &key, sizeof key) == 0)) {
+        if (A->push_graph != nullptr) {
+            cudaGraphExecDestroy(A->push_graph);
+            A->push_graph = nullptr;
+        }
+        cudaGraph_t graph = nullptr;
+        // Captured from a stream of the handle's own: the caller's stream may be the legacy default
+        // stream, which cannot be captured; the finished graph is launched on the caller's stream.
+        cudaError_t e = cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal);
+        if (e != cudaSuccess) return from_cuda(e);
+        const cudaError_t queued = enqueue(h->capture_stream);
+        e = cudaStreamEndCapture(h->capture_stream, &graph);
+        if (queued != cudaSuccess || e != cudaSuccess) {
+            if (graph != nullptr) cudaGraphDestroy(graph);
+            return from_cuda(queued != cudaSuccess ? queued : e);
+        }
+        e = cudaGraphInstantiate(&A->push_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) {
+            A->push_graph = nullptr;
+            return from_cuda(e);
+        }
+        std::memcpy(A->push_graph_key, &key, sizeof key);
+        A->push_graph_key_bytes = sizeof key;
+    }
+    return from_cuda(cudaGraphLaunch(A->push_graph, h->stream));
 }
 
 }  // namespace
@@ -558,6 +630,13 @@ mcsparseStatus_t mcsparseDestroy(mcsparseHandle_t handle) {
         cudaStreamDestroy(handle->side_stream);
         for (auto& ev : handle->events)
             if (ev != nullptr) cudaEventDestroy(ev);
+        for (auto& ev : handle->fix_events)
+            if (ev != nullptr) cudaEventDestroy(ev);
+        for (auto& ev : handle->peer_events)
+            if (ev != nullptr) cudaEventDestroy(ev);
+        for (auto& st : handle->peer_streams)
+            if (st != nullptr) cudaStreamDestroy(st);
+        if (handle->capture_stream != nullptr) cudaStreamDestroy(handle->capture_stream);
     }
     delete handle;
     return MCSPARSE_STATUS_SUCCESS;
@@ -865,6 +944,7 @@ mcsparseStatus_t mcsparseCscSetPointers(mcsparseSpMatDescr_t d, void* cscColOffs
 
 mcsparseStatus_t mcsparseDestroySpMat(mcsparseSpMatDescr_t d) {
     if (d == nullptr) return MCSPARSE_STATUS_SUCCESS;
+    if (d->push_graph != nullptr) cudaGraphExecDestroy(d->push_graph);
     delete d->mat_descr;
     delete d;
     return MCSPARSE_STATUS_SUCCESS;

@@ -23,6 +23,14 @@ struct mcsparseContext {
     // beside the kernels, and the events that order the two streams.
     cudaStream_t side_stream = nullptr;
     cudaEvent_t events[kMaxPushChunks + 1] = {};
+    // One copy stream per destination GPU, so that the copies of a chunk to different peers run on
+    // different copy engines at the same time; fix_events[c]: chunk c's rows are final;
+    // peer_events[p]: the last copy to peer p is done.
+    static constexpr int kMaxPeers = 7;
+    cudaStream_t peer_streams[kMaxPeers] = {};
+    cudaEvent_t fix_events[kMaxPushChunks] = {};
+    cudaEvent_t peer_events[kMaxPeers] = {};
+    cudaStream_t capture_stream = nullptr;  // origin stream while the step is captured as a graph
 };
 
 struct mcsparseMatDescr {
@@ -69,6 +77,11 @@ struct mcsparseSpMatDescr {
     const void* trans_probed_idx = nullptr;
     int64_t trans_probed_nnz = -1;
     bool trans_small_tiles = false;
+    // The pipelined push of one step (tile launches, fix-ups, per-destination copies and the events
+    // between them) captured once as a CUDA graph and replayed while every argument stays the same.
+    cudaGraphExec_t push_graph = nullptr;
+    unsigned char push_graph_key[256] = {};
+    size_t push_graph_key_bytes = 0;
     // Column panels recorded by mcsparseSpMM_preprocess: buffer, arrays and shape they were built for.
     void* spmm_buffer = nullptr;
     const void* spmm_rows = nullptr;
@@ -116,6 +129,13 @@ struct PeerList {
     T* y[kMax] = {};
 };
 
+// Streams and events of the per-destination row copies of the pipelined push (owned by the handle).
+struct PushStreams {
+    cudaStream_t* peer_streams = nullptr;
+    cudaEvent_t* fix_events = nullptr;
+    cudaEvent_t* peer_events = nullptr;
+};
+
 // Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
 //   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status
 // status stays 0 unless a kernel gave up a bounded wait (zeroed by the analysis kernel).
@@ -149,7 +169,8 @@ cudaError_t spmv_read_tile_rows(cudaStream_t s, const void* buf, int count, cons
 // The tiles in `chunks` launches; after each, a copy kernel on `side` pushes the rows that ended in
 // it to the peers while the next chunk computes; the carry fix-up (with its own pushes) comes last.
 template <typename T>
-cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t* events, int chunks,
+cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t* events, const PushStreams& ps,
+                                 int chunks,
                                  const int64_t* chunk_tiles, const int64_t* chunk_rows, int64_t m, int64_t nnz,
                                  int base, const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
                                  ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
