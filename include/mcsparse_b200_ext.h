@@ -19,6 +19,7 @@ extern "C" {
 #define MCSPARSE_B200_SPMV_TILE_ITEMS_F32 4096
 #define MCSPARSE_B200_SPMV_TILE_ITEMS_F64 2048
 #define MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 2048
+#define MCSPARSE_B200_SPMV_TILE_ITEMS_C64 1024 /* 16-byte values (complex double): one tile size */
 #define MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 1024
 
 /*

@@ -39,10 +39,11 @@ MCSPARSE_SPMAT_FILL_MODE, MCSPARSE_SPMAT_DIAG_TYPE = 0, 1
 MCSPARSE_SPMV_ALG_DEFAULT = 0
 MCSPARSE_SPMM_ALG_DEFAULT = 0
 MCSPARSE_ALG_MERGE_PATH = 0
-MACA_R_32F, MACA_R_64F, MACA_R_16F, MACA_C_32F, MACA_R_32I = 0, 1, 2, 4, 10
+MACA_R_32F, MACA_R_64F, MACA_R_16F, MACA_C_32F, MACA_C_64F, MACA_R_32I = 0, 1, 2, 4, 5, 10
 MAJOR_VERSION, MINOR_VERSION, PATCH_LEVEL = 0, 1, 2
 
-SPMV_TILE_ITEMS = {MACA_R_32F: (4096, 2048), MACA_R_64F: (2048, 1024)}  # (large, small) tile per value type
+SPMV_TILE_ITEMS = {MACA_R_32F: (4096, 2048), MACA_R_64F: (2048, 1024),  # (large, small) tile per value type
+                   MACA_C_32F: (2048, 1024), MACA_C_64F: (1024, 1024)}
 
 _vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 _pvp = C.POINTER(C.c_void_p)

@@ -71,7 +71,9 @@ bool value_type_known(macaDataType t) {
 }
 
 bool is_real_fp(macaDataType t) { return t == MACA_R_32F || t == MACA_R_64F; }
-size_t value_size(macaDataType t) { return t == MACA_R_64F ? 8 : 4; }
+bool is_complex_fp(macaDataType t) { return t == MACA_C_32F || t == MACA_C_64F; }
+bool is_compute_type(macaDataType t) { return is_real_fp(t) || is_complex_fp(t); }
+size_t value_size(macaDataType t) { return t == MACA_C_64F ? 16 : (t == MACA_R_64F || t == MACA_C_32F) ? 8 : 4; }
 bool too_big(int64_t v) { return (v >> 31) != 0; }  // int32 indices: every extent must fit
 
 bool descr_general(const mcsparseMatDescr* d) {
@@ -132,13 +134,17 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
           (!n_op && X->size == A->row_num && Y->size == A->col_num)))
         return BAD_SIZE;
     if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
-    // op(A) = A^T and CSC inputs run through a conversion into the buffer (32-bit CSR / CSC only).
-    if (!n_op && !(allow_transposed && opA == MCSPARSE_OPERATION_TRANSPOSE && narrow &&
+    // op(A) = A^T / A^H and CSC inputs run through a conversion into the buffer (32-bit CSR / CSC only).
+    if (!n_op && !(allow_transposed && narrow &&
                    (A->format == MCSPARSE_FORMAT_CSR || A->format == MCSPARSE_FORMAT_CSC)))
         return NOT_IMPL;
     if (A->format == MCSPARSE_FORMAT_CSC && !narrow) return NOT_IMPL;
+    // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
+    if (A->format == MCSPARSE_FORMAT_CSC && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
     if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType)) return NOT_IMPL;
-    if (!is_real_fp(computeType)) return NOT_IMPL;
+    if (!is_compute_type(computeType)) return NOT_IMPL;
+    // Complex values: the generic entry points only (the same that take transposed products), 32-bit indices.
+    if (is_complex_fp(computeType) && !(allow_transposed && narrow)) return NOT_IMPL;
     return OK;
 }
 
@@ -157,7 +163,7 @@ bool probe_small_tiles(mcsparseContext* h, const int32_t* idx, int64_t nnz, int6
         near = 4096;
     bool small = near < 1024;
     // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
-    const int64_t large = vsize == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    const int64_t large = spmv_workspace(rows, nnz, vsize, false).items_per_tile;
     if ((rows + nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) small = true;
     return small;
 }
@@ -173,7 +179,7 @@ bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, const void* i
     std::lock_guard<std::mutex> g(A->lock);
     if (A->probed_cols == idx && A->probed_nnz == A->nnz) return A->small_tiles;
     A->small_tiles = probe_small_tiles(h, static_cast<const int32_t*>(idx), A->nnz, rows,
-                                       A->valueType == MACA_R_64F ? 8 : 4, scratch);
+                                       value_size(A->valueType), scratch);
     A->probed_cols = idx;
     A->probed_nnz = A->nnz;
     return A->small_tiles;
@@ -206,11 +212,13 @@ struct CsrView {
     const void* ptr = nullptr;
     const void* idx = nullptr;
     bool transposed = false;
+    bool conjugate = false;  // op(A) = A^H on complex values
 };
 
 CsrView csr_view(const mcsparseSpMatDescr* A, mcsparseOperation_t opA) {
     CsrView v;
     const bool t_op = opA != MCSPARSE_OPERATION_NON_TRANSPOSE;
+    v.conjugate = opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE && is_complex_fp(A->valueType);
     if (A->format == MCSPARSE_FORMAT_CSC) {
         v.m = A->col_num, v.n = A->row_num, v.ptr = A->cols, v.idx = A->rows, v.transposed = !t_op;
     } else {
@@ -318,7 +326,7 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
         }
     }
     if (preprocess_only) return OK;
-    cudaError_t e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area);
+    cudaError_t e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area, v.conjugate);
     if (e != cudaSuccess) return from_cuda(e);
     e = spmv_tiled<T, int32_t>(h->stream, v.n, nnz, 0, t_ptr, t_idx, t_val, static_cast<const T*>(X->values),
                                static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, L.work);
@@ -339,9 +347,12 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     DeviceGuard guard(h->device);
     const CsrView view = csr_view(A, opA);
     if (view.transposed) {
-        if (computeType == MACA_R_64F)
-            return spmv_transposed_run<double>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
-        return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+        switch (computeType) {
+            case MACA_R_64F: return spmv_transposed_run<double>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            case MACA_C_32F: return spmv_transposed_run<cfloat>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            case MACA_C_64F: return spmv_transposed_run<cdouble>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            default: return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+        }
     }
     const bool small = choose_small_tiles(h, A, view.idx, view.m, align_up_256(buffer));
     const int ipt = spmv_workspace(view.m, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
@@ -358,6 +369,10 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         }
     }
     const bool wide = index_size(A) == 8;
+    if (computeType == MACA_C_32F)
+        return spmv_run<cfloat, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+    if (computeType == MACA_C_64F)
+        return spmv_run<cdouble, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
     if (computeType == MACA_R_64F)
         return wide ? spmv_run<double, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
                     : spmv_run<double, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
@@ -410,7 +425,8 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
         return NOT_IMPL;
     if (A->format != MCSPARSE_FORMAT_CSR) return NOT_IMPL;
     if (!(computeType == A->valueType && computeType == C->valueType && computeType == B->valueType)) return NOT_IMPL;
-    if (!is_real_fp(computeType)) return NOT_IMPL;
+    if (!is_compute_type(computeType)) return NOT_IMPL;
+    if (is_complex_fp(computeType) && A->rowIdxType != MCSPARSE_INDEX_32I) return NOT_IMPL;
     if (opA != MCSPARSE_OPERATION_NON_TRANSPOSE) return NOT_IMPL;  // :105
     if (opB == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
     // Shapes: op(B) is A.cols x C.cols, C is A.rows x C.cols. The reference trusts the caller
@@ -1131,7 +1147,7 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
     if (matA == nullptr || externalBuffer == nullptr || itemsPerTile == nullptr || numTiles == nullptr ||
         tileStarts == nullptr)
         return pub(BAD_POINTER);
-    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
     const SpmvWorkspace ws =
         spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
     *itemsPerTile = ws.items_per_tile;
@@ -1144,7 +1160,7 @@ mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMa
                                            void* externalBuffer, int* status) {
     if (handle == nullptr) return pub(BAD_HANDLE);
     if (matA == nullptr || externalBuffer == nullptr || status == nullptr) return pub(BAD_POINTER);
-    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
     const SpmvWorkspace ws =
         spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
@@ -1160,7 +1176,7 @@ mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcspa
     if (matA == nullptr || externalBuffer == nullptr || rows == nullptr || rowOffsets == nullptr || colInd == nullptr ||
         values == nullptr)
         return pub(BAD_POINTER);
-    if (!is_real_fp(matA->valueType)) return pub(NOT_IMPL);
+    if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
     const CsrView view = csr_view(matA, opA);
     if (!view.transposed) return pub(BAD_VALUE);
     const TransposedLayout L = transposed_layout(view, matA->nnz, value_size(matA->valueType), externalBuffer);
@@ -1295,6 +1311,10 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
         }
     }
     const bool wide = index_size(matA) == 8;
+    if (computeType == MACA_C_32F)
+        return pub(spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+    if (computeType == MACA_C_64F)
+        return pub(spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
     if (computeType == MACA_R_64F)
         return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr)
                         : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));

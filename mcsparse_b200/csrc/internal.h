@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "mcsparse.h"
+#include "value_types.h"
 
 // Descriptor payloads. Field meaning follows the reference's structs
 // (mcsparse/src/include/mcsp_internal_types.h:86-92,127-145,184-223 and
@@ -222,9 +223,11 @@ TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_siz
 // Structure of the transposed matrix (row offsets, column indices, permutation) of an m x n CSR matrix.
 cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
                                 const int32_t* col, const TransposePlan& plan, void* buf);
-// Values of the transposed matrix, gathered through the permutation left by transpose_structure.
+// Values of the transposed matrix, gathered through the permutation left by transpose_structure
+// (conjugated on the way for op(A) = A^H).
 template <typename T>
-cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& plan, void* buf);
+cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& plan, void* buf,
+                             bool conjugate = false);
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host);
 cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,

@@ -30,6 +30,42 @@ struct VecOf<double> {
     static constexpr int W = 2;
 };
 
+template <>
+struct VecOf<cfloat> {  // two complex numbers per 128-bit access
+    using type = float4;
+    static constexpr int W = 2;
+};
+template <>
+struct VecOf<cdouble> {
+    using type = double2;
+    static constexpr int W = 1;
+};
+
+__device__ __forceinline__ void fma_vec(float4& acc, cfloat a, const float4& b) {
+    const cfloat lo = mad(a, cfloat(b.x, b.y), cfloat(acc.x, acc.y)), hi = mad(a, cfloat(b.z, b.w), cfloat(acc.z, acc.w));
+    acc = make_float4(lo.re, lo.im, hi.re, hi.im);
+}
+__device__ __forceinline__ void fma_vec(double2& acc, cdouble a, const double2& b) {
+    const cdouble r = mad(a, cdouble(b.x, b.y), cdouble(acc.x, acc.y));
+    acc = make_double2(r.re, r.im);
+}
+__device__ __forceinline__ float4 scale(cfloat alpha, const float4& a) {
+    const cfloat lo = alpha * cfloat(a.x, a.y), hi = alpha * cfloat(a.z, a.w);
+    return make_float4(lo.re, lo.im, hi.re, hi.im);
+}
+__device__ __forceinline__ double2 scale(cdouble alpha, const double2& a) {
+    const cdouble r = alpha * cdouble(a.x, a.y);
+    return make_double2(r.re, r.im);
+}
+__device__ __forceinline__ float4 axpby(cfloat alpha, const float4& a, cfloat beta, const float4& c) {
+    const float4 p = scale(alpha, a), q = scale(beta, c);
+    return make_float4(p.x + q.x, p.y + q.y, p.z + q.z, p.w + q.w);
+}
+__device__ __forceinline__ double2 axpby(cdouble alpha, const double2& a, cdouble beta, const double2& c) {
+    const double2 p = scale(alpha, a), q = scale(beta, c);
+    return make_double2(p.x + q.x, p.y + q.y);
+}
+
 __device__ __forceinline__ void fma_vec(float4& acc, float a, const float4& b) {
     acc.x = fmaf(a, b.x, acc.x);
     acc.y = fmaf(a, b.y, acc.y);
@@ -112,14 +148,14 @@ __global__ void __launch_bounds__(kThreads)
         T vj = T(0);
         if (j + lane < j1) {
             cj = (int)__ldcs(col + j + lane);
-            vj = __ldcs(val + j + lane);
+            vj = ldcs(val + j + lane);
         }
         const int cnt = min(G, j1 - j);
         const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) & ~(G - 1)));
 #pragma unroll 8
         for (int q = 0; q < cnt; ++q) {
             const int cq = __shfl_sync(gmask, cj, q, G);
-            const T vq = __shfl_sync(gmask, vj, q, G);
+            const T vq = shfl_idx(gmask, vj, q, G);
             if (col_ok) {
                 const V b = *reinterpret_cast<const V*>(Bc + (long long)cq * ldb);
                 fma_vec(acc, vq, b);
@@ -188,7 +224,7 @@ __global__ void __launch_bounds__(kThreads)
     const int j0 = (int)__ldg(row_ptr + r) - base, j1 = (int)__ldg(row_ptr + r + 1) - base;
     T sum = T(0);
     for (int j = j0; j < j1; ++j)
-        sum += __ldg(val + j) * __ldg(B + ((long long)__ldg(col + j) - base) * b_rs + c * b_cs);
+        sum += ldg(val + j) * ldg(B + ((long long)__ldg(col + j) - base) * b_rs + c * b_cs);
     const T alpha = alpha_arg.get(), beta = beta_arg.get();
     T* out = C + r * c_rs + c * c_cs;
     T v = alpha * sum;
@@ -284,6 +320,8 @@ INSTANTIATE(float, int32_t)
 INSTANTIATE(double, int32_t)
 INSTANTIATE(float, int64_t)
 INSTANTIATE(double, int64_t)
+INSTANTIATE(cfloat, int32_t)
+INSTANTIATE(cdouble, int32_t)
 #undef INSTANTIATE
 template cudaError_t spmm_preprocess<int32_t>(cudaStream_t, int64_t, int, const int32_t*, const int32_t*,
                                               const SpmmPlan&, void*);

@@ -12,6 +12,8 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include <type_traits>
+
 #include "internal.h"
 
 namespace mcsp_b200 {
@@ -22,13 +24,16 @@ constexpr int kThreads = 256;
 
 // Items per thread of the two tile sizes. With 64-bit column indices the staged columns take twice
 // the shared memory, so only the small tile is used.
+// The sizes go by the bytes of a value: 4 (float), 8 (double, complex float), 16 (complex double, one size).
+constexpr int tile_items(size_t value_size, bool small) {
+    return value_size == 4   ? (small ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32)
+           : value_size == 8 ? (small ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F64)
+                             : MCSPARSE_B200_SPMV_TILE_ITEMS_C64;
+}
 template <typename T, typename I>
 struct TileCfg {
-    static constexpr int kSmall =
-        (sizeof(T) == 8 ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32) / kThreads;
-    static constexpr int kLarge =
-        sizeof(I) == 8 ? kSmall
-                       : (sizeof(T) == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32) / kThreads;
+    static constexpr int kSmall = tile_items(sizeof(T), true) / kThreads;
+    static constexpr int kLarge = sizeof(I) == 8 ? kSmall : tile_items(sizeof(T), false) / kThreads;
 };
 
 // Column locality probe: 1024 threads x 4 samples.
@@ -124,10 +129,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
     return true;
 }
 
-// Explicit fused multiply-add: the same rounding in every instantiation of the kernels (left
-// to the compiler, contraction choices differed between template variants by one ulp).
-__device__ __forceinline__ float mad(float a, float b, float c) { return fmaf(a, b, c); }
-__device__ __forceinline__ double mad(double a, double b, double c) { return fma(a, b, c); }
 
 // PUSH variants: a finished y value is also stored, with ordinary global stores through
 // peer-mapped pointers, into the full-length y of every other GPU of a row-sharded run, at
@@ -314,7 +315,7 @@ __global__ void __launch_bounds__(THREADS)
         const bool mine = u < 8 ? (u < front) : (g < nz_e);
         if (mine) {
             if (is_val)
-                s_val[head_v + (g - nz_s)] = __ldcs(val + g);
+                s_val[head_v + (g - nz_s)] = ldcs(val + g);
             else
                 s_col[head_c + (g - nz_s)] = __ldcs(col + g);
         }
@@ -373,21 +374,21 @@ __global__ void __launch_bounds__(THREADS)
             T sum = T(0);
             int k = b + glane;
             for (; k + 3 * G < e; k += 4 * G) {  // four independent gathers in flight per lane
-                const T x0 = __ldg(xb + colv[k]), x1 = __ldg(xb + colv[k + G]);
-                const T x2 = __ldg(xb + colv[k + 2 * G]), x3 = __ldg(xb + colv[k + 3 * G]);
+                const T x0 = ldg(xb + colv[k]), x1 = ldg(xb + colv[k + G]);
+                const T x2 = ldg(xb + colv[k + 2 * G]), x3 = ldg(xb + colv[k + 3 * G]);
                 sum = mad(valv[k], x0, sum);
                 sum = mad(valv[k + G], x1, sum);
                 sum = mad(valv[k + 2 * G], x2, sum);
                 sum = mad(valv[k + 3 * G], x3, sum);
             }
-            for (; k < e; k += G) sum = mad(valv[k], __ldg(xb + colv[k]), sum);
-            for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+            for (; k < e; k += G) sum = mad(valv[k], ldg(xb + colv[k]), sum);
+            for (int d = G >> 1; d > 0; d >>= 1) sum += shfl_xor(sum, d);
             if (glane == 0 && i <= nrows) {
                 if (i < nrows) {
                     T v = alpha * sum;
                     if (beta != T(0)) v = mad(beta, y[row_s + i], v);
                     y[row_s + i] = v;
-                    if (PUSH) {
+                    if constexpr (PUSH) {
                         if (nrows <= PUSHCAP)
                             s_push[i] = v;
                         else
@@ -399,9 +400,11 @@ __global__ void __launch_bounds__(THREADS)
                 }
             }
         }
-        if (PUSH && nrows <= PUSHCAP) {
-            __syncthreads();
-            push_tile_rows<T, THREADS>(peers, s_push, row_s, nrows, tid);
+        if constexpr (PUSH) {
+            if (nrows <= PUSHCAP) {  // block-uniform
+                __syncthreads();
+                push_tile_rows<T, THREADS>(peers, s_push, row_s, nrows, tid);
+            }
         }
         return;
     }
@@ -414,7 +417,7 @@ __global__ void __launch_bounds__(THREADS)
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
             const int k = tid + j * THREADS;
-            xv[j] = (k < nnz_tile) ? __ldg(xb + colv[k]) : T(0);
+            xv[j] = (k < nnz_tile) ? ldg(xb + colv[k]) : T(0);
         }
 #pragma unroll
         for (int j = 0; j < IPT; ++j) {
@@ -458,7 +461,7 @@ __global__ void __launch_bounds__(THREADS)
     const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        const T up = __shfl_up_sync(0xffffffffu, sum, d);
+        const T up = shfl_up(sum, d);
         const int ru = __shfl_up_sync(0xffffffffu, r, d);
         if (lane >= d && ru == r) sum += up;
     }
@@ -481,9 +484,9 @@ __global__ void __launch_bounds__(THREADS)
         T v = alpha * s_y[i];
         if (beta != T(0)) v = mad(beta, y[row_s + i], v);
         y[row_s + i] = v;
-        if (PUSH) s_y[i] = v;  // only this thread touches s_y[i] here
+        if constexpr (PUSH) s_y[i] = v;  // only this thread touches s_y[i] here
     }
-    if (PUSH) {
+    if constexpr (PUSH) {
         const T open_sum = s_y[nrows];
         __syncthreads();
         push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
@@ -551,7 +554,7 @@ __global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* _
     for (long long u = t + 1; u < num_tiles && carry_row[u] == r; ++u) sum += carry_val[u];
     const T v = mad(alpha_arg.get(), sum, y[r]);
     y[r] = v;
-    if (PUSH) push_to_peers(peers, r, v);
+    if constexpr (PUSH) push_to_peers(peers, r, v);
 }
 
 // The same correction for the tiles [t0, t1) only, looking backwards: tile t finishes its first
@@ -590,10 +593,10 @@ __global__ void __launch_bounds__(kThreads)
     if (active) {
         const int j0 = (int)__ldg(row_ptr + gid) - base, j1 = (int)__ldg(row_ptr + gid + 1) - base;
         const T* xb = x - base;
-        for (int j = j0 + lane; j < j1; j += G) sum = mad(__ldcs(val + j), __ldg(xb + __ldcs(col + j)), sum);
+        for (int j = j0 + lane; j < j1; j += G) sum = mad(ldcs(val + j), ldg(xb + __ldcs(col + j)), sum);
     }
 #pragma unroll
-    for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, G);
+    for (int d = G >> 1; d > 0; d >>= 1) sum += shfl_xor(sum, d, G);
     if (active && lane == 0) {
         const T alpha = alpha_arg.get(), beta = beta_arg.get();
         T v = alpha * sum;
@@ -621,10 +624,8 @@ static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int 
 }
 
 SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles, size_t index_size) {
-    const int small = value_size == 8 ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32;
-    const int large = index_size == 8 ? small  // 64-bit indices: one tile size (see TileCfg)
-                      : value_size == 8 ? MCSPARSE_B200_SPMV_TILE_ITEMS_F64
-                                        : MCSPARSE_B200_SPMV_TILE_ITEMS_F32;
+    const int small = tile_items(value_size, true);
+    const int large = index_size == 8 ? small : tile_items(value_size, false);  // 64-bit indices: one tile size
     SpmvWorkspace ws = spmv_layout(m, nnz, value_size, small_tiles ? small : large);
     ws.bytes = spmv_layout(m, nnz, value_size, small).bytes;
     return ws;
@@ -692,17 +693,23 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
-    cudaError_t e = peers.count > 0 ? launch_tiles<T, true, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x,
-                                                              y, alpha, beta, ws, buf, peers)
-                                    : launch_tiles<T, false, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x,
-                                                               y, alpha, beta, ws, buf, peers);
+    if constexpr (std::is_floating_point<T>::value) {  // the row push exists for the real types only
+        if (peers.count > 0) {
+            cudaError_t e = launch_tiles<T, true, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha,
+                                                     beta, ws, buf, peers);
+            if (e != cudaSuccess) return e;
+            spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y,
+                                                                      alpha, peers);
+            return cudaGetLastError();
+        }
+    } else if (peers.count > 0) {
+        return cudaErrorInvalidValue;
+    }
+    cudaError_t e = launch_tiles<T, false, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws,
+                                              buf, peers);
     if (e != cudaSuccess) return e;
-    if (peers.count > 0)
-        spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
-                                                                  peers);
-    else
-        spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
-                                                                   peers);
+    spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
+                                                               peers);
     return cudaGetLastError();
 }
 
@@ -862,6 +869,8 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
                                                  ScalarArg<T>, const SpmvWorkspace&, void*, const PeerList<T>&);
 INSTANTIATE(float)
 INSTANTIATE(double)
+INSTANTIATE_TI(cfloat, int32_t)
+INSTANTIATE_TI(cdouble, int32_t)
 template cudaError_t spmv_analysis<int32_t>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const SpmvWorkspace&,
                                             void*);
 template cudaError_t spmv_analysis<int64_t>(cudaStream_t, int64_t, int64_t, int, const int64_t*, const SpmvWorkspace&,

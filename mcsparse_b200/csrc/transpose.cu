@@ -205,19 +205,24 @@ __global__ void owner_row_kernel(long long m, long long nnz, int base, const int
 template <typename T>
 __global__ void __launch_bounds__(256)
     permute_values_kernel(long long nnz, const T* __restrict__ val, const unsigned* __restrict__ perm,
-                          T* __restrict__ out) {
+                          T* __restrict__ out, bool conjugate) {
     const long long k = 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x);
     if (k + 3 < nnz) {
         const uint4 p = __ldcs(reinterpret_cast<const uint4*>(perm + k));
-        const T a = __ldg(val + p.x), b = __ldg(val + p.y), c = __ldg(val + p.z), d = __ldg(val + p.w);
-        if constexpr (sizeof(T) == 8) {
-            __stcs(reinterpret_cast<double2*>(out + k), make_double2(a, b));
-            __stcs(reinterpret_cast<double2*>(out + k + 2), make_double2(c, d));
-        } else {
-            __stcs(reinterpret_cast<float4*>(out + k), make_float4(a, b, c, d));
+        alignas(16) T v[4] = {ldg(val + p.x), ldg(val + p.y), ldg(val + p.z), ldg(val + p.w)};
+        if (conjugate) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = conj_value(v[i]);
         }
+        const uint4* src = reinterpret_cast<const uint4*>(v);
+        uint4* dst = reinterpret_cast<uint4*>(out + k);
+#pragma unroll
+        for (int i = 0; i < (int)(4 * sizeof(T) / 16); ++i) __stcs(dst + i, src[i]);
     } else {
-        for (long long i = k; i < nnz; ++i) out[i] = __ldg(val + perm[i]);
+        for (long long i = k; i < nnz; ++i) {
+            const T v = ldg(val + perm[i]);
+            out[i] = conjugate ? conj_value(v) : v;
+        }
     }
 }
 
@@ -293,15 +298,20 @@ cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nn
 }
 
 template <typename T>
-cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& p, void* buf) {
+cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& p, void* buf,
+                             bool conjugate) {
     if (nnz == 0) return cudaSuccess;
     char* b = static_cast<char*>(buf);
     permute_values_kernel<T><<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(
-        nnz, val, reinterpret_cast<const unsigned*>(b + p.off_perm[p.final_slot()]), reinterpret_cast<T*>(b + p.off_val));
+        nnz, val, reinterpret_cast<const unsigned*>(b + p.off_perm[p.final_slot()]), reinterpret_cast<T*>(b + p.off_val),
+        conjugate);
     return cudaGetLastError();
 }
 
-template cudaError_t transpose_values<float>(cudaStream_t, int64_t, const float*, const TransposePlan&, void*);
-template cudaError_t transpose_values<double>(cudaStream_t, int64_t, const double*, const TransposePlan&, void*);
+template cudaError_t transpose_values<float>(cudaStream_t, int64_t, const float*, const TransposePlan&, void*, bool);
+template cudaError_t transpose_values<double>(cudaStream_t, int64_t, const double*, const TransposePlan&, void*, bool);
+template cudaError_t transpose_values<cfloat>(cudaStream_t, int64_t, const cfloat*, const TransposePlan&, void*, bool);
+template cudaError_t transpose_values<cdouble>(cudaStream_t, int64_t, const cdouble*, const TransposePlan&, void*,
+                                               bool);
 
 }  // namespace mcsp_b200

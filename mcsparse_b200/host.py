@@ -11,7 +11,8 @@ import torch
 from . import capi
 from .capi import check, lib
 
-_DTYPE = {torch.float32: capi.MACA_R_32F, torch.float64: capi.MACA_R_64F}
+_DTYPE = {torch.float32: capi.MACA_R_32F, torch.float64: capi.MACA_R_64F,
+          torch.complex64: capi.MACA_C_32F, torch.complex128: capi.MACA_C_64F}
 
 
 def _ptr(t):
@@ -25,7 +26,11 @@ def _ptr(t):
 
 
 def _scalar(value, dtype):
-    """A host scalar of the compute type, as the C API expects behind ``const void*``."""
+    """A host scalar of the compute type, as the C API expects behind ``const void*``
+    (complex types: the real and the imaginary part, interleaved)."""
+    if dtype in (torch.complex64, torch.complex128):
+        z = complex(value)
+        return ((C.c_float if dtype == torch.complex64 else C.c_double) * 2)(z.real, z.imag)
     return (C.c_double if dtype == torch.float64 else C.c_float)(value)
 
 
@@ -143,7 +148,7 @@ def _scalars(handle, alpha, beta, dtype):
     if handle.pointer_mode == capi.MCSPARSE_POINTER_MODE_DEVICE:
         return _ptr(alpha), _ptr(beta), (alpha, beta)
     a, b = _scalar(alpha, dtype), _scalar(beta, dtype)
-    return C.cast(C.pointer(a), C.c_void_p), C.cast(C.pointer(b), C.c_void_p), (a, b)
+    return C.cast(C.byref(a), C.c_void_p), C.cast(C.byref(b), C.c_void_p), (a, b)
 
 
 def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):

@@ -97,6 +97,81 @@ static inline int64_t dn_index(int64_t r, int64_t c, int64_t ld, int order) {
 DEFINE_ORACLE_SPMM(oracle_csr_spmm_f32, float, double)
 DEFINE_ORACLE_SPMM(oracle_csr_spmm_f64, double, long double)
 
+/* ------------------------------------------------------------------ complex oracles
+ *
+ * Values, x, y, B and C are interleaved (re, im) pairs, as MACA_C_32F / MACA_C_64F lay them out
+ * (mcspComplexFloat / mcspComplexDouble, mcsparse/src/include/mcsp_internal_types.h); the row loop
+ * and the epilogue are those of the real kernels above (csr_vector_device.hpp:35-57,66-77), on
+ * complex numbers. `conj_a` multiplies with conj(a) (what op(A) = A^H does after transposition).
+ * Outputs: y_out interleaved in double, d_out = |alpha| sum |a||x| + |beta||y0| with complex moduli. */
+#define DEFINE_ORACLE_SPMV_C(NAME, VT, ACC)                                                             \
+    void NAME(int64_t m, int base, const int32_t* row_ptr, const int32_t* col, const VT* val, const VT* x, \
+              const double* alpha, const double* beta, int conj_a, const VT* y_in, double* y_out,        \
+              double* d_out) {                                                                           \
+        const double abs_alpha = hypot(alpha[0], alpha[1]), abs_beta = hypot(beta[0], beta[1]);          \
+        _Pragma("omp parallel for schedule(dynamic, 4096)") for (int64_t r = 0; r < m; ++r) {            \
+            ACC sr = 0, si = 0, d = 0;                                                                   \
+            for (int64_t j = (int64_t)row_ptr[r] - base; j < (int64_t)row_ptr[r + 1] - base; ++j) {      \
+                const int64_t c = (int64_t)col[j] - base;                                                \
+                const ACC ar = val[2 * j], ai = conj_a ? -(ACC)val[2 * j + 1] : (ACC)val[2 * j + 1];     \
+                const ACC xr = x[2 * c], xi = x[2 * c + 1];                                              \
+                sr += ar * xr - ai * xi;                                                                 \
+                si += ar * xi + ai * xr;                                                                 \
+                d += (ACC)hypotl((long double)ar, (long double)ai) * (ACC)hypotl((long double)xr, (long double)xi); \
+            }                                                                                            \
+            ACC outr = (ACC)alpha[0] * sr - (ACC)alpha[1] * si, outi = (ACC)alpha[0] * si + (ACC)alpha[1] * sr; \
+            ACC dd = (ACC)abs_alpha * d;                                                                 \
+            if (abs_beta != 0.0) {                                                                       \
+                const ACC yr = y_in[2 * r], yi = y_in[2 * r + 1];                                        \
+                outr += (ACC)beta[0] * yr - (ACC)beta[1] * yi;                                           \
+                outi += (ACC)beta[0] * yi + (ACC)beta[1] * yr;                                           \
+                dd += (ACC)abs_beta * (ACC)hypotl((long double)yr, (long double)yi);                     \
+            }                                                                                            \
+            y_out[2 * r] = (double)outr;                                                                 \
+            y_out[2 * r + 1] = (double)outi;                                                             \
+            if (d_out) d_out[r] = (double)dd;                                                            \
+        }                                                                                                \
+    }
+
+DEFINE_ORACLE_SPMV_C(oracle_csr_spmv_c32, float, double)
+DEFINE_ORACLE_SPMV_C(oracle_csr_spmv_c64, double, long double)
+
+/* C_out (interleaved) and d_out are dense m x n row-major with leading dimension n, whatever C's order
+ * (mcsparse/src/kernels/level3/spmm/csr_spmm_device.hpp:116-137,149-165 on complex numbers). */
+#define DEFINE_ORACLE_SPMM_C(NAME, VT, ACC)                                                             \
+    void NAME(int64_t m, int64_t n, int base, const int32_t* row_ptr, const int32_t* col, const VT* val, \
+              const VT* B, int64_t ldb, int orderB, const double* alpha, const double* beta, const VT* C_in, \
+              int64_t ldc, int orderC, double* C_out, double* d_out) {                                   \
+        const double abs_alpha = hypot(alpha[0], alpha[1]), abs_beta = hypot(beta[0], beta[1]);          \
+        _Pragma("omp parallel for schedule(dynamic, 256)") for (int64_t r = 0; r < m; ++r) {             \
+            for (int64_t c = 0; c < n; ++c) {                                                            \
+                ACC sr = 0, si = 0, d = 0;                                                               \
+                for (int64_t j = (int64_t)row_ptr[r] - base; j < (int64_t)row_ptr[r + 1] - base; ++j) {  \
+                    const int64_t bi = dn_index((int64_t)col[j] - base, c, ldb, orderB);                 \
+                    const ACC ar = val[2 * j], ai = val[2 * j + 1], br = B[2 * bi], bim = B[2 * bi + 1]; \
+                    sr += ar * br - ai * bim;                                                            \
+                    si += ar * bim + ai * br;                                                            \
+                    d += (ACC)hypotl((long double)ar, (long double)ai) * (ACC)hypotl((long double)br, (long double)bim); \
+                }                                                                                        \
+                ACC outr = (ACC)alpha[0] * sr - (ACC)alpha[1] * si, outi = (ACC)alpha[0] * si + (ACC)alpha[1] * sr; \
+                ACC dd = (ACC)abs_alpha * d;                                                             \
+                if (abs_beta != 0.0) {                                                                   \
+                    const int64_t ci = dn_index(r, c, ldc, orderC);                                      \
+                    const ACC cr = C_in[2 * ci], cim = C_in[2 * ci + 1];                                 \
+                    outr += (ACC)beta[0] * cr - (ACC)beta[1] * cim;                                      \
+                    outi += (ACC)beta[0] * cim + (ACC)beta[1] * cr;                                      \
+                    dd += (ACC)abs_beta * (ACC)hypotl((long double)cr, (long double)cim);                \
+                }                                                                                        \
+                C_out[2 * (r * n + c)] = (double)outr;                                                   \
+                C_out[2 * (r * n + c) + 1] = (double)outi;                                               \
+                if (d_out) d_out[r * n + c] = (double)dd;                                                \
+            }                                                                                            \
+        }                                                                                                \
+    }
+
+DEFINE_ORACLE_SPMM_C(oracle_csr_spmm_c32, float, double)
+DEFINE_ORACLE_SPMM_C(oracle_csr_spmm_c64, double, long double)
+
 /* ------------------------------------------------------------------ analysis oracle
  *
  * Merge-path work partition. The reference's analysis hook is an empty stub

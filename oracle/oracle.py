@@ -52,14 +52,32 @@ def _vt(val):
         return "f32"
     if val.dtype == np.float64:
         return "f64"
+    if val.dtype == np.complex64:
+        return "c32"
+    if val.dtype == np.complex128:
+        return "c64"
     raise TypeError(val.dtype)
 
 
-def spmv(row_ptr, col, val, x, alpha, beta, y0=None, base=0):
-    """High-precision y = alpha A x + beta y0 and the tolerance scale d. Returns (y, d) as float64."""
+def _pair(z):
+    z = complex(z)
+    return np.array([z.real, z.imag], np.float64)
+
+
+def spmv(row_ptr, col, val, x, alpha, beta, y0=None, base=0, conj=False):
+    """High-precision y = alpha A x + beta y0 and the tolerance scale d. Returns (y, d): float64, or
+    complex128 and float64 for complex values (`conj` multiplies with conj(A))."""
     row_ptr, col, val, x = _np(row_ptr, np.int32), _np(col, np.int32), _np(val), _np(x)
     m = row_ptr.size - 1
     y_in = _np(y0).astype(val.dtype, copy=False) if y0 is not None else np.zeros(max(m, 1), val.dtype)
+    if np.iscomplexobj(val):
+        x = x.astype(val.dtype, copy=False)
+        y = np.empty(m, np.complex128)
+        d = np.empty(m, np.float64)
+        a, b = _pair(alpha), _pair(beta if y0 is not None else 0.0)
+        getattr(lib(), "oracle_csr_spmv_" + _vt(val))(C.c_int64(m), C.c_int(base), _p(row_ptr), _p(col), _p(val), _p(x),
+                                                      _p(a), _p(b), C.c_int(int(conj)), _p(y_in), _p(y), _p(d))
+        return y, d
     y = np.empty(m, np.float64)
     d = np.empty(m, np.float64)
     fn = getattr(lib(), "oracle_csr_spmv_" + _vt(val))
@@ -75,6 +93,14 @@ def spmm(row_ptr, col, val, B, ldb, order_b, n, alpha, beta, C0=None, ldc=None, 
     m = row_ptr.size - 1
     ldc = n if ldc is None else ldc
     c_in = _np(C0).ravel().astype(val.dtype, copy=False) if C0 is not None else np.zeros(1, val.dtype)
+    if np.iscomplexobj(val):
+        B = B.astype(val.dtype, copy=False)
+        out, d = np.empty((m, n), np.complex128), np.empty((m, n), np.float64)
+        a, b = _pair(alpha), _pair(beta if C0 is not None else 0.0)
+        getattr(lib(), "oracle_csr_spmm_" + _vt(val))(C.c_int64(m), C.c_int64(n), C.c_int(base), _p(row_ptr), _p(col),
+                                                      _p(val), _p(B), C.c_int64(ldb), C.c_int(order_b), _p(a), _p(b),
+                                                      _p(c_in), C.c_int64(ldc), C.c_int(order_c), _p(out), _p(d))
+        return out, d
     out = np.empty((m, n), np.float64)
     d = np.empty((m, n), np.float64)
     fn = getattr(lib(), "oracle_csr_spmm_" + _vt(val))

@@ -47,5 +47,46 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_complex():
+    """tests/golden/csr_cases_complex.npz: the same kind of cases with complex values and complex alpha, beta,
+    plus the product with the conjugate-transposed matrix (what op(A) = A^H computes)."""
+    out = {}
+    rng = np.random.default_rng(20240608)
+
+    def cplx(shape, dt):
+        return (rng.uniform(-1, 1, shape) + 1j * rng.uniform(-1, 1, shape)).astype(dt)
+
+    cases = [
+        ("c32_b0", np.complex64, 0, [3, 0, 5, 1, 0, 8, 2, 33, 0, 4], 40, 1.0 - 0.5j, 0.0),
+        ("c32_b1", np.complex64, 1, [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 0, 0, 64], 70, -0.5 + 2.0j, 2.0 - 1.0j),
+        ("c64_b0", np.complex128, 0, [16] * 50 + [0, 0, 100], 128, 1.0, 0.5j),
+        ("c64_b1", np.complex128, 1, [0, 0, 0, 7, 300, 1], 301, 2.25 + 0.75j, -1.0),
+    ]
+    for name, dt, base, lengths, ncols, alpha, beta in cases:
+        rp, col, val = csr_from_lengths(lengths, ncols, dt, seed=len(name) + base, base=base)
+        m = len(lengths)
+        x, y0 = cplx(ncols, dt), cplx(m, dt)
+        wide = np.complex128
+        A = sp.csr_matrix((val.astype(wide), col.astype(np.int64) - base, rp.astype(np.int64) - base), shape=(m, ncols))
+        y = alpha * (A @ x.astype(wide)) + beta * y0.astype(wide)
+        absA = abs(A)
+        d = abs(alpha) * (absA @ np.abs(x.astype(wide))) + abs(beta) * np.abs(y0.astype(wide))
+        xh, yh0 = cplx(m, dt), cplx(ncols, dt)
+        AH = A.conj().T.tocsr()
+        yh = alpha * (AH @ xh.astype(wide)) + beta * yh0.astype(wide)
+        dh = abs(alpha) * (abs(AH) @ np.abs(xh.astype(wide))) + abs(beta) * np.abs(yh0.astype(wide))
+        n = 6
+        B, C0 = cplx((ncols, n), dt), cplx((m, n), dt)
+        Cx = alpha * (A @ B.astype(wide)) + beta * C0.astype(wide)
+        dC = abs(alpha) * (absA @ np.abs(B.astype(wide))) + abs(beta) * np.abs(C0.astype(wide))
+        for k, v in dict(row_ptr=rp, col=col, val=val, x=x, y0=y0, y=y, d=d, xh=xh, yh0=yh0, yh=yh, dh=dh, B=B, C0=C0,
+                         C=Cx, dC=dC, meta=np.array([base, ncols, alpha, beta], np.complex128)).items():
+            out[f"{name}.{k}"] = v
+    path = os.path.join(os.path.dirname(__file__), "csr_cases_complex.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
+    main_complex()

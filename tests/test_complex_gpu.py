@@ -1,0 +1,140 @@
+"""GPU parity tests of the complex value types (MACA_C_32F / MACA_C_64F) of mcsparseSpMV and mcsparseSpMM."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import mcsparse_b200 as mc
+from mcsparse_b200 import capi
+from mcsparse_b200.capi import lib
+from oracle import oracle
+from tests.util import ADVERSARIAL_LENGTHS, TOL, assert_close, csr_from_lengths
+
+pytestmark = pytest.mark.gpu
+N, T, H = (capi.MCSPARSE_OPERATION_NON_TRANSPOSE, capi.MCSPARSE_OPERATION_TRANSPOSE,
+           capi.MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE)
+ROW, COL = capi.MCSPARSE_ORDER_ROW, capi.MCSPARSE_ORDER_COL
+MACA = {np.complex64: capi.MACA_C_32F, np.complex128: capi.MACA_C_64F}
+
+
+def cplx(rng, shape, dtype):
+    return (rng.uniform(-1, 1, shape) + 1j * rng.uniform(-1, 1, shape)).astype(dtype)
+
+
+def up(a, device):
+    t = torch.empty(a.size + 1, dtype=torch.from_numpy(a[:0]).dtype, device=device)
+    t[:a.size] = torch.from_numpy(a).to(device)
+    return t[:a.size]
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("beta", [0.0, -0.75 + 0.5j])
+@pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
+def test_complex_spmv(handle, device, name, dtype, base, beta):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, n = len(lengths), max(max(lengths), 1) + 17
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=29, base=base)
+    rng = np.random.default_rng(12)
+    x, y0 = cplx(rng, n, dtype), cplx(rng, m, dtype)
+    A = mc.CsrMatrix(m, n, up(rp, device), up(col, device), up(val, device), base=base)
+    d_y = up(y0.copy(), device)
+    X, Y = mc.DnVec(up(x, device)), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+    alpha = 1.25 - 0.5j
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(rp, col, val, x, alpha, beta, y0, base=base)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], name)
+    # the work partition for this value type's tile size is bit-exact against the CPU partition
+    items, nt, p = C.c_int(), C.c_int64(), C.c_void_p()
+    capi.check(lib.mcsparseB200SpMVPartitionView(A.d, C.c_void_p(buf.data_ptr()), C.byref(items), C.byref(nt), C.byref(p)))
+    assert items.value in capi.SPMV_TILE_ITEMS[MACA[dtype]]
+    part = oracle.merge_path_partition(rp, col.size, items.value, base)
+    off = p.value - buf.data_ptr()
+    got = buf[off:off + part.size * 4].view(torch.int32).cpu().numpy().reshape(-1, 2)
+    np.testing.assert_array_equal(got, part)
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+@pytest.mark.parametrize("op", [T, H])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle", "mixed_medium_long"])
+def test_complex_spmv_transposed(handle, device, name, dtype, op):
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, n = len(lengths), max(max(lengths), 1) + 9
+    base = 1
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=31, base=base)
+    rng = np.random.default_rng(13)
+    x, y0 = cplx(rng, m, dtype), cplx(rng, n, dtype)
+    A = mc.CsrMatrix(m, n, up(rp, device), up(col, device), up(val, device), base=base)
+    d_y = up(y0.copy(), device)
+    X, Y = mc.DnVec(up(x, device)), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=op), dtype=torch.uint8, device=device)
+    alpha, beta = -0.5 + 2.0j, 0.25 - 1.0j
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=beta, op=op)
+    torch.cuda.synchronize()
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+    ref, d = oracle.spmv(t_ptr, t_idx, val[perm], x, alpha, beta, y0, conj=(op == H))
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], f"{name} op {op}")
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+@pytest.mark.parametrize("n,order", [(1, ROW), (2, ROW), (3, ROW), (8, ROW), (64, ROW), (5, COL)])
+def test_complex_spmm(handle, device, dtype, n, order):
+    lengths = ADVERSARIAL_LENGTHS["lengths_1_to_33"] + ADVERSARIAL_LENGTHS["empty_start_mid_end"] + [300]
+    k, m, base = 400, None, n % 2
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=n, base=base)
+    m = len(lengths)
+    rng = np.random.default_rng(n)
+    ldb = (n if order == ROW else k) + (2 if n == 3 else 0)
+    ldc = n if order == ROW else m
+    majorB, majorC = (k, m) if order == ROW else (n, n)
+    B = cplx(rng, majorB * ldb, dtype)
+    C0 = cplx(rng, majorC * ldc, dtype)
+    t = [up(a, device) for a in (rp, col, val, B, C0.copy())]
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2], base=base)
+    Bm, Cm = mc.DnMat(t[3], k, n, ldb, order), mc.DnMat(t[4], m, n, ldc, order)
+    buf = torch.empty(256, dtype=torch.uint8, device=device)
+    alpha, beta = 0.75 + 0.25j, -0.5 + 1.5j
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=alpha, beta=beta)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, B, ldb, order, n, alpha, beta, C0, ldc, order, base=base)
+    raw = t[4].cpu().numpy()
+    got = raw.reshape(m, ldc)[:, :n] if order == ROW else raw.reshape(n, ldc)[:, :m].T
+    assert_close(got, ref, d, TOL[np.dtype(dtype)], f"complex SpMM n={n}")
+
+
+def test_complex_refusals(handle, device):
+    """Complex values on the entry points that stay real-only, with 64-bit indices, or as A^H of a CSC matrix."""
+    rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.complex64)
+    t = [up(a, device) for a in (rp, col, val)]
+    A = mc.CsrMatrix(4, 5, *t)
+    A64 = mc.CsrMatrix(4, 5, t[0].long(), t[1].long(), t[2])
+    x, y = torch.ones(5, dtype=torch.complex64, device=device), torch.zeros(4, dtype=torch.complex64, device=device)
+    X, Y = mc.DnVec(x), mc.DnVec(y)
+    one = (C.c_float * 2)(1.0, 0.0)
+    pa = C.cast(C.byref(one), C.c_void_p)
+    size = C.c_size_t()
+    c32 = capi.MACA_C_32F
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0, C.byref(size)) == 0
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A64.d, X.d, pa, Y.d, c32, 0,
+                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert lib.mcsparseB200SpMVNoAlloc(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    csc = mc.CscMatrix.__new__(mc.CscMatrix)  # a CSC descriptor over the same arrays, only to query the status
+    d = C.c_void_p()
+    capi.check(lib.mcsparseCreateCsc(C.byref(d), 4, 5, 6, C.c_void_p(t[0].data_ptr()), C.c_void_p(t[1].data_ptr()),
+                                     C.c_void_p(t[2].data_ptr()), capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, 0,
+                                     c32))
+    csc.d = d
+    assert lib.mcsparseSpMV_bufferSize(handle.h, H, pa, d, Y.d, pa, X.d, c32, 0,
+                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    # real values with op(A) = A^H stay an invalid combination, as in the reference
+    rpr, colr, valr = csr_from_lengths([2, 3, 0, 1], 5, np.float32)
+    Ar = mc.CsrMatrix(4, 5, *[up(a, device) for a in (rpr, colr, valr)])
+    Xr, Yr = mc.DnVec(torch.ones(4, device=device)), mc.DnVec(torch.zeros(5, device=device))
+    onef = C.c_float(1.0)
+    assert lib.mcsparseSpMV_bufferSize(handle.h, H, C.byref(onef), Ar.d, Xr.d, C.byref(onef), Yr.d, capi.MACA_R_32F, 0,
+                                       C.byref(size)) == capi.MCSPARSE_STATUS_INVALID_VALUE

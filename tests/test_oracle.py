@@ -201,3 +201,26 @@ def test_csr_transpose_matches_scipy():
             np.testing.assert_array_equal(t_idx, ref.indices)
             np.testing.assert_array_equal(val[perm], ref.data)
             assert sorted(perm.tolist()) == list(range(col.size))
+
+
+GOLDEN_C = np.load(os.path.join(os.path.dirname(__file__), "golden", "csr_cases_complex.npz"))
+CASES_C = sorted({k.split(".")[0] for k in GOLDEN_C.files})
+
+
+@pytest.mark.parametrize("case", CASES_C)
+def test_complex_oracle_matches_golden(case):
+    gc = lambda key: GOLDEN_C[f"{case}.{key}"]
+    base, _, alpha, beta = gc("meta")
+    base = int(base.real)
+    y, d = oracle.spmv(gc("row_ptr"), gc("col"), gc("val"), gc("x"), alpha, beta, gc("y0"), base=base)
+    assert_close(y, gc("y"), gc("d"), 1e-14, case)
+    np.testing.assert_allclose(d, gc("d"), rtol=1e-13)
+    # conjugate-transposed product: transpose on the CPU, then multiply with conj(values)
+    n = gc("x").size
+    t_ptr, t_idx, perm = oracle.csr_transpose(gc("row_ptr"), gc("col"), n, base)
+    yh, dh = oracle.spmv(t_ptr, t_idx, gc("val")[perm], gc("xh"), alpha, beta, gc("yh0"), conj=True)
+    assert_close(yh, gc("yh"), gc("dh"), 1e-14, case + " A^H")
+    B, C0 = gc("B"), gc("C0")
+    out, dC = oracle.spmm(gc("row_ptr"), gc("col"), gc("val"), B, B.shape[1], 2, B.shape[1], alpha, beta, C0,
+                          B.shape[1], 2, base=base)
+    assert_close(out, gc("C"), gc("dC"), 1e-14, case + " SpMM")

@@ -4,7 +4,8 @@ import numpy as np
 import torch
 
 TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12,
-       torch.float32: 1e-5, torch.float64: 1e-12}
+       np.dtype(np.complex64): 1e-5, np.dtype(np.complex128): 1e-12,
+       torch.float32: 1e-5, torch.float64: 1e-12, torch.complex64: 1e-5, torch.complex128: 1e-12}
 
 
 def csr_from_lengths(lengths, ncols, dtype, seed=0, base=0):
@@ -18,12 +19,14 @@ def csr_from_lengths(lengths, ncols, dtype, seed=0, base=0):
         if L:
             col[row_ptr[r]:row_ptr[r + 1]] = np.sort(rng.choice(ncols, size=L, replace=False))
     val = rng.uniform(-1, 1, size=row_ptr[-1]).astype(dtype)
+    if np.iscomplexobj(val):
+        val = (val + 1j * rng.uniform(-1, 1, size=row_ptr[-1])).astype(dtype)
     return (row_ptr + base).astype(np.int32), col + np.int32(base), val
 
 
 def assert_close(got, ref, d, tol, what=""):
     """|got - ref| <= tol * d elementwise (d = |alpha| sum |a||x| + |beta||y0|)."""
-    got = np.asarray(got, dtype=np.float64)
+    got = np.asarray(got, dtype=np.complex128 if np.iscomplexobj(ref) or np.iscomplexobj(got) else np.float64)
     err = np.abs(got - ref)
     bad = ~(err <= tol * d + 1e-300)
     if bad.any():
