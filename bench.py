@@ -399,6 +399,19 @@ def run_gpu(args, rank, world, local_rank):
             print(json.dumps(r), flush=True)
         return
 
+    if args.transposed:  # y = A^T x through the conversion: single GPU, one compact line
+        if rank == 0:
+            j = TransposedSpmvJob(args.workload, device, h, args.scale)
+            r = measure_job(torch, j, args.steps, args.warmup, peak, flush_buf)
+            r.update({"metric": METRIC, "value": r["gbs"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "higher_is_better": True, "dtype": "f64" if j.vsize == 8 else "f32",
+                      "data": "synthetic", "conversion_ms_once": round(j.preprocess_ms, 3),
+                      "buffer_bytes": j.buf.numel(),
+                      "config": {"workload": workload_label(args.workload) + " transposed (op(A) = A^T)"
+                                 + ("" if args.scale == 1 else f" / {args.scale}")}})
+            print(json.dumps(r), flush=True)
+        return
+
     job = SpmvJob(args.workload, device, rank, world, h, args.scale)
     flush = flush_buf if job.local_bytes < 4 * L2_BYTES else None
 
@@ -557,6 +570,8 @@ def main():
     ap.add_argument("--scale", type=int, default=1, help="shrink the workload's rows by this factor (profiling)")
     ap.add_argument("--e2e-depth", type=int, default=3,
                     help="independent products kept in flight by the end-to-end (host buffer) measurement")
+    ap.add_argument("--transposed", action="store_true",
+                    help="time y = A^T x (conversion once, then value gather + SpMV per step) instead of y = A x")
     ap.add_argument("--quick", action="store_true", help="tuning runs: skip the comparison timings")
     ap.add_argument("--headline-only", action="store_true", help="skip the per-configuration block at N=1")
     args = ap.parse_args()
