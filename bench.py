@@ -293,7 +293,7 @@ def measure_job(torch, job, steps, warmup, peak, flush_buf):
     return out
 
 
-def cpu_baseline(name, seconds=8.0, steps=None, warmup=1):
+def cpu_baseline(name, seconds=12.0, steps=None, warmup=1):
     """Times the OpenMP CSR kernel of oracle/ on a bounded row block of the workload (host cores)."""
     import numpy as np
     import torch
@@ -331,7 +331,7 @@ def cpu_baseline(name, seconds=8.0, steps=None, warmup=1):
     fn()
     one = time.perf_counter() - t
     if steps is None:
-        steps = int(min(50, max(3, seconds / max(one, 1e-6))))
+        steps = int(min(20000, max(3, seconds / max(one, 1e-6))))  # about `seconds` of CPU work
     t = time.perf_counter()
     for _ in range(steps):
         fn()

@@ -7,7 +7,7 @@
  * mcSparse source tree : line).
  *
  * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO or MCSPARSE_FORMAT_CSC
- * as an input of mcsparseSpMV), MCSPARSE_OPERATION_NON_TRANSPOSE (mcsparseSpMV: also
+ * as an input of mcsparseSpMV / mcsparseSpMM), MCSPARSE_OPERATION_NON_TRANSPOSE (mcsparseSpMV: also
  * MCSPARSE_OPERATION_TRANSPOSE, through a conversion into the external buffer),
  * MACA_R_32F / MACA_R_64F / MACA_C_32F / MACA_C_64F (complex: 32-bit indices; mcsparseSpMV also takes
  * MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE), offsets and columns both MCSPARSE_INDEX_32I or (CSR only) both
@@ -23,6 +23,7 @@
 
 #include <cuda_runtime_api.h> /* cudaStream_t */
 #include <library_types.h>    /* libraryPropertyType: MAJOR_VERSION, MINOR_VERSION, PATCH_LEVEL */
+#include <cuComplex.h>        /* interleaved (re, im) pairs behind mcComplex / mcDoubleComplex */
 
 #ifdef __cplusplus
 extern "C" {
@@ -316,9 +317,16 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
                               const void* beta, mcsparseDnMatDescr_t matC, macaDataType computeType,
                               mcsparseSpMMAlg_t alg, void* externalBuffer);
 
+/* Complex scalars and arrays of the legacy entry points: the MetaX SDK's mcComplex / mcDoubleComplex
+ * (common/mcComplex.h, used by mcsparse/include/interface/mcsp_level2.h:36-44) have the layout of
+ * cuComplex / cuDoubleComplex. */
+typedef cuComplex mcComplex;
+typedef cuComplex mcFloatComplex;
+typedef cuDoubleComplex mcDoubleComplex;
+
 /* ---- Legacy entry points onto the same kernels.
- * Reference: mcsparse/include/interface/mcsp_level2.h:10-34 and
- * mcsparse/include/interface/mcsp_level3.h:138-169; forwarding
+ * Reference: mcsparse/include/interface/mcsp_level2.h:10-44 and
+ * mcsparse/include/interface/mcsp_level3.h:138-181; forwarding
  * mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:905-953. The S/D csrmv calls take
  * no work buffer, so they run the thread-group-per-row kernel that needs no partition. ---- */
 mcsparseStatus_t mcsparseScsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
@@ -329,6 +337,14 @@ mcsparseStatus_t mcsparseDcsrmv(mcsparseHandle_t handle, mcsparseOperation_t tra
                                 const double* alpha, const mcsparseMatDescr_t descrA, const double* csrValA,
                                 const int* csrRowPtrA, const int* csrColIndA, const double* x, const double* beta,
                                 double* y);
+mcsparseStatus_t mcsparseCcsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const mcComplex* alpha, const mcsparseMatDescr_t descrA, const mcComplex* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const mcComplex* x,
+                                const mcComplex* beta, mcComplex* y);
+mcsparseStatus_t mcsparseZcsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const mcDoubleComplex* alpha, const mcsparseMatDescr_t descrA,
+                                const mcDoubleComplex* csrValA, const int* csrRowPtrA, const int* csrColIndA,
+                                const mcDoubleComplex* x, const mcDoubleComplex* beta, mcDoubleComplex* y);
 mcsparseStatus_t mcsparseCsrmvEx_bufferSize(mcsparseHandle_t handle, mcsparseAlgMode_t alg,
                                             mcsparseOperation_t transA, int m, int n, int nnz, const void* alpha,
                                             macaDataType alphatype, const mcsparseMatDescr_t descrA,
@@ -351,6 +367,16 @@ mcsparseStatus_t mcsparseDcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t tr
                                  const mcsparseMatDescr_t descrA, const double* csrValA, const int* csrRowPtrA,
                                  const int* csrColIndA, const double* B, int ldb, const double* beta, double* C,
                                  int ldc);
+mcsparseStatus_t mcsparseCcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const mcComplex* alpha,
+                                 const mcsparseMatDescr_t descrA, const mcComplex* csrValA, const int* csrRowPtrA,
+                                 const int* csrColIndA, const mcComplex* B, int ldb, const mcComplex* beta,
+                                 mcComplex* C, int ldc);
+mcsparseStatus_t mcsparseZcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const mcDoubleComplex* alpha,
+                                 const mcsparseMatDescr_t descrA, const mcDoubleComplex* csrValA,
+                                 const int* csrRowPtrA, const int* csrColIndA, const mcDoubleComplex* B, int ldb,
+                                 const mcDoubleComplex* beta, mcDoubleComplex* C, int ldc);
 mcsparseStatus_t mcsparseScsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
                                 const float* alpha, const mcsparseMatDescr_t descrA, const float* csrValA,
                                 const int* csrRowPtrA, const int* csrColIndA, const float* B, int ldb,
@@ -359,6 +385,15 @@ mcsparseStatus_t mcsparseDcsrmm(mcsparseHandle_t handle, mcsparseOperation_t tra
                                 const double* alpha, const mcsparseMatDescr_t descrA, const double* csrValA,
                                 const int* csrRowPtrA, const int* csrColIndA, const double* B, int ldb,
                                 const double* beta, double* C, int ldc);
+mcsparseStatus_t mcsparseCcsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const mcComplex* alpha, const mcsparseMatDescr_t descrA, const mcComplex* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const mcComplex* B, int ldb,
+                                const mcComplex* beta, mcComplex* C, int ldc);
+mcsparseStatus_t mcsparseZcsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const mcDoubleComplex* alpha, const mcsparseMatDescr_t descrA,
+                                const mcDoubleComplex* csrValA, const int* csrRowPtrA, const int* csrColIndA,
+                                const mcDoubleComplex* B, int ldb, const mcDoubleComplex* beta, mcDoubleComplex* C,
+                                int ldc);
 
 #ifdef __cplusplus
 }

@@ -113,13 +113,19 @@ PROTOTYPES = {
     "mcsparseSpMM_preprocess": (_i, _SPMM_ARGS + [_vp]),
     "mcsparseSpMM": (_i, _SPMM_ARGS + [_vp]),
     "mcsparseScsrmv": (_i, _CSRMV),
+    "mcsparseCcsrmv": (_i, _CSRMV),
+    "mcsparseZcsrmv": (_i, _CSRMV),
     "mcsparseDcsrmv": (_i, _CSRMV),
     "mcsparseCsrmvEx_bufferSize": (_i, _CSRMVEX + [_psz]),
     "mcsparseCsrmvEx": (_i, _CSRMVEX + [_vp]),
     "mcsparseScsrmm2": (_i, _CSRMM2),
     "mcsparseDcsrmm2": (_i, _CSRMM2),
+    "mcsparseCcsrmm2": (_i, _CSRMM2),
+    "mcsparseZcsrmm2": (_i, _CSRMM2),
     "mcsparseScsrmm": (_i, _CSRMM),
     "mcsparseDcsrmm": (_i, _CSRMM),
+    "mcsparseCcsrmm": (_i, _CSRMM),
+    "mcsparseZcsrmm": (_i, _CSRMM),
     "mcsparseB200SpMVNoAlloc": (_i, _SPMV_ARGS),
     "mcsparseB200SpMVPush": (_i, _SPMV_ARGS + [_vp, _i, _pvp, _i64]),
     "mcsparseB200SpMVPushMulticast": (_i, _SPMV_ARGS + [_vp, _vp, _i64]),

@@ -423,7 +423,11 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
     if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(B->row_num) ||
         too_big(B->col_num) || too_big(B->ld) || too_big(C->row_num) || too_big(C->col_num) || too_big(C->ld))
         return NOT_IMPL;
-    if (A->format != MCSPARSE_FORMAT_CSR) return NOT_IMPL;
+    // CSR runs as it is; a row-sorted COO or a CSC matrix is converted into the external buffer on every call
+    // (32-bit indices, one product), as the reference does for CSC (mcsp_spmm_gpu.cpp:818-848).
+    if (!(A->format == MCSPARSE_FORMAT_CSR || A->format == MCSPARSE_FORMAT_COO || A->format == MCSPARSE_FORMAT_CSC))
+        return NOT_IMPL;
+    if (A->format != MCSPARSE_FORMAT_CSR && (A->rowIdxType != MCSPARSE_INDEX_32I || A->batchCount != 1)) return NOT_IMPL;
     if (!(computeType == A->valueType && computeType == C->valueType && computeType == B->valueType)) return NOT_IMPL;
     if (!is_compute_type(computeType)) return NOT_IMPL;
     if (is_complex_fp(computeType) && A->rowIdxType != MCSPARSE_INDEX_32I) return NOT_IMPL;
@@ -449,12 +453,56 @@ bool spmm_row_major(mcsparseOperation_t opB, const mcsparseDnMatDescr* B, const 
 
 SpmmPlan spmm_plan_for(mcsparseOperation_t opB, const mcsparseSpMatDescr* A, const mcsparseDnMatDescr* B,
                        const mcsparseDnMatDescr* C, macaDataType computeType) {
+    if (A->format != MCSPARSE_FORMAT_CSR) return SpmmPlan();  // converted inputs run in one pass
     return spmm_plan(A->row_num, A->col_num, C->col_num, A->nnz, value_size(computeType), spmm_row_major(opB, B, C));
+}
+
+// Bytes a COO or CSC input adds to the SpMM buffer, and where that area starts.
+size_t spmm_conversion_bytes(const mcsparseSpMatDescr* A, size_t vsize) {
+    if (A->format == MCSPARSE_FORMAT_COO) return ((size_t(A->row_num) + 1) * 4 + 255 + 256) & ~size_t(255);
+    if (A->format == MCSPARSE_FORMAT_CSC) return transpose_plan(A->col_num, A->row_num, A->nnz, vsize).bytes + 256;
+    return 0;
 }
 
 template <typename T, typename I>
 St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, mcsparseDnMatDescr* B,
-            mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr) {
+            mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr,
+            void* conversion_area) {
+    if (A->format != MCSPARSE_FORMAT_CSR) {
+        if constexpr (sizeof(I) != 4) {
+            return NOT_IMPL;
+        } else {
+            // Convert into the buffer, then the CSR kernels: COO -> row offsets from the sorted row indices;
+            // CSC (= CSR of the transposed matrix) -> stable transposition, which yields the CSR of A, 0-based.
+            void* area = align_up_256(conversion_area);
+            const int32_t *rows = nullptr, *cols = static_cast<const int32_t*>(A->cols);
+            const T* vals = static_cast<const T*>(A->vals);
+            int base = A->mat_descr->base;
+            cudaError_t e = cudaSuccess;
+            if (A->format == MCSPARSE_FORMAT_COO) {
+                int32_t* offsets = static_cast<int32_t*>(area);
+                e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows), offsets);
+                rows = offsets;
+            } else {
+                const TransposePlan plan = transpose_plan(A->col_num, A->row_num, A->nnz, sizeof(T));
+                e = transpose_structure(h->stream, A->col_num, A->row_num, A->nnz, base,
+                                        static_cast<const int32_t*>(A->cols), static_cast<const int32_t*>(A->rows), plan, area);
+                if (e == cudaSuccess) e = transpose_values<T>(h->stream, A->nnz, vals, plan, area);
+                const char* a = static_cast<const char*>(area);
+                rows = reinterpret_cast<const int32_t*>(a + plan.off_ptr);
+                cols = reinterpret_cast<const int32_t*>(a + plan.off_keys[plan.col_slot()]);
+                vals = reinterpret_cast<const T*>(a + plan.off_val);
+                base = 0;
+            }
+            if (e != cudaSuccess) return from_cuda(e);
+            int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
+            if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
+            const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
+            return from_cuda(spmm<T, int32_t>(h->stream, A->row_num, C->col_num, base, rows, cols, vals,
+                                              static_cast<const T*>(B->values), b_rs, b_cs, static_cast<T*>(C->values),
+                                              c_rs, c_cs, scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
+        }
+    }
     int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
     if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
     const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
@@ -621,6 +669,12 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
     }
     return from_cuda(cudaGraphLaunch(A->push_graph, h->stream));
 }
+
+// mcComplex / mcDoubleComplex and the kernels' complex types are both interleaved (re, im) pairs.
+const cfloat* cx(const mcComplex* p) { return reinterpret_cast<const cfloat*>(p); }
+cfloat* cx(mcComplex* p) { return reinterpret_cast<cfloat*>(p); }
+const cdouble* cx(const mcDoubleComplex* p) { return reinterpret_cast<const cdouble*>(p); }
+cdouble* cx(mcDoubleComplex* p) { return reinterpret_cast<cdouble*>(p); }
 
 }  // namespace
 
@@ -1249,7 +1303,8 @@ mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     if (bufferSize == nullptr) return pub(BAD_POINTER);
     // 128 is MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15); a B too large
     // for L2 adds the per-row panel offsets that mcsparseSpMM_preprocess computes.
-    *bufferSize = spmm_plan_for(opB, matA, matB, matC, computeType).bytes;
+    *bufferSize = spmm_plan_for(opB, matA, matB, matC, computeType).bytes +
+                  spmm_conversion_bytes(matA, value_size(computeType));
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -1310,16 +1365,19 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
             panel_ptr = static_cast<const int*>(align_up_256(externalBuffer));
         }
     }
+    // A COO or CSC input is converted behind the (panel) plan's part of the buffer.
+    void* conversion_area =
+        static_cast<char*>(externalBuffer) + spmm_plan_for(opB, matA, matB, matC, computeType).bytes;
     const bool wide = index_size(matA) == 8;
     if (computeType == MACA_C_32F)
-        return pub(spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+        return pub(spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
     if (computeType == MACA_C_64F)
-        return pub(spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+        return pub(spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
     if (computeType == MACA_R_64F)
-        return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr)
-                        : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
-    return pub(wide ? spmm_run<float, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr)
-                    : spmm_run<float, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr));
+        return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
+                        : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+    return pub(wide ? spmm_run<float, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
+                    : spmm_run<float, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
 }
 
 // ----------------------------------------------------------------------------- legacy entry points
@@ -1340,6 +1398,22 @@ mcsparseStatus_t mcsparseDcsrmv(mcsparseHandle_t handle, mcsparseOperation_t tra
                                    beta, y, nullptr, false));
 }
 
+mcsparseStatus_t mcsparseCcsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const mcComplex* alpha, const mcsparseMatDescr_t descrA, const mcComplex* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const mcComplex* x,
+                                const mcComplex* beta, mcComplex* y) {
+    return pub(csrmv_entry<cfloat>(handle, transA, m, n, nnz, cx(alpha), descrA, cx(csrValA), csrRowPtrA, csrColIndA,
+                                   cx(x), cx(beta), cx(y), nullptr, false));
+}
+
+mcsparseStatus_t mcsparseZcsrmv(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int nnz,
+                                const mcDoubleComplex* alpha, const mcsparseMatDescr_t descrA,
+                                const mcDoubleComplex* csrValA, const int* csrRowPtrA, const int* csrColIndA,
+                                const mcDoubleComplex* x, const mcDoubleComplex* beta, mcDoubleComplex* y) {
+    return pub(csrmv_entry<cdouble>(handle, transA, m, n, nnz, cx(alpha), descrA, cx(csrValA), csrRowPtrA, csrColIndA,
+                                    cx(x), cx(beta), cx(y), nullptr, false));
+}
+
 static bool csrmvex_types_equal(macaDataType a, macaDataType v, macaDataType x, macaDataType b, macaDataType y,
                                 macaDataType e) {
     return a == x && v == x && b == x && y == x && e == x;  // mcsp_spmv_gpu.cpp:911-914
@@ -1357,7 +1431,7 @@ mcsparseStatus_t mcsparseCsrmvEx_bufferSize(mcsparseHandle_t handle, mcsparseAlg
     if (handle == nullptr) return pub(BAD_HANDLE);
     if (bufferSizeInBytes == nullptr) return pub(BAD_POINTER);
     if (m < 0 || nnz < 0) return pub(BAD_SIZE);
-    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_real_fp(xtype))
+    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_compute_type(xtype))
         return pub(NOT_IMPL);
     *bufferSizeInBytes = spmv_workspace(m, nnz, value_size(xtype)).bytes + 256;
     return MCSPARSE_STATUS_SUCCESS;
@@ -1370,8 +1444,18 @@ mcsparseStatus_t mcsparseCsrmvEx(mcsparseHandle_t handle, mcsparseAlgMode_t alg,
                                  const void* beta, macaDataType betatype, void* y, macaDataType ytype,
                                  macaDataType executiontype, void* buffer) {
     (void)alg;
-    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_real_fp(xtype))
+    if (!csrmvex_types_equal(alphatype, csrValAtype, xtype, betatype, ytype, executiontype) || !is_compute_type(xtype))
         return pub(NOT_IMPL);
+    if (xtype == MACA_C_32F)
+        return pub(csrmv_entry<cfloat>(handle, transA, m, n, nnz, static_cast<const cfloat*>(alpha), descrA,
+                                       static_cast<const cfloat*>(csrValA), csrRowPtrA, csrColIndA,
+                                       static_cast<const cfloat*>(x), static_cast<const cfloat*>(beta),
+                                       static_cast<cfloat*>(y), buffer, true));
+    if (xtype == MACA_C_64F)
+        return pub(csrmv_entry<cdouble>(handle, transA, m, n, nnz, static_cast<const cdouble*>(alpha), descrA,
+                                        static_cast<const cdouble*>(csrValA), csrRowPtrA, csrColIndA,
+                                        static_cast<const cdouble*>(x), static_cast<const cdouble*>(beta),
+                                        static_cast<cdouble*>(y), buffer, true));
     if (xtype == MACA_R_64F)
         return pub(csrmv_entry<double>(handle, transA, m, n, nnz, static_cast<const double*>(alpha), descrA,
                                        static_cast<const double*>(csrValA), csrRowPtrA, csrColIndA,
@@ -1414,6 +1498,41 @@ mcsparseStatus_t mcsparseDcsrmm(mcsparseHandle_t handle, mcsparseOperation_t tra
                                 const double* beta, double* C, int ldc) {
     return pub(csrmm_entry<double>(handle, transA, MCSPARSE_OPERATION_NON_TRANSPOSE, m, n, k, nnz, alpha, descrA,
                                    csrValA, csrRowPtrA, csrColIndA, B, ldb, beta, C, ldc));
+}
+
+mcsparseStatus_t mcsparseCcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const mcComplex* alpha,
+                                 const mcsparseMatDescr_t descrA, const mcComplex* csrValA, const int* csrRowPtrA,
+                                 const int* csrColIndA, const mcComplex* B, int ldb, const mcComplex* beta,
+                                 mcComplex* C, int ldc) {
+    return pub(csrmm_entry<cfloat>(handle, transA, transB, m, n, k, nnz, cx(alpha), descrA, cx(csrValA), csrRowPtrA,
+                                   csrColIndA, cx(B), ldb, cx(beta), cx(C), ldc));
+}
+
+mcsparseStatus_t mcsparseZcsrmm2(mcsparseHandle_t handle, mcsparseOperation_t transA, mcsparseOperation_t transB,
+                                 int m, int n, int k, int nnz, const mcDoubleComplex* alpha,
+                                 const mcsparseMatDescr_t descrA, const mcDoubleComplex* csrValA,
+                                 const int* csrRowPtrA, const int* csrColIndA, const mcDoubleComplex* B, int ldb,
+                                 const mcDoubleComplex* beta, mcDoubleComplex* C, int ldc) {
+    return pub(csrmm_entry<cdouble>(handle, transA, transB, m, n, k, nnz, cx(alpha), descrA, cx(csrValA), csrRowPtrA,
+                                    csrColIndA, cx(B), ldb, cx(beta), cx(C), ldc));
+}
+
+mcsparseStatus_t mcsparseCcsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const mcComplex* alpha, const mcsparseMatDescr_t descrA, const mcComplex* csrValA,
+                                const int* csrRowPtrA, const int* csrColIndA, const mcComplex* B, int ldb,
+                                const mcComplex* beta, mcComplex* C, int ldc) {
+    return pub(csrmm_entry<cfloat>(handle, transA, MCSPARSE_OPERATION_NON_TRANSPOSE, m, n, k, nnz, cx(alpha), descrA,
+                                   cx(csrValA), csrRowPtrA, csrColIndA, cx(B), ldb, cx(beta), cx(C), ldc));
+}
+
+mcsparseStatus_t mcsparseZcsrmm(mcsparseHandle_t handle, mcsparseOperation_t transA, int m, int n, int k, int nnz,
+                                const mcDoubleComplex* alpha, const mcsparseMatDescr_t descrA,
+                                const mcDoubleComplex* csrValA, const int* csrRowPtrA, const int* csrColIndA,
+                                const mcDoubleComplex* B, int ldb, const mcDoubleComplex* beta, mcDoubleComplex* C,
+                                int ldc) {
+    return pub(csrmm_entry<cdouble>(handle, transA, MCSPARSE_OPERATION_NON_TRANSPOSE, m, n, k, nnz, cx(alpha), descrA,
+                                    cx(csrValA), csrRowPtrA, csrColIndA, cx(B), ldb, cx(beta), cx(C), ldc));
 }
 
 // ----------------------------------------------------------------------------- sharding helpers

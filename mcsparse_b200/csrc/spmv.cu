@@ -871,6 +871,11 @@ INSTANTIATE(float)
 INSTANTIATE(double)
 INSTANTIATE_TI(cfloat, int32_t)
 INSTANTIATE_TI(cdouble, int32_t)
+template cudaError_t spmv_rowgroup<cfloat>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
+                                           const cfloat*, const cfloat*, cfloat*, ScalarArg<cfloat>, ScalarArg<cfloat>);
+template cudaError_t spmv_rowgroup<cdouble>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
+                                            const cdouble*, const cdouble*, cdouble*, ScalarArg<cdouble>,
+                                            ScalarArg<cdouble>);
 template cudaError_t spmv_analysis<int32_t>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const SpmvWorkspace&,
                                             void*);
 template cudaError_t spmv_analysis<int64_t>(cudaStream_t, int64_t, int64_t, int, const int64_t*, const SpmvWorkspace&,

@@ -107,6 +107,59 @@ def test_complex_spmm(handle, device, dtype, n, order):
     assert_close(got, ref, d, TOL[np.dtype(dtype)], f"complex SpMM n={n}")
 
 
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "many_short", "one_row_all_nnz", "all_empty"])
+def test_legacy_complex_csrmv_csrmvex_csrmm(handle, device, dtype, name):
+    """mcsparse{C,Z}csrmv, mcsparseCsrmvEx with complex types, mcsparse{C,Z}csrmm2 / csrmm (column-major B and C)."""
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, ncols, base = len(lengths), max(max(lengths), 1) + 5, 1
+    rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=6, base=base)
+    rng = np.random.default_rng(9)
+    x, y0 = cplx(rng, ncols, dtype), cplx(rng, m, dtype)
+    alpha, beta = 0.5 - 0.25j, 1.5 + 2.0j
+    ref, d = oracle.spmv(rp, col, val, x, alpha, beta, y0, base=base)
+    t = {k: up(v, device) for k, v in dict(rp=rp, col=col, val=val, x=x).items()}
+    P = lambda k: mc.host._ptr(t[k])  # non-null also for empty arrays
+    descr = C.c_void_p()
+    capi.check(lib.mcsparseCreateMatDescr(C.byref(descr)))
+    capi.check(lib.mcsparseSetMatIndexBase(descr, base))
+    ct = C.c_float if dtype == np.complex64 else C.c_double
+    a, b = (ct * 2)(alpha.real, alpha.imag), (ct * 2)(beta.real, beta.imag)
+    pa, pb = C.cast(C.byref(a), C.c_void_p), C.cast(C.byref(b), C.c_void_p)
+    single = dtype == np.complex64
+    nnz = col.size
+
+    y = up(y0.copy(), device)
+    fn = lib.mcsparseCcsrmv if single else lib.mcsparseZcsrmv
+    capi.check(fn(handle.h, N, m, ncols, nnz, pa, descr, P("val"), P("rp"), P("col"), P("x"), pb, C.c_void_p(y.data_ptr())))
+    torch.cuda.synchronize()
+    assert_close(y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], "csrmv")
+
+    y = up(y0.copy(), device)
+    dt = MACA[dtype]
+    sz = C.c_size_t()
+    ex_args = (handle.h, capi.MCSPARSE_ALG_MERGE_PATH, N, m, ncols, nnz, pa, dt, descr, P("val"), dt, P("rp"), P("col"),
+               P("x"), dt, pb, dt, C.c_void_p(y.data_ptr()), dt, dt)
+    capi.check(lib.mcsparseCsrmvEx_bufferSize(*ex_args, C.byref(sz)))
+    buf = torch.empty(sz.value, dtype=torch.uint8, device=device)
+    capi.check(lib.mcsparseCsrmvEx(*ex_args, C.c_void_p(buf.data_ptr())))
+    torch.cuda.synchronize()
+    assert_close(y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], "CsrmvEx")
+
+    n, ldb, ldc = 3, ncols + 1, m + 2
+    B, C0 = cplx(rng, n * ldb, dtype), cplx(rng, n * ldc, dtype)
+    refC, dC = oracle.spmm(rp, col, val, B, ldb, COL, n, alpha, beta, C0, ldc, COL, base=base)
+    for fn2, extra in ((lib.mcsparseCcsrmm2 if single else lib.mcsparseZcsrmm2, (N,)),
+                       (lib.mcsparseCcsrmm if single else lib.mcsparseZcsrmm, ())):
+        dB, dC0 = up(B, device), up(C0.copy(), device)
+        capi.check(fn2(handle.h, N, *extra, m, n, ncols, nnz, pa, descr, P("val"), P("rp"), P("col"),
+                       C.c_void_p(dB.data_ptr()), ldb, pb, C.c_void_p(dC0.data_ptr()), ldc))
+        torch.cuda.synchronize()
+        got = dC0.cpu().numpy().reshape(n, ldc)[:, :m].T
+        assert_close(got, refC, dC, TOL[np.dtype(dtype)], "csrmm")
+    lib.mcsparseDestroyMatDescr(descr)
+
+
 def test_complex_refusals(handle, device):
     """Complex values on the entry points that stay real-only, with 64-bit indices, or as A^H of a CSC matrix."""
     rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.complex64)

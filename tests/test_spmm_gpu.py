@@ -286,3 +286,62 @@ def test_spmm_strided_batch(handle, device, dtype, shared_a):
         ref, d = oracle.spmm(rpb, colb, valb, Bs[b], n, ROW, n, 0.5, 2.0, C0[b], n, ROW)
         assert_close(got[b], ref, d, TOL[np.dtype(dtype)], f"batch {b}")
     assert lib.mcsparseCsrSetStridedBatch(A.d, 0, 0, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
+
+
+class _Descr:
+    """Holder with the two attributes mc.spmm needs (descriptor and value dtype)."""
+
+    def __init__(self, d, dtype, keep):
+        self.d, self.dtype, self.keep = d, dtype, keep
+
+    def __del__(self):
+        if lib is not None and self.d is not None:
+            lib.mcsparseDestroySpMat(self.d)
+            self.d = None
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.complex64])
+@pytest.mark.parametrize("fmt", ["coo", "csc"])
+@pytest.mark.parametrize("n,order", [(64, ROW), (12, ROW), (5, COL)])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty"])
+def test_spmm_coo_and_csc_inputs(handle, device, name, n, order, fmt, dtype):
+    """A given as row-sorted COO or as CSC: converted into the external buffer, then the CSR SpMM kernels."""
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    m, k, base = lengths.size, max(int(lengths.max()), 1) + 7, 1
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=41, base=base)
+    rng = np.random.default_rng(3)
+
+    def rand(count):
+        v = rng.uniform(-1, 1, count)
+        return (v + 1j * rng.uniform(-1, 1, count)).astype(dtype) if np.iscomplexobj(val) else v.astype(dtype)
+
+    ldb, ldc = (n, n) if order == ROW else (k, m)
+    B, C0 = rand((k if order == ROW else n) * ldb), rand((m if order == ROW else n) * ldc)
+    pad = lambda a: np.concatenate([a, np.zeros(1, a.dtype)])  # non-null device pointers for empty arrays
+    up = lambda a: torch.from_numpy(pad(a)).to(device)[:a.size]
+    d = C.c_void_p()
+    tdtype = torch.from_numpy(val[:0]).dtype
+    maca = {np.float32: capi.MACA_R_32F, np.float64: capi.MACA_R_64F, np.complex64: capi.MACA_C_32F}[dtype]
+    if fmt == "coo":
+        coo_rows = (np.repeat(np.arange(m), lengths) + base).astype(np.int32)
+        t = [up(coo_rows), up(col), up(val)]
+        capi.check(lib.mcsparseCreateCoo(C.byref(d), m, k, col.size, mc.host._ptr(t[0]),
+                                         mc.host._ptr(t[1]), mc.host._ptr(t[2]),
+                                         capi.MCSPARSE_INDEX_32I, base, maca))
+    else:
+        t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, k, base)
+        t = [up((t_ptr + base).astype(np.int32)), up((t_idx + base).astype(np.int32)), up(val[perm])]
+        capi.check(lib.mcsparseCreateCsc(C.byref(d), m, k, col.size, mc.host._ptr(t[0]),
+                                         mc.host._ptr(t[1]), mc.host._ptr(t[2]),
+                                         capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, base, maca))
+    A = _Descr(d, tdtype, t)
+    dB, dC = up(B), up(C0.copy())
+    Bm, Cm = mc.DnMat(dB, k, n, ldb, order), mc.DnMat(dC, m, n, ldc, order)
+    buf = torch.empty(mc.spmm_buffer_size(handle, A, Bm, Cm), dtype=torch.uint8, device=device)
+    alpha, beta = (0.75, -0.5) if not np.iscomplexobj(val) else (0.75 - 0.5j, -0.5 + 0.25j)
+    mc.spmm(handle, A, Bm, Cm, buf, alpha=alpha, beta=beta)
+    torch.cuda.synchronize()
+    ref, dd = oracle.spmm(rp, col, val, B, ldb, order, n, alpha, beta, C0, ldc, order, base=base)
+    raw = dC.cpu().numpy()
+    got = raw.reshape(m, ldc)[:, :n] if order == ROW else raw.reshape(n, ldc)[:, :m].T
+    assert_close(got, ref, dd, TOL[np.dtype(dtype)], f"{fmt} input, n={n}")
