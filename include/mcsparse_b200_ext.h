@@ -29,7 +29,11 @@ extern "C" {
  * analysis. The reference has no such call: its analysis hook is an empty stub
  * (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:129-158) and mcsparseSpMV needs
  * none. Without it, mcsparseSpMV re-runs the (cheap) analysis on every call, which is
- * always safe when the caller edits the row offsets in place.
+ * always safe when the caller edits the row offsets in place. Between the preprocess call
+ * and the products that rely on it, externalBuffer must not be handed to a call on another
+ * matrix (the same matrix may alternate between op(A) = A and op(A) = A^T on one buffer:
+ * each switch redoes the analysis or the conversion). With op(A) = A^T / A^H or a CSC
+ * matrix the preprocess call also records the converted structure in externalBuffer.
  */
 mcsparseStatus_t mcsparseSpMV_preprocess(mcsparseHandle_t handle, mcsparseOperation_t opA, const void* alpha,
                                          mcsparseSpMatDescr_t matA, mcsparseDnVecDescr_t vecX, const void* beta,

@@ -302,6 +302,11 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
         small = A->trans_small_tiles;
     }
     if (!cached) {
+        {   // this buffer is about to hold the transposed matrix's partition: forget what else was recorded in it
+            std::lock_guard<std::mutex> g(A->lock);
+            if (A->analysed_buffer == buffer) A->analysed_buffer = nullptr;
+            if (A->push_buffer == buffer) A->push_buffer = nullptr;
+        }
         cudaError_t e = transpose_structure(h->stream, v.m, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
                                             static_cast<const int32_t*>(v.idx), L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
@@ -359,6 +364,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
+        if (A->trans_buffer == buffer) A->trans_buffer = nullptr;  // the buffer changes hands: a later A^T product reconverts
         if (preprocess_only) {
             A->analysed_buffer = buffer;
             A->analysed_rows = view.ptr;

@@ -146,3 +146,30 @@ def test_spmv_transpose_refusals(handle, device):
     Xn, Yn = mc.DnVec(torch.ones(5, device=device)), mc.DnVec(torch.zeros(4, device=device))
     assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, Xn.d, pa, Yn.d, capi.MACA_R_32F, 0, C.byref(plain)) == 0
     assert size.value > plain.value  # the conversion area is part of the reported size
+
+
+def test_one_buffer_alternating_between_a_and_a_transposed(handle, device):
+    """The same external buffer used for A x and A^T x in turn, with preprocess calls in between: whatever
+    was recorded in the buffer for one product must not be trusted by the other."""
+    dtype = np.float64
+    lengths = ADVERSARIAL_LENGTHS["many_short"] + ADVERSARIAL_LENGTHS["lengths_255_257"] + ADVERSARIAL_LENGTHS["tile_straddle"]
+    m = len(lengths)
+    n = m  # square, so that one pair of vectors serves both products
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=37)
+    A = mc.CsrMatrix(m, n, up(rp, device), up(col, device), up(val, device))
+    rng = np.random.default_rng(14)
+    x = rng.uniform(-1, 1, n).astype(dtype)
+    d_x, d_y = up(x, device), torch.zeros(m, dtype=torch.float64, device=device)
+    X, Y = mc.DnVec(d_x), mc.DnVec(d_y)
+    size = max(mc.spmv_buffer_size(handle, A, X, Y, op=T), mc.spmv_buffer_size(handle, A, X, Y, op=N))
+    buf = torch.empty(size, dtype=torch.uint8, device=device)
+    ref_n, d_n = oracle.spmv(rp, col, val, x, 1.0, 0.0)
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n)
+    ref_t, d_t = oracle.spmv(t_ptr, t_idx, val[perm], x, 1.0, 0.0)
+    for op, pre in [(N, True), (T, True), (N, False), (T, False), (T, True), (N, True), (N, False), (T, False)]:
+        if pre:
+            mc.spmv_preprocess(handle, A, X, Y, buf, op=op)
+        mc.spmv(handle, A, X, Y, buf, op=op)
+        torch.cuda.synchronize()
+        ref, d = (ref_n, d_n) if op == N else (ref_t, d_t)
+        assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], f"op {op} preprocess {pre}")
