@@ -11,10 +11,13 @@ also carries the other configurations under "configs".
 
   value     algorithmic bytes / s with all operands resident in HBM (events on the handle's stream)
   e2e       same metric through the C ABI with x copied from pinned host memory and y copied back
-            inside the timed region of every step (the matrix stays resident, as in a solver loop)
+            inside the timed region of every step (the matrix stays resident): throughput with
+            --e2e-depth independent products in flight (HostSpmvPipeline), and serial_ms_per_step
+            for one product at a time
   roofline  algorithmic bytes / mean device time of one mcsparseSpMV call (tile kernel + carry
             fix-up kernel, so slightly conservative for the tile kernel alone) against the measured
             HBM copy bandwidth in MEASURED_PEAKS.json
+  --transposed       y = A^T x of the chosen workload instead (conversion timed once, then the products)
   --impl reference   the OpenMP C CSR kernels of oracle/ on the host cores (the mcSparse reference has
             no CPU implementation and builds only with the MetaX toolchain), on a bounded row block
 """
