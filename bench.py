@@ -116,7 +116,7 @@ def visible_device_index(local_rank):
 class SpmvJob:
     """One configuration on one rank: a row block of A resident in HBM, x replicated."""
 
-    def __init__(self, name, device, rank, world, handle, scale=1):
+    def __init__(self, name, device, rank, world, handle, scale=1, index_bits=32, complex_values=False):
         import torch
 
         import mcsparse_b200 as mc
@@ -138,6 +138,16 @@ class SpmvJob:
         r0, r1 = bounds[rank], bounds[rank + 1]
         w = workloads.generate(cfg, device, row_range=(r0, r1))
         self.w = w
+        isize = 4
+        if index_bits == 64:  # variant: the same matrix with 64-bit row offsets and column indices (N = 1 only)
+            w.row_ptr, w.col, isize = w.row_ptr.long(), w.col.long(), 8
+        if complex_values:  # variant: the same structure with complex values, x and y of twice the bytes (N = 1 only)
+            cdt = torch.complex64 if cfg.dtype == torch.float32 else torch.complex128
+            w.val = torch.complex(w.val, w.val.flip(0)).to(cdt)
+            w.x = torch.complex(w.x, w.x.flip(0)).to(cdt)
+            if w.y0 is not None:
+                w.y0 = torch.complex(w.y0, w.y0.flip(0)).to(cdt)
+            self.vsize *= 2
         self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
         if world > 1:
             from mcsparse_b200 import sharding
@@ -149,7 +159,7 @@ class SpmvJob:
             self.X, self.Y, self.buf = self.sharded.X, self.sharded.Y, self.sharded.buffer
         else:
             self.sharded = None
-            self.y_full = torch.zeros(cfg.rows, dtype=cfg.dtype, device=device)
+            self.y_full = torch.zeros(cfg.rows, dtype=w.val.dtype, device=device)
             self.y = self.y_full[r0:r1]
             self.X, self.Y = mc.DnVec(w.x), mc.DnVec(self.y)
             self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y), dtype=torch.uint8,
@@ -158,8 +168,8 @@ class SpmvJob:
         if cfg.beta != 0:
             self.y.copy_(w.y0)
         self.parts = [self.y_full[bounds[g]:bounds[g + 1]] for g in range(world)]
-        self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta)
-        self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta)
+        self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta, index_size=isize)
+        self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta, index_size=isize)
         self.flops = 2 * self.total_nnz
         # tile kernel + carry fix-up; with one peer the step is pipelined: 4 tile launches + 4 fix-ups
         self.launches_per_step = 8 if 2 <= world <= 4 else 2
@@ -540,6 +550,12 @@ def run_gpu(args, rank, world, local_rank):
             for name in ("C1", "C2", "C3"):
                 j = SpmvJob(name, device, 0, 1, h)
                 extra[name] = measure_job(torch, j, 100, 5, peak, flush_buf)
+                del j
+                torch.cuda.empty_cache()
+            # the headline matrix with 64-bit indices, and with complex double values (bytes counted accordingly)
+            for key, kw in (("C5_index64", {"index_bits": 64}), ("C5_complex", {"complex_values": True})):
+                j = SpmvJob("C5", device, 0, 1, h, **kw)
+                extra[key] = measure_job(torch, j, 30, 3, peak, flush_buf)
                 del j
                 torch.cuda.empty_cache()
             for name in ("C2", "C5"):

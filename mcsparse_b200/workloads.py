@@ -314,9 +314,9 @@ def generate(cfg, device, base=0, row_range=None, with_dense=True):
     return w
 
 
-def algorithmic_bytes(rows, cols, nnz, value_size, beta, dense_cols=None):
+def algorithmic_bytes(rows, cols, nnz, value_size, beta, dense_cols=None, index_size=4):
     """Bytes one call must move: A once, row offsets, x (or B) once, y (or C) written, and read iff beta != 0."""
-    a = nnz * (value_size + 4) + (rows + 1) * 4
+    a = nnz * (value_size + index_size) + (rows + 1) * index_size
     n = 1 if dense_cols is None else dense_cols
     dense_in = cols * n * value_size
     out = rows * n * value_size
