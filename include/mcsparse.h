@@ -231,10 +231,11 @@ mcsparseStatus_t mcsparseSpMatSetAttribute(mcsparseSpMatDescr_t spMatDescr, mcsp
                                            const void* data, size_t dataSize);
 
 /* ---- COO (structure of arrays) sparse matrix descriptor, accepted by mcsparseSpMV as an input format.
- *      Reference: mcsp_helper.h.in:52-58, mcsp_helper.cpp:433-438,526-560,597-605. Entries must be
- *      sorted by row (any order inside a row); mcsparseSpMV derives CSR row offsets from cooRowInd
- *      into the external buffer (the reference's coo2csr step,
- *      mcsparse/src/kernels/conversion/coo2csr_device.hpp:8-24) and runs the CSR kernels. ---- */
+ *      Reference: mcsp_helper.h.in:52-58, mcsp_helper.cpp:433-438,526-560,597-605. Entries may come
+ *      in any order. For entries sorted by row, mcsparseSpMV / mcsparseSpMM derive CSR row offsets
+ *      from cooRowInd into the external buffer (the reference's coo2csr step,
+ *      mcsparse/src/kernels/conversion/coo2csr_device.hpp:8-24); otherwise, and for op(A) = A^T / A^H,
+ *      the entries are first sorted (stable) into the external buffer. Then the CSR kernels run. ---- */
 mcsparseStatus_t mcsparseCreateCoo(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
                                    void* cooRowInd, void* cooColInd, void* cooValues, mcsparseIndexType_t cooIdxType,
                                    mcsparseIndexBase_t idxBase, macaDataType valueType);

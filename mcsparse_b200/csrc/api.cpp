@@ -135,8 +135,7 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return BAD_SIZE;
     if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
     // op(A) = A^T / A^H and CSC inputs run through a conversion into the buffer (32-bit CSR / CSC only).
-    if (!n_op && !(allow_transposed && narrow &&
-                   (A->format == MCSPARSE_FORMAT_CSR || A->format == MCSPARSE_FORMAT_CSC)))
+    if (!n_op && !(allow_transposed && narrow))
         return NOT_IMPL;
     if (A->format == MCSPARSE_FORMAT_CSC && !narrow) return NOT_IMPL;
     // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
@@ -213,12 +212,41 @@ struct CsrView {
     const void* idx = nullptr;
     bool transposed = false;
     bool conjugate = false;  // op(A) = A^H on complex values
+    // COO entries that must be sorted first: ptr holds the index array to sort by (rows, or columns for
+    // a transposed product), idx the other one, n the number of rows of the matrix the kernels will see.
+    bool coo_sort = false;
+    bool converted() const { return transposed || coo_sort; }
 };
 
-CsrView csr_view(const mcsparseSpMatDescr* A, mcsparseOperation_t opA) {
+// Whether a COO matrix has its entries out of row order: one small kernel and a stream synchronisation the
+// first time a row-index array is seen, remembered on the descriptor after that.
+bool coo_unsorted(mcsparseContext* h, mcsparseSpMatDescr* A) {
+    if (A->format != MCSPARSE_FORMAT_COO || A->rows == nullptr) return false;
+    std::lock_guard<std::mutex> g(A->lock);
+    if (A->coo_checked_rows == A->rows && A->coo_checked_nnz == A->nnz) return A->coo_unsorted;
+    if (h == nullptr) return false;  // nothing to check with: the answer of the last check, if any, was given above
+    DeviceGuard guard(h->device);
+    int flag = 0;
+    if (indices_unsorted(h->stream, A->nnz, static_cast<const int32_t*>(A->rows), &flag) != cudaSuccess) flag = 1;
+    A->coo_unsorted = flag != 0;
+    A->coo_checked_rows = A->rows;
+    A->coo_checked_nnz = A->nnz;
+    return A->coo_unsorted;
+}
+
+CsrView csr_view(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseOperation_t opA) {
     CsrView v;
     const bool t_op = opA != MCSPARSE_OPERATION_NON_TRANSPOSE;
     v.conjugate = opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE && is_complex_fp(A->valueType);
+    if (A->format == MCSPARSE_FORMAT_COO && (t_op || coo_unsorted(h, A))) {
+        // Sorting by row gives the CSR of A, sorting by column the CSR of A^T: no further transposition.
+        v.coo_sort = true;
+        if (t_op)
+            v.m = A->row_num, v.n = A->col_num, v.ptr = A->cols, v.idx = A->rows;
+        else
+            v.m = A->col_num, v.n = A->row_num, v.ptr = A->rows, v.idx = A->cols;
+        return v;
+    }
     if (A->format == MCSPARSE_FORMAT_CSC) {
         v.m = A->col_num, v.n = A->row_num, v.ptr = A->cols, v.idx = A->rows, v.transposed = !t_op;
     } else {
@@ -307,8 +335,11 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
             if (A->analysed_buffer == buffer) A->analysed_buffer = nullptr;
             if (A->push_buffer == buffer) A->push_buffer = nullptr;
         }
-        cudaError_t e = transpose_structure(h->stream, v.m, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
-                                            static_cast<const int32_t*>(v.idx), L.plan, L.area);
+        cudaError_t e = v.coo_sort
+                            ? coo_sort_structure(h->stream, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
+                                                 static_cast<const int32_t*>(v.idx), L.plan, L.area)
+                            : transpose_structure(h->stream, v.m, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
+                                                  static_cast<const int32_t*>(v.idx), L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
         if (!probed) {  // tile size for the transposed matrix: probed once (synchronises), then remembered
             small = probe_small_tiles(h, t_idx, nnz, v.n, sizeof(T), L.work);
@@ -350,8 +381,8 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
-    const CsrView view = csr_view(A, opA);
-    if (view.transposed) {
+    const CsrView view = csr_view(h, A, opA);
+    if (view.converted()) {
         switch (computeType) {
             case MACA_R_64F: return spmv_transposed_run<double>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
             case MACA_C_32F: return spmv_transposed_run<cfloat>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
@@ -464,7 +495,8 @@ SpmmPlan spmm_plan_for(mcsparseOperation_t opB, const mcsparseSpMatDescr* A, con
 }
 
 // Bytes a COO or CSC input adds to the SpMM buffer, and where that area starts.
-size_t spmm_conversion_bytes(const mcsparseSpMatDescr* A, size_t vsize) {
+size_t spmm_conversion_bytes(const mcsparseSpMatDescr* A, size_t vsize, bool coo_sort) {
+    if (A->format == MCSPARSE_FORMAT_COO && coo_sort) return transpose_plan(A->col_num, A->row_num, A->nnz, vsize).bytes + 256;
     if (A->format == MCSPARSE_FORMAT_COO) return ((size_t(A->row_num) + 1) * 4 + 255 + 256) & ~size_t(255);
     if (A->format == MCSPARSE_FORMAT_CSC) return transpose_plan(A->col_num, A->row_num, A->nnz, vsize).bytes + 256;
     return 0;
@@ -485,7 +517,17 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
             const T* vals = static_cast<const T*>(A->vals);
             int base = A->mat_descr->base;
             cudaError_t e = cudaSuccess;
-            if (A->format == MCSPARSE_FORMAT_COO) {
+            if (A->format == MCSPARSE_FORMAT_COO && coo_unsorted(h, A)) {  // entries in any order: sort by row first
+                const TransposePlan plan = transpose_plan(A->col_num, A->row_num, A->nnz, sizeof(T));
+                e = coo_sort_structure(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows),
+                                       static_cast<const int32_t*>(A->cols), plan, area);
+                if (e == cudaSuccess) e = transpose_values<T>(h->stream, A->nnz, vals, plan, area);
+                const char* a = static_cast<const char*>(area);
+                rows = reinterpret_cast<const int32_t*>(a + plan.off_ptr);
+                cols = reinterpret_cast<const int32_t*>(a + plan.off_keys[plan.col_slot()]);
+                vals = reinterpret_cast<const T*>(a + plan.off_val);
+                base = 0;
+            } else if (A->format == MCSPARSE_FORMAT_COO) {
                 int32_t* offsets = static_cast<int32_t*>(area);
                 e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows), offsets);
                 rows = offsets;
@@ -967,6 +1009,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     d->analysed_rows = nullptr;
     d->trans_buffer = nullptr;
     d->trans_probed_idx = nullptr;
+    d->coo_checked_rows = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -1176,8 +1219,8 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     if (st != OK) return pub(st);
     // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
     // also needs room for the row offsets derived from its row indices.
-    const CsrView view = csr_view(matA, opA);
-    if (view.transposed) {  // work area of the transposed matrix + the conversion area
+    const CsrView view = csr_view(handle, matA, opA);
+    if (view.converted()) {  // work area of the converted matrix + the conversion area
         *bufferSize = transposed_buffer_bytes(view, matA->nnz, value_size(computeType));
         return MCSPARSE_STATUS_SUCCESS;
     }
@@ -1237,8 +1280,8 @@ mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcspa
         values == nullptr)
         return pub(BAD_POINTER);
     if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
-    const CsrView view = csr_view(matA, opA);
-    if (!view.transposed) return pub(BAD_VALUE);
+    const CsrView view = csr_view(nullptr, matA, opA);  // no handle here: a COO's order as found by its last product
+    if (!view.converted()) return pub(BAD_VALUE);
     const TransposedLayout L = transposed_layout(view, matA->nnz, value_size(matA->valueType), externalBuffer);
     const char* area = static_cast<const char*>(L.area);
     *rows = view.n;
@@ -1310,7 +1353,7 @@ mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     // 128 is MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15); a B too large
     // for L2 adds the per-row panel offsets that mcsparseSpMM_preprocess computes.
     *bufferSize = spmm_plan_for(opB, matA, matB, matC, computeType).bytes +
-                  spmm_conversion_bytes(matA, value_size(computeType));
+                  spmm_conversion_bytes(matA, value_size(computeType), coo_unsorted(handle, matA));
     return MCSPARSE_STATUS_SUCCESS;
 }
 

@@ -16,6 +16,7 @@
 //      through the permutation);
 //   4. values gathered through the permutation (repeated on every product: values may have changed).
 #include <cstdint>
+#include <mutex>
 
 #include "internal.h"
 
@@ -193,17 +194,25 @@ __global__ void __launch_bounds__(256)
 }
 
 // out[k] = row_of[perm[k]]: the column index of the k-th nonzero of the transposed matrix.
+// (`sub` is taken off every gathered index: the index base when the source is a caller's array.)
 __global__ void __launch_bounds__(256)
     gather_rows_kernel(long long nnz, const int* __restrict__ row_of, const unsigned* __restrict__ perm,
-                       int* __restrict__ out) {
+                       int* __restrict__ out, int sub) {
     const long long k = 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x);
     if (k + 3 < nnz) {
         const uint4 p = __ldcs(reinterpret_cast<const uint4*>(perm + k));
-        const int4 r = make_int4(__ldg(row_of + p.x), __ldg(row_of + p.y), __ldg(row_of + p.z), __ldg(row_of + p.w));
+        const int4 r = make_int4(__ldg(row_of + p.x) - sub, __ldg(row_of + p.y) - sub, __ldg(row_of + p.z) - sub,
+                                 __ldg(row_of + p.w) - sub);
         *reinterpret_cast<int4*>(out + k) = r;
     } else {
-        for (long long i = k; i < nnz; ++i) out[i] = __ldg(row_of + perm[i]);
+        for (long long i = k; i < nnz; ++i) out[i] = __ldg(row_of + perm[i]) - sub;
     }
+}
+
+// flag[0] = 1 if the indices are not in ascending order somewhere.
+__global__ void unsorted_flag_kernel(long long count, const int* __restrict__ idx, int* __restrict__ flag) {
+    const long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (j + 1 < count && __ldg(idx + j) > __ldg(idx + j + 1)) *flag = 1;
 }
 
 // out[k] = val[perm[k]]. Four consecutive k per thread: one 128-bit load of the permutation, four
@@ -269,33 +278,77 @@ TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_siz
     return p;
 }
 
+// Stable sort of the positions 0 .. nnz-1 by key (key - base in [0, 2^(8 passes))): leaves the sorted
+// 0-based keys in keys[final_slot()] and the permutation in perm[final_slot()].
+static cudaError_t radix_sort_positions(cudaStream_t s, int64_t nnz, int base, const int32_t* key_src,
+                                        const TransposePlan& p, void* buf) {
+    char* b = static_cast<char*>(buf);
+    int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
+    unsigned* perm[2] = {reinterpret_cast<unsigned*>(b + p.off_perm[0]), reinterpret_cast<unsigned*>(b + p.off_perm[1])};
+    unsigned* hist = reinterpret_cast<unsigned*>(b + p.off_hist);
+    unsigned* sums = reinterpret_cast<unsigned*>(b + p.off_sums);
+    cudaError_t e = cudaSuccess;
+    const int* src_keys = key_src;
+    const unsigned* src_perm = nullptr;
+    int sub = base;
+    for (int pass = 0; pass < p.passes && nnz > 0; ++pass) {
+        const int dst = pass & 1;
+        radix_hist_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, nnz, 8 * pass, hist, p.tiles);
+        scan_chunk_sums_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
+        scan_sums_kernel<<<1, kScanThreads, 0, s>>>(sums, p.scan_chunks);
+        scan_apply_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
+        radix_scatter_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, src_perm, keys[dst], perm[dst], nnz,
+                                                                         8 * pass, hist, p.tiles);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        src_keys = keys[dst];
+        src_perm = perm[dst];
+        sub = 0;
+    }
+    return e;
+}
+
+cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const int32_t* key_idx,
+                               const int32_t* other_idx, const TransposePlan& p, void* buf) {
+    char* b = static_cast<char*>(buf);
+    int32_t* ptr = reinterpret_cast<int32_t*>(b + p.off_ptr);
+    int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
+    unsigned* perm[2] = {reinterpret_cast<unsigned*>(b + p.off_perm[0]), reinterpret_cast<unsigned*>(b + p.off_perm[1])};
+    cudaError_t e = radix_sort_positions(s, nnz, base, key_idx, p, buf);
+    if (e != cudaSuccess) return e;
+    const int fin = p.final_slot();
+    if ((e = coo_row_offsets(s, key_range, nnz, 0, keys[fin], ptr)) != cudaSuccess) return e;
+    if (nnz > 0) {
+        gather_rows_kernel<<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, other_idx, perm[fin], keys[fin ^ 1], base);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+__device__ int g_unsorted_flag;  // result word of indices_unsorted (one check at a time per process)
+
+cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const int32_t* idx, int* host_flag) {
+    static std::mutex one_at_a_time;
+    std::lock_guard<std::mutex> g(one_at_a_time);
+    int* device_flag = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&device_flag), g_unsorted_flag);
+    if (e == cudaSuccess) e = cudaMemsetAsync(device_flag, 0, sizeof(int), s);
+    if (e == cudaSuccess && count > 1) {
+        unsorted_flag_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(count, idx, device_flag);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_flag, device_flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e;
+}
+
 cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
                                 const int32_t* col, const TransposePlan& p, void* buf) {
     char* b = static_cast<char*>(buf);
     int32_t* ptr = reinterpret_cast<int32_t*>(b + p.off_ptr);
     int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
     unsigned* perm[2] = {reinterpret_cast<unsigned*>(b + p.off_perm[0]), reinterpret_cast<unsigned*>(b + p.off_perm[1])};
-    unsigned* hist = reinterpret_cast<unsigned*>(b + p.off_hist);
-    unsigned* sums = reinterpret_cast<unsigned*>(b + p.off_sums);
-    cudaError_t e = cudaSuccess;
-    if (nnz > 0) {
-        const int* src_keys = col;
-        const unsigned* src_perm = nullptr;
-        int sub = base;
-        for (int pass = 0; pass < p.passes; ++pass) {
-            const int dst = pass & 1;
-            radix_hist_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, nnz, 8 * pass, hist, p.tiles);
-            scan_chunk_sums_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
-            scan_sums_kernel<<<1, kScanThreads, 0, s>>>(sums, p.scan_chunks);
-            scan_apply_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
-            radix_scatter_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, src_perm, keys[dst],
-                                                                             perm[dst], nnz, 8 * pass, hist, p.tiles);
-            if ((e = cudaGetLastError()) != cudaSuccess) return e;
-            src_keys = keys[dst];
-            src_perm = perm[dst];
-            sub = 0;
-        }
-    }
+    cudaError_t e = radix_sort_positions(s, nnz, base, col, p, buf);
+    if (e != cudaSuccess) return e;
     const int fin = p.final_slot();
     // Row offsets of the transposed matrix from the sorted (0-based) columns; with no nonzeros they are all zero.
     if ((e = coo_row_offsets(s, n, nnz, 0, keys[fin], ptr)) != cudaSuccess) return e;
@@ -304,7 +357,7 @@ cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nn
         // position, the other the column indices of the transposed matrix.
         int* row_of = reinterpret_cast<int*>(perm[fin ^ 1]);
         expand_rows_kernel<<<(unsigned)((m * 8 + 255) / 256), 256, 0, s>>>(m, base, row_ptr, row_of);
-        gather_rows_kernel<<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, row_of, perm[fin], keys[fin ^ 1]);
+        gather_rows_kernel<<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, row_of, perm[fin], keys[fin ^ 1], 0);
         e = cudaGetLastError();
     }
     return e;

@@ -301,7 +301,7 @@ class _Descr:
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64, np.complex64])
-@pytest.mark.parametrize("fmt", ["coo", "csc"])
+@pytest.mark.parametrize("fmt", ["coo", "coo_shuffled", "csc"])
 @pytest.mark.parametrize("n,order", [(64, ROW), (12, ROW), (5, COL)])
 @pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty"])
 def test_spmm_coo_and_csc_inputs(handle, device, name, n, order, fmt, dtype):
@@ -322,9 +322,10 @@ def test_spmm_coo_and_csc_inputs(handle, device, name, n, order, fmt, dtype):
     d = C.c_void_p()
     tdtype = torch.from_numpy(val[:0]).dtype
     maca = {np.float32: capi.MACA_R_32F, np.float64: capi.MACA_R_64F, np.complex64: capi.MACA_C_32F}[dtype]
-    if fmt == "coo":
+    if fmt.startswith("coo"):
         coo_rows = (np.repeat(np.arange(m), lengths) + base).astype(np.int32)
-        t = [up(coo_rows), up(col), up(val)]
+        shuffle = rng.permutation(col.size) if fmt == "coo_shuffled" else np.arange(col.size)
+        t = [up(coo_rows[shuffle]), up(col[shuffle]), up(val[shuffle])]
         capi.check(lib.mcsparseCreateCoo(C.byref(d), m, k, col.size, mc.host._ptr(t[0]),
                                          mc.host._ptr(t[1]), mc.host._ptr(t[2]),
                                          capi.MCSPARSE_INDEX_32I, base, maca))

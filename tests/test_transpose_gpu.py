@@ -173,3 +173,55 @@ def test_one_buffer_alternating_between_a_and_a_transposed(handle, device):
         torch.cuda.synchronize()
         ref, d = (ref_n, d_n) if op == N else (ref_t, d_t)
         assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], f"op {op} preprocess {pre}")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.complex128])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("op", [N, T])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle", "many_short"])
+def test_spmv_coo_any_order_and_transposed(handle, device, name, dtype, base, op):
+    """COO entries shuffled: the library sorts them (stable, by row; by column for A^T) into the external
+    buffer and runs the CSR kernels. The sorted structure is compared bit for bit with a stable CPU sort."""
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    m, n = lengths.size, max(int(lengths.max()), 1) + 13
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=43, base=base)
+    rows = (np.repeat(np.arange(m), lengths) + base).astype(np.int32)
+    rng = np.random.default_rng(21)
+    shuffle = rng.permutation(col.size)
+    rows_s, col_s, val_s = rows[shuffle], col[shuffle], val[shuffle]
+    d = C.c_void_p()
+    t = [up(a, device) for a in (rows_s, col_s, val_s)]
+    maca = {np.float32: capi.MACA_R_32F, np.float64: capi.MACA_R_64F, np.complex128: capi.MACA_C_64F}[dtype]
+    capi.check(lib.mcsparseCreateCoo(C.byref(d), m, n, col.size, mc.host._ptr(t[0]), mc.host._ptr(t[1]),
+                                     mc.host._ptr(t[2]), capi.MCSPARSE_INDEX_32I, base, maca))
+
+    class Holder:
+        pass
+
+    A = Holder()
+    A.d, A.dtype = d, t[2].dtype
+    xlen, ylen = (n, m) if op == N else (m, n)
+
+    def rand(count):
+        v = rng.uniform(-1, 1, count)
+        return (v + 1j * rng.uniform(-1, 1, count)).astype(dtype) if np.iscomplexobj(val) else v.astype(dtype)
+
+    x, y0 = rand(xlen), rand(ylen)
+    alpha, beta = (1.25, -0.5) if not np.iscomplexobj(val) else (1.25 - 0.5j, -0.5 + 0.75j)
+    d_y, buf, _ = run(handle, device, A, op, x, y0, alpha, beta, preprocess=True)
+    if op == N:
+        ref, dd = oracle.spmv(rp, col, val, x, alpha, beta, y0, base=base)
+    else:
+        t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+        ref, dd = oracle.spmv(t_ptr, t_idx, val[perm], x, alpha, beta, y0)
+    assert_close(d_y.cpu().numpy(), ref, dd, TOL[np.dtype(dtype)], f"{name} shuffled COO op {op}")
+    if col.size > 1 and (op == T or np.any(np.diff(rows_s) < 0)):  # converted: stable sort by row (or by column)
+        key, other = (rows_s, col_s) if op == N else (col_s, rows_s)
+        order = np.argsort(key, kind="stable")
+        rows_out, g_ptr, g_idx, g_val = device_view(A, op, buf, col.size, dtype)
+        assert rows_out == ylen
+        np.testing.assert_array_equal(g_ptr, np.concatenate([[0], np.cumsum(np.bincount(key - base, minlength=ylen))]))
+        np.testing.assert_array_equal(g_idx, other[order] - base)
+        np.testing.assert_array_equal(g_val, val_s[order])
+    lib.mcsparseDestroySpMat(d)
