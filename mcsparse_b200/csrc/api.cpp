@@ -73,6 +73,12 @@ bool value_type_known(macaDataType t) {
 bool is_real_fp(macaDataType t) { return t == MACA_R_32F || t == MACA_R_64F; }
 bool is_complex_fp(macaDataType t) { return t == MACA_C_32F || t == MACA_C_64F; }
 bool is_compute_type(macaDataType t) { return is_real_fp(t) || is_complex_fp(t); }
+// A real matrix applied to complex vectors with complex scalars (mcsp_spmv_gpu.cpp:852-855 routes this pair
+// of types to the CSR kernel instantiated with real values and complex x, y).
+bool real_matrix_complex_vectors(macaDataType a, macaDataType x, macaDataType y, macaDataType compute) {
+    return ((a == MACA_R_32F && compute == MACA_C_32F) || (a == MACA_R_64F && compute == MACA_C_64F)) &&
+           x == compute && y == compute;
+}
 size_t value_size(macaDataType t) { return t == MACA_C_64F ? 16 : (t == MACA_R_64F || t == MACA_C_32F) ? 8 : 4; }
 bool too_big(int64_t v) { return (v >> 31) != 0; }  // int32 indices: every extent must fit
 
@@ -140,7 +146,10 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     if (A->format == MCSPARSE_FORMAT_CSC && !narrow) return NOT_IMPL;
     // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
     if (A->format == MCSPARSE_FORMAT_CSC && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
-    if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType)) return NOT_IMPL;
+    const bool mixed = real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType);
+    if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType) && !mixed)
+        return NOT_IMPL;
+    if (mixed && !(n_op && A->format == MCSPARSE_FORMAT_CSR)) return NOT_IMPL;
     if (!is_compute_type(computeType)) return NOT_IMPL;
     // Complex values: the generic entry points only (the same that take transposed products), 32-bit indices.
     if (is_complex_fp(computeType) && !(allow_transposed && narrow)) return NOT_IMPL;
@@ -381,6 +390,20 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
+    if (real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType)) {
+        if (preprocess_only) return OK;  // nothing to record: the buffer only holds the intermediate product
+        void* z = align_up_256(buffer);
+        const int32_t *rp = static_cast<const int32_t*>(A->rows), *ci = static_cast<const int32_t*>(A->cols);
+        if (computeType == MACA_C_64F)
+            return from_cuda(spmv_real_matrix_complex_vectors<double>(
+                h->stream, A->row_num, A->mat_descr->base, rp, ci, static_cast<const double*>(A->vals),
+                static_cast<const cdouble*>(X->values), static_cast<cdouble*>(Y->values), scalar_arg<cdouble>(h, alpha),
+                scalar_arg<cdouble>(h, beta), static_cast<cdouble*>(z)));
+        return from_cuda(spmv_real_matrix_complex_vectors<float>(
+            h->stream, A->row_num, A->mat_descr->base, rp, ci, static_cast<const float*>(A->vals),
+            static_cast<const cfloat*>(X->values), static_cast<cfloat*>(Y->values), scalar_arg<cfloat>(h, alpha),
+            scalar_arg<cfloat>(h, beta), static_cast<cfloat*>(z)));
+    }
     const CsrView view = csr_view(h, A, opA);
     if (view.converted()) {
         switch (computeType) {
@@ -1219,6 +1242,10 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     if (st != OK) return pub(st);
     // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
     // also needs room for the row offsets derived from its row indices.
+    if (real_matrix_complex_vectors(matA->valueType, vecX->valueType, vecY->valueType, computeType)) {
+        *bufferSize = size_t(matA->row_num) * value_size(computeType) + 512;  // the intermediate A * x
+        return MCSPARSE_STATUS_SUCCESS;
+    }
     const CsrView view = csr_view(handle, matA, opA);
     if (view.converted()) {  // work area of the converted matrix + the conversion area
         *bufferSize = transposed_buffer_bytes(view, matA->nnz, value_size(computeType));

@@ -207,6 +207,13 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_pt
                  int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels = 1,
                  const int* panel_ptr = nullptr);
 
+// y = alpha * A * x + beta * y with a real CSR matrix and complex x, y, alpha, beta; scratch: m complex numbers.
+template <typename F>
+cudaError_t spmv_real_matrix_complex_vectors(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr,
+                                             const int32_t* col, const F* val, const Complex<F>* x, Complex<F>* y,
+                                             ScalarArg<Complex<F>> alpha, ScalarArg<Complex<F>> beta,
+                                             Complex<F>* scratch);
+
 cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
                             int32_t* offsets);
 

@@ -312,6 +312,42 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_pt
     return cudaGetLastError();
 }
 
+// y = alpha * z + beta * y on complex vectors (y is not read when beta == 0).
+template <typename T>
+__global__ void complex_axpby_kernel(long long m, ScalarArg<T> alpha_arg, const T* __restrict__ z,
+                                     ScalarArg<T> beta_arg, T* __restrict__ y) {
+    const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (r >= m) return;
+    const T alpha = alpha_arg.get(), beta = beta_arg.get();
+    T v = alpha * ldcs(z + r);
+    if (beta != T(0)) v = mad(beta, y[r], v);
+    y[r] = v;
+}
+
+// Real matrix, complex vectors (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:633-658 instantiates its
+// CSR kernel with real values and complex x, y, alpha, beta). A complex vector is a two-column row-major real
+// matrix, so z = A * x is the real SpMM with n = 2 into `scratch` (m complex numbers), and the complex
+// scaling follows in a second small kernel.
+template <typename F>
+cudaError_t spmv_real_matrix_complex_vectors(cudaStream_t s, int64_t m, int base, const int32_t* row_ptr,
+                                             const int32_t* col, const F* val, const Complex<F>* x, Complex<F>* y,
+                                             ScalarArg<Complex<F>> alpha, ScalarArg<Complex<F>> beta,
+                                             Complex<F>* scratch) {
+    if (m == 0) return cudaSuccess;
+    const ScalarArg<F> one{F(1), nullptr}, zero{F(0), nullptr};
+    cudaError_t e = spmm<F, int32_t>(s, m, 2, base, row_ptr, col, val, reinterpret_cast<const F*>(x), 2, 1,
+                                     reinterpret_cast<F*>(scratch), 2, 1, one, zero, 1, nullptr);
+    if (e != cudaSuccess) return e;
+    complex_axpby_kernel<Complex<F>><<<(unsigned)((m + 255) / 256), 256, 0, s>>>(m, alpha, scratch, beta, y);
+    return cudaGetLastError();
+}
+template cudaError_t spmv_real_matrix_complex_vectors<float>(cudaStream_t, int64_t, int, const int32_t*,
+                                                             const int32_t*, const float*, const cfloat*, cfloat*,
+                                                             ScalarArg<cfloat>, ScalarArg<cfloat>, cfloat*);
+template cudaError_t spmv_real_matrix_complex_vectors<double>(cudaStream_t, int64_t, int, const int32_t*,
+                                                              const int32_t*, const double*, const cdouble*, cdouble*,
+                                                              ScalarArg<cdouble>, ScalarArg<cdouble>, cdouble*);
+
 #define INSTANTIATE(T, I)                                                                                     \
     template cudaError_t spmm<T, I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*, const T*, const T*, \
                                     int64_t, int64_t, T*, int64_t, int64_t, ScalarArg<T>, ScalarArg<T>, int,   \

@@ -160,6 +160,39 @@ def test_legacy_complex_csrmv_csrmvex_csrmm(handle, device, dtype, name):
     lib.mcsparseDestroyMatDescr(descr)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("beta", [0.0, 0.5 - 1.25j])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle", "many_short"])
+def test_real_matrix_complex_vectors(handle, device, name, dtype, base, beta):
+    """Real values in A, complex x, y, alpha and beta (compute type complex)."""
+    cdtype = np.complex64 if dtype == np.float32 else np.complex128
+    lengths = ADVERSARIAL_LENGTHS[name]
+    m, n = len(lengths), max(max(lengths), 1) + 3
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=47, base=base)
+    rng = np.random.default_rng(17)
+    x, y0 = cplx(rng, n, cdtype), cplx(rng, m, cdtype)
+    t = [up(a, device) for a in (rp, col, val)]
+    A = mc.CsrMatrix(m, n, *t, base=base)
+    d_y = up(y0.copy(), device)
+    X, Y = mc.DnVec(up(x, device)), mc.DnVec(d_y)
+    alpha = -0.75 + 0.5j
+    ct = C.c_float if dtype == np.float32 else C.c_double
+    a, b = (ct * 2)(alpha.real, alpha.imag), (ct * 2)(complex(beta).real, complex(beta).imag)
+    pa, pb = C.cast(C.byref(a), C.c_void_p), C.cast(C.byref(b), C.c_void_p)
+    size = C.c_size_t()
+    args = (handle.h, N, pa, A.d, X.d, pb, Y.d, MACA[cdtype], 0)
+    capi.check(lib.mcsparseSpMV_bufferSize(*args, C.byref(size)))
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    capi.check(lib.mcsparseSpMV(*args, C.c_void_p(buf.data_ptr())))
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(rp, col, val.astype(cdtype), x, alpha, beta, y0, base=base)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(cdtype)], name)
+    assert lib.mcsparseSpMV_bufferSize(handle.h, T, pa, A.d, Y.d, pb, X.d, MACA[cdtype], 0,
+                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+
+
 def test_complex_refusals(handle, device):
     """Complex values on the entry points that stay real-only, with 64-bit indices, or as A^H of a CSC matrix."""
     rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.complex64)
