@@ -9,8 +9,8 @@
  * Supported compute path: MCSPARSE_FORMAT_CSR (and row-sorted MCSPARSE_FORMAT_COO or MCSPARSE_FORMAT_CSC
  * as an input of mcsparseSpMV / mcsparseSpMM), MCSPARSE_OPERATION_NON_TRANSPOSE (mcsparseSpMV: also
  * MCSPARSE_OPERATION_TRANSPOSE, through a conversion into the external buffer),
- * MACA_R_32F / MACA_R_64F / MACA_C_32F / MACA_C_64F (complex: 32-bit indices; mcsparseSpMV also takes
- * MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE), offsets and columns both MCSPARSE_INDEX_32I or (CSR only) both
+ * MACA_R_32F / MACA_R_64F / MACA_C_32F / MACA_C_64F (complex: mcsparseSpMV also takes
+ * MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE), offsets and columns both MCSPARSE_INDEX_32I or both
  * MCSPARSE_INDEX_64I with extents below 2^31, index base 0 or 1.
  * Everything else that the reference accepts on these entry points returns
  * MCSPARSE_STATUS_NOT_SUPPORTED here.

@@ -123,11 +123,11 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     if (h == nullptr) return BAD_HANDLE;
     if (alpha == nullptr || beta == nullptr || A == nullptr || X == nullptr || Y == nullptr) return BAD_POINTER;
     if (need_size_out && size_out == nullptr) return BAD_POINTER;
-    // Index types come in matched pairs (mcsp_spmv_gpu.cpp:1112-1118); 64-bit indices run on CSR only,
-    // and the extents must still fit 31 bits.
+    // Index types come in matched pairs (mcsp_spmv_gpu.cpp:1112-1118); with 64-bit indices the extents
+    // must still fit 31 bits.
     const bool narrow = A->rowIdxType == MCSPARSE_INDEX_32I && A->colIdxType == MCSPARSE_INDEX_32I;
     const bool wide = A->rowIdxType == MCSPARSE_INDEX_64I && A->colIdxType == MCSPARSE_INDEX_64I;
-    if (!(narrow || (wide && allow_wide_indices && A->format == MCSPARSE_FORMAT_CSR))) return NOT_IMPL;
+    if (!(narrow || (wide && allow_wide_indices))) return NOT_IMPL;
     if (too_big(A->row_num) || too_big(A->col_num) || too_big(A->nnz) || too_big(X->size) || too_big(Y->size) ||
         too_big(A->row_num + A->nnz) || too_big(A->col_num + A->nnz))
         return NOT_IMPL;
@@ -140,10 +140,8 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
           (!n_op && X->size == A->row_num && Y->size == A->col_num)))
         return BAD_SIZE;
     if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
-    // op(A) = A^T / A^H and CSC inputs run through a conversion into the buffer (32-bit CSR / CSC only).
-    if (!n_op && !(allow_transposed && narrow))
-        return NOT_IMPL;
-    if (A->format == MCSPARSE_FORMAT_CSC && !narrow) return NOT_IMPL;
+    // op(A) = A^T / A^H and CSC inputs run through a conversion into the buffer.
+    if (!n_op && !allow_transposed) return NOT_IMPL;
     // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
     if (A->format == MCSPARSE_FORMAT_CSC && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
     const bool mixed = real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType);
@@ -151,8 +149,9 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return NOT_IMPL;
     if (mixed && !(n_op && A->format == MCSPARSE_FORMAT_CSR)) return NOT_IMPL;
     if (!is_compute_type(computeType)) return NOT_IMPL;
-    // Complex values: the generic entry points only (the same that take transposed products), 32-bit indices.
-    if (is_complex_fp(computeType) && !(allow_transposed && narrow)) return NOT_IMPL;
+    // Complex values: the generic entry points only (the same that take transposed products).
+    if (is_complex_fp(computeType) && !allow_transposed) return NOT_IMPL;
+    if (mixed && !narrow) return NOT_IMPL;
     return OK;
 }
 
@@ -236,7 +235,10 @@ bool coo_unsorted(mcsparseContext* h, mcsparseSpMatDescr* A) {
     if (h == nullptr) return false;  // nothing to check with: the answer of the last check, if any, was given above
     DeviceGuard guard(h->device);
     int flag = 0;
-    if (indices_unsorted(h->stream, A->nnz, static_cast<const int32_t*>(A->rows), &flag) != cudaSuccess) flag = 1;
+    const cudaError_t e = A->rowIdxType == MCSPARSE_INDEX_64I
+                              ? indices_unsorted(h->stream, A->nnz, static_cast<const int64_t*>(A->rows), &flag)
+                              : indices_unsorted(h->stream, A->nnz, static_cast<const int32_t*>(A->rows), &flag);
+    if (e != cudaSuccess) flag = 1;
     A->coo_unsorted = flag != 0;
     A->coo_checked_rows = A->rows;
     A->coo_checked_nnz = A->nnz;
@@ -247,7 +249,9 @@ CsrView csr_view(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseOperation_t 
     CsrView v;
     const bool t_op = opA != MCSPARSE_OPERATION_NON_TRANSPOSE;
     v.conjugate = opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE && is_complex_fp(A->valueType);
-    if (A->format == MCSPARSE_FORMAT_COO && (t_op || coo_unsorted(h, A))) {
+    // (64-bit COO always goes through the sort: it leaves 32-bit arrays, which is what the kernels take when
+    // the row offsets are derived rather than given.)
+    if (A->format == MCSPARSE_FORMAT_COO && (t_op || A->rowIdxType == MCSPARSE_INDEX_64I || coo_unsorted(h, A))) {
         // Sorting by row gives the CSR of A, sorting by column the CSR of A^T: no further transposition.
         v.coo_sort = true;
         if (t_op)
@@ -319,13 +323,27 @@ size_t transposed_buffer_bytes(const CsrView& v, int64_t nnz, size_t vsize) {
     return spmv_workspace(v.n, nnz, vsize).bytes + 256 + transpose_plan(v.m, v.n, nnz, vsize).bytes + 256;
 }
 
+// Structure of the matrix the kernels will run on, for a transposed view or a COO that needs sorting.
+template <typename I>
+cudaError_t convert_structure_as(cudaStream_t s, const mcsparseSpMatDescr* A, const CsrView& v, const TransposePlan& plan,
+                                 void* area) {
+    const int base = A->mat_descr->base;
+    const I *ptr = static_cast<const I*>(v.ptr), *idx = static_cast<const I*>(v.idx);
+    return v.coo_sort ? coo_sort_structure<I>(s, v.n, A->nnz, base, ptr, idx, plan, area)
+                      : transpose_structure<I>(s, v.m, v.n, A->nnz, base, ptr, idx, plan, area);
+}
+cudaError_t convert_structure(cudaStream_t s, const mcsparseSpMatDescr* A, const CsrView& v, const TransposePlan& plan,
+                              void* area) {
+    return A->rowIdxType == MCSPARSE_INDEX_64I ? convert_structure_as<int64_t>(s, A, v, plan, area)
+                                               : convert_structure_as<int32_t>(s, A, v, plan, area);
+}
+
 // y = alpha * V^T * x + beta * y for the CSR view V: convert (structure once per preprocess, or on
 // every call without one; values on every call), then the ordinary tile kernels on the result.
 template <typename T>
 St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X,
                        mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer, bool preprocess_only) {
     const int64_t nnz = A->nnz;
-    const int base = A->mat_descr->base;
     const TransposedLayout L = transposed_layout(v, nnz, sizeof(T), buffer);
     char* area = static_cast<char*>(L.area);
     const int32_t* t_ptr = reinterpret_cast<const int32_t*>(area + L.plan.off_ptr);
@@ -344,11 +362,7 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
             if (A->analysed_buffer == buffer) A->analysed_buffer = nullptr;
             if (A->push_buffer == buffer) A->push_buffer = nullptr;
         }
-        cudaError_t e = v.coo_sort
-                            ? coo_sort_structure(h->stream, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
-                                                 static_cast<const int32_t*>(v.idx), L.plan, L.area)
-                            : transpose_structure(h->stream, v.m, v.n, nnz, base, static_cast<const int32_t*>(v.ptr),
-                                                  static_cast<const int32_t*>(v.idx), L.plan, L.area);
+        cudaError_t e = convert_structure(h->stream, A, v, L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
         if (!probed) {  // tile size for the transposed matrix: probed once (synchronises), then remembered
             small = probe_small_tiles(h, t_idx, nnz, v.n, sizeof(T), L.work);
@@ -430,9 +444,11 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     }
     const bool wide = index_size(A) == 8;
     if (computeType == MACA_C_32F)
-        return spmv_run<cfloat, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+        return wide ? spmv_run<cfloat, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                    : spmv_run<cfloat, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
     if (computeType == MACA_C_64F)
-        return spmv_run<cdouble, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
+        return wide ? spmv_run<cdouble, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
+                    : spmv_run<cdouble, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
     if (computeType == MACA_R_64F)
         return wide ? spmv_run<double, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
                     : spmv_run<double, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
@@ -484,13 +500,12 @@ St spmm_check(mcsparseHandle_t h, mcsparseOperation_t opA, mcsparseOperation_t o
         too_big(B->col_num) || too_big(B->ld) || too_big(C->row_num) || too_big(C->col_num) || too_big(C->ld))
         return NOT_IMPL;
     // CSR runs as it is; a row-sorted COO or a CSC matrix is converted into the external buffer on every call
-    // (32-bit indices, one product), as the reference does for CSC (mcsp_spmm_gpu.cpp:818-848).
+    // (one product), as the reference does for CSC (mcsp_spmm_gpu.cpp:818-848).
     if (!(A->format == MCSPARSE_FORMAT_CSR || A->format == MCSPARSE_FORMAT_COO || A->format == MCSPARSE_FORMAT_CSC))
         return NOT_IMPL;
-    if (A->format != MCSPARSE_FORMAT_CSR && (A->rowIdxType != MCSPARSE_INDEX_32I || A->batchCount != 1)) return NOT_IMPL;
+    if (A->format != MCSPARSE_FORMAT_CSR && A->batchCount != 1) return NOT_IMPL;
     if (!(computeType == A->valueType && computeType == C->valueType && computeType == B->valueType)) return NOT_IMPL;
     if (!is_compute_type(computeType)) return NOT_IMPL;
-    if (is_complex_fp(computeType) && A->rowIdxType != MCSPARSE_INDEX_32I) return NOT_IMPL;
     if (opA != MCSPARSE_OPERATION_NON_TRANSPOSE) return NOT_IMPL;  // :105
     if (opB == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
     // Shapes: op(B) is A.cols x C.cols, C is A.rows x C.cols. The reference trusts the caller
@@ -530,49 +545,39 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
             mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr,
             void* conversion_area) {
     if (A->format != MCSPARSE_FORMAT_CSR) {
-        if constexpr (sizeof(I) != 4) {
-            return NOT_IMPL;
+        // Convert into the buffer, then the CSR kernels on the (always 32-bit) result: a row-sorted 32-bit COO only
+        // needs row offsets; any other COO is sorted by row; CSC (= CSR of the transposed matrix) is transposed.
+        void* area = align_up_256(conversion_area);
+        const int32_t *rows = nullptr, *cols = nullptr;
+        const T* vals = static_cast<const T*>(A->vals);
+        int base = A->mat_descr->base;
+        cudaError_t e = cudaSuccess;
+        const bool coo = A->format == MCSPARSE_FORMAT_COO;
+        if (coo && sizeof(I) == 4 && !coo_unsorted(h, A)) {
+            int32_t* offsets = static_cast<int32_t*>(area);
+            e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows), offsets);
+            rows = offsets;
+            cols = static_cast<const int32_t*>(A->cols);
         } else {
-            // Convert into the buffer, then the CSR kernels: COO -> row offsets from the sorted row indices;
-            // CSC (= CSR of the transposed matrix) -> stable transposition, which yields the CSR of A, 0-based.
-            void* area = align_up_256(conversion_area);
-            const int32_t *rows = nullptr, *cols = static_cast<const int32_t*>(A->cols);
-            const T* vals = static_cast<const T*>(A->vals);
-            int base = A->mat_descr->base;
-            cudaError_t e = cudaSuccess;
-            if (A->format == MCSPARSE_FORMAT_COO && coo_unsorted(h, A)) {  // entries in any order: sort by row first
-                const TransposePlan plan = transpose_plan(A->col_num, A->row_num, A->nnz, sizeof(T));
-                e = coo_sort_structure(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows),
-                                       static_cast<const int32_t*>(A->cols), plan, area);
-                if (e == cudaSuccess) e = transpose_values<T>(h->stream, A->nnz, vals, plan, area);
-                const char* a = static_cast<const char*>(area);
-                rows = reinterpret_cast<const int32_t*>(a + plan.off_ptr);
-                cols = reinterpret_cast<const int32_t*>(a + plan.off_keys[plan.col_slot()]);
-                vals = reinterpret_cast<const T*>(a + plan.off_val);
-                base = 0;
-            } else if (A->format == MCSPARSE_FORMAT_COO) {
-                int32_t* offsets = static_cast<int32_t*>(area);
-                e = coo_row_offsets(h->stream, A->row_num, A->nnz, base, static_cast<const int32_t*>(A->rows), offsets);
-                rows = offsets;
-            } else {
-                const TransposePlan plan = transpose_plan(A->col_num, A->row_num, A->nnz, sizeof(T));
-                e = transpose_structure(h->stream, A->col_num, A->row_num, A->nnz, base,
-                                        static_cast<const int32_t*>(A->cols), static_cast<const int32_t*>(A->rows), plan, area);
-                if (e == cudaSuccess) e = transpose_values<T>(h->stream, A->nnz, vals, plan, area);
-                const char* a = static_cast<const char*>(area);
-                rows = reinterpret_cast<const int32_t*>(a + plan.off_ptr);
-                cols = reinterpret_cast<const int32_t*>(a + plan.off_keys[plan.col_slot()]);
-                vals = reinterpret_cast<const T*>(a + plan.off_val);
-                base = 0;
-            }
-            if (e != cudaSuccess) return from_cuda(e);
-            int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
-            if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
-            const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
-            return from_cuda(spmm<T, int32_t>(h->stream, A->row_num, C->col_num, base, rows, cols, vals,
-                                              static_cast<const T*>(B->values), b_rs, b_cs, static_cast<T*>(C->values),
-                                              c_rs, c_cs, scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
+            const TransposePlan plan = transpose_plan(A->col_num, A->row_num, A->nnz, sizeof(T));
+            e = coo ? coo_sort_structure<I>(h->stream, A->row_num, A->nnz, base, static_cast<const I*>(A->rows),
+                                            static_cast<const I*>(A->cols), plan, area)
+                    : transpose_structure<I>(h->stream, A->col_num, A->row_num, A->nnz, base,
+                                             static_cast<const I*>(A->cols), static_cast<const I*>(A->rows), plan, area);
+            if (e == cudaSuccess) e = transpose_values<T>(h->stream, A->nnz, vals, plan, area);
+            const char* a = static_cast<const char*>(area);
+            rows = reinterpret_cast<const int32_t*>(a + plan.off_ptr);
+            cols = reinterpret_cast<const int32_t*>(a + plan.off_keys[plan.col_slot()]);
+            vals = reinterpret_cast<const T*>(a + plan.off_val);
+            base = 0;
         }
+        if (e != cudaSuccess) return from_cuda(e);
+        int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
+        if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
+        const int64_t c_rs = C->order == MCSPARSE_ORDER_ROW ? C->ld : 1, c_cs = C->order == MCSPARSE_ORDER_ROW ? 1 : C->ld;
+        return from_cuda(spmm<T, int32_t>(h->stream, A->row_num, C->col_num, base, rows, cols, vals,
+                                          static_cast<const T*>(B->values), b_rs, b_cs, static_cast<T*>(C->values), c_rs,
+                                          c_cs, scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
     }
     int64_t b_rs = B->order == MCSPARSE_ORDER_ROW ? B->ld : 1, b_cs = B->order == MCSPARSE_ORDER_ROW ? 1 : B->ld;
     if (opB == MCSPARSE_OPERATION_TRANSPOSE) std::swap(b_rs, b_cs);
@@ -1380,7 +1385,8 @@ mcsparseStatus_t mcsparseSpMM_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     // 128 is MIN_BUFFER_SIZE of the reference (mcsparse/src/include/mcsp_config.h:11-15); a B too large
     // for L2 adds the per-row panel offsets that mcsparseSpMM_preprocess computes.
     *bufferSize = spmm_plan_for(opB, matA, matB, matC, computeType).bytes +
-                  spmm_conversion_bytes(matA, value_size(computeType), coo_unsorted(handle, matA));
+                  spmm_conversion_bytes(matA, value_size(computeType),
+                                        index_size(matA) == 8 || coo_unsorted(handle, matA));
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -1446,9 +1452,11 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
         static_cast<char*>(externalBuffer) + spmm_plan_for(opB, matA, matB, matC, computeType).bytes;
     const bool wide = index_size(matA) == 8;
     if (computeType == MACA_C_32F)
-        return pub(spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+        return pub(wide ? spmm_run<cfloat, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
+                        : spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
     if (computeType == MACA_C_64F)
-        return pub(spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+        return pub(wide ? spmm_run<cdouble, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
+                        : spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
     if (computeType == MACA_R_64F)
         return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
                         : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));

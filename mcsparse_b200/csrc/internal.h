@@ -232,16 +232,20 @@ struct TransposePlan {
 };
 TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_size);
 // Structure of the transposed matrix (row offsets, column indices, permutation) of an m x n CSR matrix.
-cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
-                                const int32_t* col, const TransposePlan& plan, void* buf);
+// (I: the caller's index type; the converted arrays are always 32-bit, extents fit 31 bits.)
+template <typename I>
+cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const I* row_ptr,
+                                const I* col, const TransposePlan& plan, void* buf);
 // CSR structure of a COO matrix whose entries come in any order, by the same stable sort: sorted by
 // `key_idx` (the row indices; or the column indices, which yields the transposed matrix), row
 // offsets over [0, key_range], and the other index of every entry gathered into keys[col_slot()],
 // 0-based. The plan is transpose_plan(any, key_range, nnz, value_size).
-cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const int32_t* key_idx,
-                               const int32_t* other_idx, const TransposePlan& plan, void* buf);
+template <typename I>
+cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const I* key_idx,
+                               const I* other_idx, const TransposePlan& plan, void* buf);
 // *host_flag = 1 if idx[0 .. count) is not ascending (one kernel, a 4-byte copy, a stream synchronisation).
-cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const int32_t* idx, int* host_flag);
+template <typename I>
+cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* host_flag);
 // Values of the transposed matrix, gathered through the permutation left by transpose_structure
 // (conjugated on the way for op(A) = A^H).
 template <typename T>

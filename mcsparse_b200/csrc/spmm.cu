@@ -358,6 +358,8 @@ INSTANTIATE(float, int64_t)
 INSTANTIATE(double, int64_t)
 INSTANTIATE(cfloat, int32_t)
 INSTANTIATE(cdouble, int32_t)
+INSTANTIATE(cfloat, int64_t)
+INSTANTIATE(cdouble, int64_t)
 #undef INSTANTIATE
 template cudaError_t spmm_preprocess<int32_t>(cudaStream_t, int64_t, int, const int32_t*, const int32_t*,
                                               const SpmmPlan&, void*);

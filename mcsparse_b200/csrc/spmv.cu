@@ -871,6 +871,8 @@ INSTANTIATE(float)
 INSTANTIATE(double)
 INSTANTIATE_TI(cfloat, int32_t)
 INSTANTIATE_TI(cdouble, int32_t)
+INSTANTIATE_TI(cfloat, int64_t)
+INSTANTIATE_TI(cdouble, int64_t)
 template cudaError_t spmv_rowgroup<cfloat>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
                                            const cfloat*, const cfloat*, cfloat*, ScalarArg<cfloat>, ScalarArg<cfloat>);
 template cudaError_t spmv_rowgroup<cdouble>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,

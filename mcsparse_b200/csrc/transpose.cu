@@ -31,13 +31,17 @@ constexpr int kScanThreads = 1024;
 constexpr int kScanItems = 8;                                   // consecutive items per thread
 constexpr int kScanChunk = kScanThreads * kScanItems;
 
-__device__ __forceinline__ unsigned sort_key(const int* __restrict__ keys, long long i, int sub) {
+// K: type of the keys a pass reads (the caller's 32- or 64-bit indices in the first pass, the
+// 32-bit keys of the previous pass after that; sorted keys always fit 31 bits).
+template <typename K>
+__device__ __forceinline__ unsigned sort_key(const K* __restrict__ keys, long long i, int sub) {
     return (unsigned)(__ldg(keys + i) - sub);
 }
 
 // hist[d * tiles + t] = number of items of tile t whose digit is d.
+template <typename K>
 __global__ void __launch_bounds__(kSortThreads)
-    radix_hist_kernel(const int* __restrict__ keys, int sub, long long count, int shift, unsigned* __restrict__ hist,
+    radix_hist_kernel(const K* __restrict__ keys, int sub, long long count, int shift, unsigned* __restrict__ hist,
                       long long tiles) {
     __shared__ unsigned s_cnt[256];
     const long long t = blockIdx.x;
@@ -58,8 +62,9 @@ __global__ void __launch_bounds__(kSortThreads)
 // Stable scatter of one tile: item idx goes to offsets[digit][tile] + (number of earlier items of
 // the tile with the same digit). Warps own consecutive 1024-item pieces of the tile and walk them
 // 32 items at a time, so "earlier" is decided by (warp, round, lane) = ascending idx.
+template <typename K>
 __global__ void __launch_bounds__(kSortThreads)
-    radix_scatter_kernel(const int* __restrict__ keys_in, int sub, const unsigned* __restrict__ perm_in,
+    radix_scatter_kernel(const K* __restrict__ keys_in, int sub, const unsigned* __restrict__ perm_in,
                          int* __restrict__ keys_out, unsigned* __restrict__ perm_out, long long count, int shift,
                          const unsigned* __restrict__ offsets, long long tiles) {
     __shared__ unsigned s_cnt[kSortWarps][256];
@@ -184,33 +189,36 @@ __global__ void __launch_bounds__(kScanThreads)
 // row_of[j] = the row that holds source position j (0-based): eight lanes per row write the row's
 // number over the row's positions. (One binary search in row_ptr per position, in order or through
 // the permutation, cost 1.1 ms where this costs well under a tenth of that.)
+template <typename I>
 __global__ void __launch_bounds__(256)
-    expand_rows_kernel(long long m, int base, const int* __restrict__ row_ptr, int* __restrict__ row_of) {
+    expand_rows_kernel(long long m, int base, const I* __restrict__ row_ptr, int* __restrict__ row_of) {
     const long long r = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;
     const int lane = threadIdx.x & 7;
     if (r >= m) return;
-    const int j1 = __ldg(row_ptr + r + 1) - base;
-    for (int j = __ldg(row_ptr + r) - base + lane; j < j1; j += 8) row_of[j] = (int)r;
+    const int j1 = (int)__ldg(row_ptr + r + 1) - base;
+    for (int j = (int)__ldg(row_ptr + r) - base + lane; j < j1; j += 8) row_of[j] = (int)r;
 }
 
 // out[k] = row_of[perm[k]]: the column index of the k-th nonzero of the transposed matrix.
 // (`sub` is taken off every gathered index: the index base when the source is a caller's array.)
+template <typename I>
 __global__ void __launch_bounds__(256)
-    gather_rows_kernel(long long nnz, const int* __restrict__ row_of, const unsigned* __restrict__ perm,
+    gather_rows_kernel(long long nnz, const I* __restrict__ row_of, const unsigned* __restrict__ perm,
                        int* __restrict__ out, int sub) {
     const long long k = 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x);
     if (k + 3 < nnz) {
         const uint4 p = __ldcs(reinterpret_cast<const uint4*>(perm + k));
-        const int4 r = make_int4(__ldg(row_of + p.x) - sub, __ldg(row_of + p.y) - sub, __ldg(row_of + p.z) - sub,
-                                 __ldg(row_of + p.w) - sub);
+        const int4 r = make_int4((int)__ldg(row_of + p.x) - sub, (int)__ldg(row_of + p.y) - sub,
+                                 (int)__ldg(row_of + p.z) - sub, (int)__ldg(row_of + p.w) - sub);
         *reinterpret_cast<int4*>(out + k) = r;
     } else {
-        for (long long i = k; i < nnz; ++i) out[i] = __ldg(row_of + perm[i]) - sub;
+        for (long long i = k; i < nnz; ++i) out[i] = (int)__ldg(row_of + perm[i]) - sub;
     }
 }
 
 // flag[0] = 1 if the indices are not in ascending order somewhere.
-__global__ void unsorted_flag_kernel(long long count, const int* __restrict__ idx, int* __restrict__ flag) {
+template <typename I>
+__global__ void unsorted_flag_kernel(long long count, const I* __restrict__ idx, int* __restrict__ flag) {
     const long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (j + 1 < count && __ldg(idx + j) > __ldg(idx + j + 1)) *flag = 1;
 }
@@ -280,7 +288,8 @@ TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_siz
 
 // Stable sort of the positions 0 .. nnz-1 by key (key - base in [0, 2^(8 passes))): leaves the sorted
 // 0-based keys in keys[final_slot()] and the permutation in perm[final_slot()].
-static cudaError_t radix_sort_positions(cudaStream_t s, int64_t nnz, int base, const int32_t* key_src,
+template <typename I>
+static cudaError_t radix_sort_positions(cudaStream_t s, int64_t nnz, int base, const I* key_src,
                                         const TransposePlan& p, void* buf) {
     char* b = static_cast<char*>(buf);
     int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
@@ -288,27 +297,30 @@ static cudaError_t radix_sort_positions(cudaStream_t s, int64_t nnz, int base, c
     unsigned* hist = reinterpret_cast<unsigned*>(b + p.off_hist);
     unsigned* sums = reinterpret_cast<unsigned*>(b + p.off_sums);
     cudaError_t e = cudaSuccess;
-    const int* src_keys = key_src;
-    const unsigned* src_perm = nullptr;
-    int sub = base;
     for (int pass = 0; pass < p.passes && nnz > 0; ++pass) {
         const int dst = pass & 1;
-        radix_hist_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, nnz, 8 * pass, hist, p.tiles);
+        const int shift = 8 * pass;
+        if (pass == 0)  // the caller's indices, with their base, and the identity permutation
+            radix_hist_kernel<I><<<(unsigned)p.tiles, kSortThreads, 0, s>>>(key_src, base, nnz, shift, hist, p.tiles);
+        else
+            radix_hist_kernel<int><<<(unsigned)p.tiles, kSortThreads, 0, s>>>(keys[dst ^ 1], 0, nnz, shift, hist, p.tiles);
         scan_chunk_sums_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
         scan_sums_kernel<<<1, kScanThreads, 0, s>>>(sums, p.scan_chunks);
         scan_apply_kernel<<<(unsigned)p.scan_chunks, kScanThreads, 0, s>>>(hist, p.hist_count, sums);
-        radix_scatter_kernel<<<(unsigned)p.tiles, kSortThreads, 0, s>>>(src_keys, sub, src_perm, keys[dst], perm[dst], nnz,
-                                                                         8 * pass, hist, p.tiles);
+        if (pass == 0)
+            radix_scatter_kernel<I><<<(unsigned)p.tiles, kSortThreads, 0, s>>>(key_src, base, nullptr, keys[dst], perm[dst],
+                                                                                nnz, shift, hist, p.tiles);
+        else
+            radix_scatter_kernel<int><<<(unsigned)p.tiles, kSortThreads, 0, s>>>(keys[dst ^ 1], 0, perm[dst ^ 1], keys[dst],
+                                                                                  perm[dst], nnz, shift, hist, p.tiles);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        src_keys = keys[dst];
-        src_perm = perm[dst];
-        sub = 0;
     }
     return e;
 }
 
-cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const int32_t* key_idx,
-                               const int32_t* other_idx, const TransposePlan& p, void* buf) {
+template <typename I>
+cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const I* key_idx,
+                               const I* other_idx, const TransposePlan& p, void* buf) {
     char* b = static_cast<char*>(buf);
     int32_t* ptr = reinterpret_cast<int32_t*>(b + p.off_ptr);
     int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
@@ -318,7 +330,7 @@ cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, i
     const int fin = p.final_slot();
     if ((e = coo_row_offsets(s, key_range, nnz, 0, keys[fin], ptr)) != cudaSuccess) return e;
     if (nnz > 0) {
-        gather_rows_kernel<<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, other_idx, perm[fin], keys[fin ^ 1], base);
+        gather_rows_kernel<I><<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, other_idx, perm[fin], keys[fin ^ 1], base);
         e = cudaGetLastError();
     }
     return e;
@@ -326,14 +338,15 @@ cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, i
 
 __device__ int g_unsorted_flag;  // result word of indices_unsorted (one check at a time per process)
 
-cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const int32_t* idx, int* host_flag) {
+template <typename I>
+cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* host_flag) {
     static std::mutex one_at_a_time;
     std::lock_guard<std::mutex> g(one_at_a_time);
     int* device_flag = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&device_flag), g_unsorted_flag);
     if (e == cudaSuccess) e = cudaMemsetAsync(device_flag, 0, sizeof(int), s);
     if (e == cudaSuccess && count > 1) {
-        unsorted_flag_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(count, idx, device_flag);
+        unsorted_flag_kernel<I><<<(unsigned)((count + 255) / 256), 256, 0, s>>>(count, idx, device_flag);
         e = cudaGetLastError();
     }
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_flag, device_flag, sizeof(int), cudaMemcpyDeviceToHost, s);
@@ -341,8 +354,9 @@ cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const int32_t* idx, 
     return e;
 }
 
-cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const int32_t* row_ptr,
-                                const int32_t* col, const TransposePlan& p, void* buf) {
+template <typename I>
+cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nnz, int base, const I* row_ptr,
+                                const I* col, const TransposePlan& p, void* buf) {
     char* b = static_cast<char*>(buf);
     int32_t* ptr = reinterpret_cast<int32_t*>(b + p.off_ptr);
     int* keys[2] = {reinterpret_cast<int*>(b + p.off_keys[0]), reinterpret_cast<int*>(b + p.off_keys[1])};
@@ -356,8 +370,8 @@ cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nn
         // Both buffers the last pass did not write are free now: one takes the row of every source
         // position, the other the column indices of the transposed matrix.
         int* row_of = reinterpret_cast<int*>(perm[fin ^ 1]);
-        expand_rows_kernel<<<(unsigned)((m * 8 + 255) / 256), 256, 0, s>>>(m, base, row_ptr, row_of);
-        gather_rows_kernel<<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, row_of, perm[fin], keys[fin ^ 1], 0);
+        expand_rows_kernel<I><<<(unsigned)((m * 8 + 255) / 256), 256, 0, s>>>(m, base, row_ptr, row_of);
+        gather_rows_kernel<int><<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, row_of, perm[fin], keys[fin ^ 1], 0);
         e = cudaGetLastError();
     }
     return e;
@@ -373,6 +387,16 @@ cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const Tr
         conjugate);
     return cudaGetLastError();
 }
+
+#define INSTANTIATE_INDEX(I)                                                                                  \
+    template cudaError_t transpose_structure<I>(cudaStream_t, int64_t, int64_t, int64_t, int, const I*, const I*, \
+                                                const TransposePlan&, void*);                                   \
+    template cudaError_t coo_sort_structure<I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*,          \
+                                               const TransposePlan&, void*);                                    \
+    template cudaError_t indices_unsorted<I>(cudaStream_t, int64_t, const I*, int*);
+INSTANTIATE_INDEX(int32_t)
+INSTANTIATE_INDEX(int64_t)
+#undef INSTANTIATE_INDEX
 
 template cudaError_t transpose_values<float>(cudaStream_t, int64_t, const float*, const TransposePlan&, void*, bool);
 template cudaError_t transpose_values<double>(cudaStream_t, int64_t, const double*, const TransposePlan&, void*, bool);

@@ -193,8 +193,38 @@ def test_real_matrix_complex_vectors(handle, device, name, dtype, base, beta):
                                        C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
 
 
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+def test_complex_with_64bit_indices(handle, device, dtype):
+    """SpMV and SpMM with complex values and 64-bit indices agree bit for bit with the 32-bit run (SpMV at the
+    small tile size, the only one 64-bit indices use)."""
+    lengths = ADVERSARIAL_LENGTHS["long_then_short"] + ADVERSARIAL_LENGTHS["lengths_1_to_33"]
+    m, k, base, n = len(lengths), 9100, 1, 6
+    rp, col, val = csr_from_lengths(lengths, k, dtype, seed=59, base=base)
+    rng = np.random.default_rng(19)
+    x, B = cplx(rng, k, dtype), cplx(rng, k * n, dtype)
+    alpha = 0.5 + 0.25j
+    ys, cs = [], []
+    for idx in (np.int32, np.int64):
+        A = mc.CsrMatrix(m, k, up(rp.astype(idx), device), up(col.astype(idx), device), up(val, device), base=base)
+        d_y = torch.zeros(m, dtype=torch.from_numpy(val[:0]).dtype, device=device)
+        X, Y = mc.DnVec(up(x, device)), mc.DnVec(d_y)
+        buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y), dtype=torch.uint8, device=device)
+        mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=0.0)
+        d_c = torch.zeros(m * n, dtype=d_y.dtype, device=device)
+        Bm, Cm = mc.DnMat(up(B, device), k, n, n, ROW), mc.DnMat(d_c, m, n, n, ROW)
+        mc.spmm(handle, A, Bm, Cm, torch.empty(256, dtype=torch.uint8, device=device), alpha=alpha, beta=0.0)
+        torch.cuda.synchronize()
+        ys.append(d_y.cpu().numpy())
+        cs.append(d_c.cpu().numpy())
+    ref, d = oracle.spmv(rp, col, val, x, alpha, 0.0, base=base)
+    assert_close(ys[1], ref, d, TOL[np.dtype(dtype)], "complex SpMV, 64-bit indices")
+    refC, dC = oracle.spmm(rp, col, val, B, n, ROW, n, alpha, 0.0, base=base)
+    assert_close(cs[1].reshape(m, n), refC, dC, TOL[np.dtype(dtype)], "complex SpMM, 64-bit indices")
+    np.testing.assert_array_equal(cs[0], cs[1])
+
+
 def test_complex_refusals(handle, device):
-    """Complex values on the entry points that stay real-only, with 64-bit indices, or as A^H of a CSC matrix."""
+    """Complex values on the entry points that stay real-only, or as A^H of a CSC matrix."""
     rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.complex64)
     t = [up(a, device) for a in (rp, col, val)]
     A = mc.CsrMatrix(4, 5, *t)
@@ -206,8 +236,7 @@ def test_complex_refusals(handle, device):
     size = C.c_size_t()
     c32 = capi.MACA_C_32F
     assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0, C.byref(size)) == 0
-    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A64.d, X.d, pa, Y.d, c32, 0,
-                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A64.d, X.d, pa, Y.d, c32, 0, C.byref(size)) == 0
     assert lib.mcsparseB200SpMVNoAlloc(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
     csc = mc.CscMatrix.__new__(mc.CscMatrix)  # a CSC descriptor over the same arrays, only to query the status
     d = C.c_void_p()

@@ -134,9 +134,8 @@ def test_spmv_transpose_refusals(handle, device):
     one = C.c_float(1.0)
     pa = C.cast(C.pointer(one), C.c_void_p)
     size = C.c_size_t()
-    # 64-bit indices are not converted; the peer-push and built-in-buffer entry points take op(A) = A only
-    assert lib.mcsparseSpMV_bufferSize(handle.h, T, pa, A64.d, X.d, pa, Y.d, capi.MACA_R_32F, 0,
-                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
+    # the peer-push and built-in-buffer entry points take op(A) = A only; 64-bit indices are converted like 32-bit ones
+    assert lib.mcsparseSpMV_bufferSize(handle.h, T, pa, A64.d, X.d, pa, Y.d, capi.MACA_R_32F, 0, C.byref(size)) == 0
     t32 = [torch.from_numpy(a).to(device) for a in (rp, col, val)]
     A = mc.CsrMatrix(4, 5, *t32)
     assert lib.mcsparseB200SpMVNoAlloc(handle.h, T, pa, A.d, X.d, pa, Y.d, capi.MACA_R_32F,
@@ -225,3 +224,63 @@ def test_spmv_coo_any_order_and_transposed(handle, device, name, dtype, base, op
         np.testing.assert_array_equal(g_idx, other[order] - base)
         np.testing.assert_array_equal(g_val, val_s[order])
     lib.mcsparseDestroySpMat(d)
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.complex64])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "tile_straddle"])
+def test_converted_products_with_64bit_indices(handle, device, name, dtype):
+    """A^T x on CSR, A x and A^T x on CSC, A x and A^T x on (sorted) COO, all with 64-bit indices: the conversion
+    leaves the same 32-bit arrays as for 32-bit inputs, so the results agree bit for bit."""
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    m, n, base = lengths.size, max(int(lengths.max()), 1) + 9, 1
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=53, base=base)
+    rows = (np.repeat(np.arange(m), lengths) + base).astype(np.int32)
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+    maca = {np.float64: capi.MACA_R_64F, np.complex64: capi.MACA_C_32F}[dtype]
+    rng = np.random.default_rng(23)
+
+    def rand(count):
+        v = rng.uniform(-1, 1, count)
+        return (v + 1j * rng.uniform(-1, 1, count)).astype(dtype) if np.iscomplexobj(val) else v.astype(dtype)
+
+    xn, xm = rand(n), rand(m)
+    alpha, beta = (0.5, 0.0)
+
+    class Holder:
+        pass
+
+    def make(kind, idx_dtype):
+        it = capi.MCSPARSE_INDEX_64I if idx_dtype == np.int64 else capi.MCSPARSE_INDEX_32I
+        d = C.c_void_p()
+        if kind == "csr":
+            t = [up(rp.astype(idx_dtype), device), up(col.astype(idx_dtype), device), up(val, device)]
+            capi.check(lib.mcsparseCreateCsr(C.byref(d), m, n, col.size, mc.host._ptr(t[0]), mc.host._ptr(t[1]),
+                                             mc.host._ptr(t[2]), it, it, base, maca))
+        elif kind == "csc":
+            t = [up((t_ptr + base).astype(idx_dtype), device), up((t_idx + base).astype(idx_dtype), device),
+                 up(val[perm], device)]
+            capi.check(lib.mcsparseCreateCsc(C.byref(d), m, n, col.size, mc.host._ptr(t[0]), mc.host._ptr(t[1]),
+                                             mc.host._ptr(t[2]), it, it, base, maca))
+        else:
+            t = [up(rows.astype(idx_dtype), device), up(col.astype(idx_dtype), device), up(val, device)]
+            capi.check(lib.mcsparseCreateCoo(C.byref(d), m, n, col.size, mc.host._ptr(t[0]), mc.host._ptr(t[1]),
+                                             mc.host._ptr(t[2]), it, base, maca))
+        A = Holder()
+        A.d, A.dtype, A.keep = d, t[2].dtype, t
+        return A
+
+    ref_n, d_n = oracle.spmv(rp, col, val, xn, alpha, beta, base=base)
+    ref_t, d_t = oracle.spmv(t_ptr, t_idx, val[perm], xm, alpha, beta)
+    for kind, ops in (("csr", (T,)), ("csc", (N, T)), ("coo", (N, T))):
+        for op in ops:
+            out = []
+            for idx_dtype in (np.int32, np.int64):
+                A = make(kind, idx_dtype)
+                x, ylen = (xn, m) if op == N else (xm, n)
+                d_y, _, _ = run(handle, device, A, op, x, np.zeros(ylen, dtype), alpha, beta)
+                out.append(d_y.cpu().numpy())
+                lib.mcsparseDestroySpMat(A.d)
+            ref, d = (ref_n, d_n) if op == N else (ref_t, d_t)
+            assert_close(out[1], ref, d, TOL[np.dtype(dtype)], f"{kind} op {op} 64-bit")
+            if not (kind == "coo" and op == N):  # sorted 32-bit COO takes the direct path, 64-bit COO is re-sorted
+                np.testing.assert_array_equal(out[0], out[1])
