@@ -245,6 +245,17 @@ mcsparseStatus_t mcsparseCooGet(mcsparseSpMatDescr_t spMatDescr, int64_t* rows, 
 mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t spMatDescr, void* cooRows, void* cooColumns,
                                         void* cooValues);
 
+/* ---- COO stored as an array of (row, column) pairs, accepted by mcsparseSpMV (32-bit indices).
+ *      Reference: mcsparse/include/interface/mcsp_generic.h:188-196, mcsparse/src/common/mcsp_helper.cpp:486-500,568-585.
+ *      The pairs are split into two arrays in the external buffer (as the reference does,
+ *      mcsp_spmv_gpu.cpp:773-789) and the entries are sorted there; any entry order is accepted. ---- */
+mcsparseStatus_t mcsparseCreateCooAoS(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                      void* cooInd, void* cooValues, mcsparseIndexType_t cooIdxType,
+                                      mcsparseIndexBase_t idxBase, macaDataType valueType);
+mcsparseStatus_t mcsparseCooAoSGet(mcsparseSpMatDescr_t spMatDescr, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                   void** cooInd, void** cooValues, mcsparseIndexType_t* idxType,
+                                   mcsparseIndexBase_t* idxBase, macaDataType* valueType);
+
 /* ---- CSC sparse matrix descriptor, accepted by mcsparseSpMV (32-bit indices).
  *      Reference: mcsp_helper.h.in:69-72, mcsparse/src/common/mcsp_helper.cpp:447-452,607-615.
  *      The CSC arrays are the CSR arrays of the transposed matrix: op(A) = A^T on a CSC matrix runs the CSR

@@ -88,6 +88,8 @@ PROTOTYPES = {
     "mcsparseCreateCoo": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i]),
     "mcsparseCooGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pvp, _pvp, _pi, _pi, _pi]),
     "mcsparseCooSetPointers": (_i, [_vp, _vp, _vp, _vp]),
+    "mcsparseCreateCooAoS": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _i, _i, _i]),
+    "mcsparseCooAoSGet": (_i, [_vp, _pi64, _pi64, _pi64, _pvp, _pvp, _pi, _pi, _pi]),
     "mcsparseCreateCsc": (_i, [_pvp, _i64, _i64, _i64, _vp, _vp, _vp, _i, _i, _i, _i]),
     "mcsparseCscSetPointers": (_i, [_vp, _vp, _vp, _vp]),
     "mcsparseDestroySpMat": (_i, [_vp]),

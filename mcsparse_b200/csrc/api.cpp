@@ -133,8 +133,9 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         return NOT_IMPL;
     if (need_buffer && buffer == nullptr) return BAD_POINTER;
     if (!(A->format == MCSPARSE_FORMAT_CSR || (allow_coo && A->format == MCSPARSE_FORMAT_COO) ||
-          (allow_transposed && A->format == MCSPARSE_FORMAT_CSC)))
+          (allow_transposed && (A->format == MCSPARSE_FORMAT_CSC || A->format == MCSPARSE_FORMAT_COO_AOS))))
         return NOT_IMPL;
+    if (A->format == MCSPARSE_FORMAT_COO_AOS && !narrow) return NOT_IMPL;  // pairs are split as 32-bit integers
     const bool n_op = opA == MCSPARSE_OPERATION_NON_TRANSPOSE;
     if (!((n_op && X->size == A->col_num && Y->size == A->row_num) ||
           (!n_op && X->size == A->row_num && Y->size == A->col_num)))
@@ -303,6 +304,20 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
     return from_cuda(e);
 }
 
+// COO as an array of (row, column) pairs: the pairs are split into two arrays behind the rest of the buffer
+// (the reference does the same first, mcsp_spmv_gpu.cpp:773-789) and the entries then go through the sort.
+CsrView aos_view(const mcsparseSpMatDescr* A, mcsparseOperation_t opA, int32_t* split_rows, int32_t* split_cols) {
+    CsrView v;
+    const bool t_op = opA != MCSPARSE_OPERATION_NON_TRANSPOSE;
+    v.conjugate = opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE && is_complex_fp(A->valueType);
+    v.coo_sort = true;
+    if (t_op)
+        v.m = A->row_num, v.n = A->col_num, v.ptr = split_cols, v.idx = split_rows;
+    else
+        v.m = A->col_num, v.n = A->row_num, v.ptr = split_rows, v.idx = split_cols;
+    return v;
+}
+
 // Layout of the external buffer of a transposed product: the SpMV work area of the n x m transposed
 // matrix, then (256-byte aligned) the conversion area described by TransposePlan.
 struct TransposedLayout {
@@ -399,11 +414,29 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
                        push.count == 0, push.count == 0);
     if (st != OK) return st;
     // mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:217-225
-    if (A->rows == nullptr || A->cols == nullptr || A->vals == nullptr || X->values == nullptr ||
+    const bool aos = A->format == MCSPARSE_FORMAT_COO_AOS;  // one index array (kept in `rows`)
+    if (A->rows == nullptr || (A->cols == nullptr && !aos) || A->vals == nullptr || X->values == nullptr ||
         Y->values == nullptr || A->mat_descr == nullptr)
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
     DeviceGuard guard(h->device);
+    if (aos) {
+        const int64_t out_rows = opA == MCSPARSE_OPERATION_NON_TRANSPOSE ? A->row_num : A->col_num;
+        CsrView probe;
+        probe.m = A->row_num + A->col_num - out_rows, probe.n = out_rows;
+        char* tail = static_cast<char*>(align_up_256(buffer)) + transposed_buffer_bytes(probe, A->nnz, value_size(computeType));
+        int32_t* split_rows = reinterpret_cast<int32_t*>(tail);
+        int32_t* split_cols = reinterpret_cast<int32_t*>(tail + ((size_t(A->nnz) * 4 + 255) & ~size_t(255)));
+        cudaError_t e = split_index_pairs(h->stream, A->nnz, static_cast<const int32_t*>(A->rows), split_rows, split_cols);
+        if (e != cudaSuccess) return from_cuda(e);
+        const CsrView view = aos_view(A, opA, split_rows, split_cols);
+        switch (computeType) {
+            case MACA_R_64F: return spmv_transposed_run<double>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            case MACA_C_32F: return spmv_transposed_run<cfloat>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            case MACA_C_64F: return spmv_transposed_run<cdouble>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+            default: return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
+        }
+    }
     if (real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType)) {
         if (preprocess_only) return OK;  // nothing to record: the buffer only holds the intermediate product
         void* z = align_up_256(buffer);
@@ -1073,6 +1106,35 @@ mcsparseStatus_t mcsparseCooSetPointers(mcsparseSpMatDescr_t d, void* cooRows, v
     return mcsparseCsrSetPointers(d, cooRows, cooColumns, cooValues);
 }
 
+// COO as an array of (row, column) pairs (mcsparse/src/common/mcsp_helper.cpp:486-500, :568-585): the pair
+// array is kept in `rows`, `cols` stays null.
+mcsparseStatus_t mcsparseCreateCooAoS(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                      void* cooInd, void* cooValues, mcsparseIndexType_t cooIdxType,
+                                      mcsparseIndexBase_t idxBase, macaDataType valueType) {
+    if (cooInd == nullptr) return pub(BAD_POINTER);
+    mcsparseStatus_t st = mcsparseCreateCsr(spMatDescr, rows, cols, nnz, cooInd, nullptr, cooValues, cooIdxType, cooIdxType,
+                                            idxBase, valueType);
+    if (st == MCSPARSE_STATUS_SUCCESS) (*spMatDescr)->format = MCSPARSE_FORMAT_COO_AOS;
+    return st;
+}
+
+mcsparseStatus_t mcsparseCooAoSGet(mcsparseSpMatDescr_t d, int64_t* rows, int64_t* cols, int64_t* nnz, void** cooInd,
+                                   void** cooValues, mcsparseIndexType_t* idxType, mcsparseIndexBase_t* idxBase,
+                                   macaDataType* valueType) {
+    if (d == nullptr || rows == nullptr || cols == nullptr || nnz == nullptr || cooInd == nullptr ||
+        cooValues == nullptr || idxType == nullptr || idxBase == nullptr || valueType == nullptr)
+        return pub(BAD_POINTER);
+    *rows = d->row_num;
+    *cols = d->col_num;
+    *nnz = d->nnz;
+    *cooInd = d->rows;
+    *cooValues = d->vals;
+    *idxType = d->rowIdxType;
+    *idxBase = d->idxBase;
+    *valueType = d->valueType;
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
 // CSC: the descriptor keeps the row indices in `rows` and the column offsets in `cols`, as the
 // reference does (mcsparse/src/common/mcsp_helper.cpp:447-452, :607-615).
 mcsparseStatus_t mcsparseCreateCsc(mcsparseSpMatDescr_t* spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
@@ -1249,6 +1311,12 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     // also needs room for the row offsets derived from its row indices.
     if (real_matrix_complex_vectors(matA->valueType, vecX->valueType, vecY->valueType, computeType)) {
         *bufferSize = size_t(matA->row_num) * value_size(computeType) + 512;  // the intermediate A * x
+        return MCSPARSE_STATUS_SUCCESS;
+    }
+    if (matA->format == MCSPARSE_FORMAT_COO_AOS) {  // sort path + the two arrays the pairs are split into
+        const CsrView v = aos_view(matA, opA, nullptr, nullptr);
+        *bufferSize = 256 + transposed_buffer_bytes(v, matA->nnz, value_size(computeType)) +
+                      2 * ((size_t(matA->nnz) * 4 + 255) & ~size_t(255)) + 256;
         return MCSPARSE_STATUS_SUCCESS;
     }
     const CsrView view = csr_view(handle, matA, opA);

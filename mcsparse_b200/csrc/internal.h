@@ -243,6 +243,8 @@ cudaError_t transpose_structure(cudaStream_t s, int64_t m, int64_t n, int64_t nn
 template <typename I>
 cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, int base, const I* key_idx,
                                const I* other_idx, const TransposePlan& plan, void* buf);
+// Array-of-pairs COO indices (row0, col0, row1, col1, ...; 8-byte aligned) -> two arrays.
+cudaError_t split_index_pairs(cudaStream_t s, int64_t nnz, const int32_t* pairs, int32_t* rows, int32_t* cols);
 // *host_flag = 1 if idx[0 .. count) is not ascending (one kernel, a 4-byte copy, a stream synchronisation).
 template <typename I>
 cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* host_flag);

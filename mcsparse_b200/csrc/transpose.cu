@@ -216,6 +216,16 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// COO stored as an array of (row, column) pairs -> separate row and column arrays.
+__global__ void split_index_pairs_kernel(long long nnz, const int2* __restrict__ pairs, int* __restrict__ rows,
+                                         int* __restrict__ cols) {
+    const long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (j >= nnz) return;
+    const int2 p = __ldcs(pairs + j);
+    rows[j] = p.x;
+    cols[j] = p.y;
+}
+
 // flag[0] = 1 if the indices are not in ascending order somewhere.
 template <typename I>
 __global__ void unsorted_flag_kernel(long long count, const I* __restrict__ idx, int* __restrict__ flag) {
@@ -337,6 +347,13 @@ cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, i
 }
 
 __device__ int g_unsorted_flag;  // result word of indices_unsorted (one check at a time per process)
+
+cudaError_t split_index_pairs(cudaStream_t s, int64_t nnz, const int32_t* pairs, int32_t* rows, int32_t* cols) {
+    if (nnz == 0) return cudaSuccess;
+    split_index_pairs_kernel<<<(unsigned)((nnz + 255) / 256), 256, 0, s>>>(nnz, reinterpret_cast<const int2*>(pairs), rows,
+                                                                         cols);
+    return cudaGetLastError();
+}
 
 template <typename I>
 cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* host_flag) {

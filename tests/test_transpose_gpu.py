@@ -284,3 +284,48 @@ def test_converted_products_with_64bit_indices(handle, device, name, dtype):
             assert_close(out[1], ref, d, TOL[np.dtype(dtype)], f"{kind} op {op} 64-bit")
             if not (kind == "coo" and op == N):  # sorted 32-bit COO takes the direct path, 64-bit COO is re-sorted
                 np.testing.assert_array_equal(out[0], out[1])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.complex128])
+@pytest.mark.parametrize("op", [N, T])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty"])
+def test_spmv_coo_array_of_pairs(handle, device, name, dtype, op):
+    """COO given as one array of (row, column) pairs, entries shuffled."""
+    lengths = np.asarray(ADVERSARIAL_LENGTHS[name])
+    m, n, base = lengths.size, max(int(lengths.max()), 1) + 13, 1
+    rp, col, val = csr_from_lengths(lengths, n, dtype, seed=61, base=base)
+    rows = (np.repeat(np.arange(m), lengths) + base).astype(np.int32)
+    rng = np.random.default_rng(29)
+    shuffle = rng.permutation(col.size)
+    pairs = np.stack([rows[shuffle], col[shuffle]], axis=1).astype(np.int32).ravel()
+    t = [up(pairs, device), up(val[shuffle], device)]
+    maca = {np.float32: capi.MACA_R_32F, np.complex128: capi.MACA_C_64F}[dtype]
+    d = C.c_void_p()
+    capi.check(lib.mcsparseCreateCooAoS(C.byref(d), m, n, col.size, mc.host._ptr(t[0]), mc.host._ptr(t[1]),
+                                        capi.MCSPARSE_INDEX_32I, base, maca))
+    got = [C.c_int64(), C.c_int64(), C.c_int64(), C.c_void_p(), C.c_void_p(), C.c_int(), C.c_int(), C.c_int()]
+    capi.check(lib.mcsparseCooAoSGet(d, *[C.byref(g) for g in got]))
+    assert (got[0].value, got[1].value, got[2].value, got[7].value) == (m, n, col.size, maca)
+
+    class Holder:
+        pass
+
+    A = Holder()
+    A.d, A.dtype = d, t[1].dtype
+    xlen, ylen = (n, m) if op == N else (m, n)
+
+    def rand(count):
+        v = rng.uniform(-1, 1, count)
+        return (v + 1j * rng.uniform(-1, 1, count)).astype(dtype) if np.iscomplexobj(val) else v.astype(dtype)
+
+    x, y0 = rand(xlen), rand(ylen)
+    alpha, beta = (1.25, -0.5) if not np.iscomplexobj(val) else (1.25 - 0.5j, -0.5 + 0.75j)
+    for pre in (False, True):
+        d_y, _, _ = run(handle, device, A, op, x, y0, alpha, beta, preprocess=pre)
+        if op == N:
+            ref, dd = oracle.spmv(rp, col, val, x, alpha, beta, y0, base=base)
+        else:
+            t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, n, base)
+            ref, dd = oracle.spmv(t_ptr, t_idx, val[perm], x, alpha, beta, y0)
+        assert_close(d_y.cpu().numpy(), ref, dd, TOL[np.dtype(dtype)], f"{name} pairs op {op} preprocess {pre}")
+    lib.mcsparseDestroySpMat(d)
