@@ -157,3 +157,18 @@ def test_coo_descriptor_roundtrip():
                               C.byref(it), C.byref(b), None) == capi.MCSPARSE_STATUS_INVALID_VALUE
     assert lib.mcsparseCreateCoo(C.byref(d), 3, 4, -5, FAKE, FAKE, FAKE, 2, 0, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
     assert lib.mcsparseDestroySpMat(d) == 0
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """include/mcsparse.h is the C ABI: it must compile as C99 with nothing but the CUDA toolkit's C headers."""
+    import shutil
+    import subprocess
+
+    cuda_inc = "/usr/local/cuda/include"
+    if shutil.which("gcc") is None or not os.path.isdir(cuda_inc):
+        pytest.skip("needs gcc and the CUDA toolkit headers")
+    root = os.path.join(os.path.dirname(__file__), "..")
+    src = tmp_path / "abi.c"
+    src.write_text('#include "mcsparse.h"\nint main(void) { mcsparseHandle_t h = 0; (void)h; return 0; }\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(root, "include"), "-I",
+                    cuda_inc, str(src)], check=True)
