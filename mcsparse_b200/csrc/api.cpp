@@ -673,7 +673,7 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
         const void *alpha_dev, *beta_dev;
         int chunks, count, items_per_tile, base, value_bytes;
     } key;
-    static_assert(sizeof(Key) <= sizeof(A->push_graph_key), "key buffer too small");
+    static_assert(sizeof(Key) <= sizeof(A->push_graphs[0].key), "key buffer too small");
     std::memset(&key, 0, sizeof key);
     key.rows = rows, key.cols = A->cols, key.vals = A->vals, key.x = X->values, key.y = Y->values, key.buf = buf;
     key.stream = h->stream;
@@ -683,11 +683,20 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
     key.chunks = chunks, key.count = push.count, key.items_per_tile = ws.items_per_tile, key.base = base;
     key.value_bytes = (int)sizeof(T);
     std::lock_guard<std::mutex> g(A->lock);
-    if (!(A->push_graph != nullptr && A->push_graph_key_bytes == sizeof key &&
-          std::memcmp(A->push_graph_key, &key, sizeof key) == 0)) {
-        if (A->push_graph != nullptr) {
-            cudaGraphExecDestroy(A->push_graph);
-            A->push_graph = nullptr;
+    mcsparseSpMatDescr::PushGraph* slot = nullptr;
+    for (auto& cand : A->push_graphs)
+        if (cand.exec != nullptr && cand.key_bytes == sizeof key && std::memcmp(cand.key, &key, sizeof key) == 0)
+            slot = &cand;
+    if (slot == nullptr) {
+        slot = &A->push_graphs[0];  // an empty slot, else the least recently used one
+        for (auto& cand : A->push_graphs)
+            if (cand.exec == nullptr || (slot->exec != nullptr && cand.last_use < slot->last_use)) {
+                slot = &cand;
+                if (cand.exec == nullptr) break;
+            }
+        if (slot->exec != nullptr) {
+            cudaGraphExecDestroy(slot->exec);
+            slot->exec = nullptr;
         }
         cudaGraph_t graph = nullptr;
         // Captured from a stream of the handle's own: the caller's stream may be the legacy default
@@ -700,16 +709,17 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
             if (graph != nullptr) cudaGraphDestroy(graph);
             return from_cuda(queued != cudaSuccess ? queued : e);
         }
-        e = cudaGraphInstantiate(&A->push_graph, graph, 0);
+        e = cudaGraphInstantiate(&slot->exec, graph, 0);
         cudaGraphDestroy(graph);
         if (e != cudaSuccess) {
-            A->push_graph = nullptr;
+            slot->exec = nullptr;
             return from_cuda(e);
         }
-        std::memcpy(A->push_graph_key, &key, sizeof key);
-        A->push_graph_key_bytes = sizeof key;
+        std::memcpy(slot->key, &key, sizeof key);
+        slot->key_bytes = sizeof key;
     }
-    return from_cuda(cudaGraphLaunch(A->push_graph, h->stream));
+    slot->last_use = ++A->push_graph_clock;
+    return from_cuda(cudaGraphLaunch(slot->exec, h->stream));
 }
 
 // mcComplex / mcDoubleComplex and the kernels' complex types are both interleaved (re, im) pairs.

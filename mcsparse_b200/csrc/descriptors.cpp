@@ -374,7 +374,8 @@ mcsparseStatus_t mcsparseCscSetPointers(mcsparseSpMatDescr_t d, void* cscColOffs
 
 mcsparseStatus_t mcsparseDestroySpMat(mcsparseSpMatDescr_t d) {
     if (d == nullptr) return MCSPARSE_STATUS_SUCCESS;
-    if (d->push_graph != nullptr) cudaGraphExecDestroy(d->push_graph);
+    for (auto& g : d->push_graphs)
+        if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
     delete d->mat_descr;
     delete d;
     return MCSPARSE_STATUS_SUCCESS;

@@ -84,9 +84,17 @@ struct mcsparseSpMatDescr {
     bool coo_unsorted = false;
     // The pipelined push of one step (tile launches, fix-ups, per-destination copies and the events
     // between them) captured once as a CUDA graph and replayed while every argument stays the same.
-    cudaGraphExec_t push_graph = nullptr;
-    unsigned char push_graph_key[256] = {};
-    size_t push_graph_key_bytes = 0;
+    // A few are kept (least recently used one replaced): a solver that alternates between two vector pairs
+    // replays two graphs instead of re-capturing on every call.
+    static constexpr int kPushGraphs = 4;
+    struct PushGraph {
+        cudaGraphExec_t exec = nullptr;
+        unsigned char key[256] = {};
+        size_t key_bytes = 0;
+        uint64_t last_use = 0;
+    };
+    PushGraph push_graphs[kPushGraphs];
+    uint64_t push_graph_clock = 0;
     // Column panels recorded by mcsparseSpMM_preprocess: buffer, arrays and shape they were built for.
     void* spmm_buffer = nullptr;
     const void* spmm_rows = nullptr;

@@ -158,3 +158,36 @@ def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, 
     assert torch.isnan(peer[:offset]).all() and torch.isnan(peer[offset + w.rows:]).all()
     assert lib.mcsparseB200SpMVPush(handle.h, 0, pa, A.d, X.d, pb, Y2.d, host._DTYPE[cfg.dtype], 0, host._ptr(buf),
                                     8, arr, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
+
+
+def test_pipelined_push_replays_with_alternating_vectors(handle, device, monkeypatch):
+    """The pipelined push replays a captured graph per set of arguments and keeps a few of them: a caller that
+    cycles through more vector pairs than are kept must still get every product right."""
+    from mcsparse_b200 import host
+
+    monkeypatch.setenv("MCSPARSE_B200_PUSH_CHUNKS", "4")
+    cfg = workloads.scaled("C5", 512)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    pairs = 5
+    xs = [workloads.dense_values(cfg, device, w.cols, 90 + i) for i in range(pairs)]
+    ys = [torch.zeros(w.rows, dtype=cfg.dtype, device=device) for _ in range(pairs)]
+    peers = [torch.zeros(w.rows, dtype=cfg.dtype, device=device) for _ in range(pairs)]
+    expect = []
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, mc.DnVec(xs[0]), mc.DnVec(ys[0])), dtype=torch.uint8, device=device)
+    for x in xs:
+        y = torch.zeros(w.rows, dtype=cfg.dtype, device=device)
+        mc.spmv(handle, A, mc.DnVec(x), mc.DnVec(y), buf, alpha=2.0, beta=0.0)
+        expect.append(y)
+    pa, pb, keep = host._scalars(handle, 2.0, 0.0, cfg.dtype)
+    X = [mc.DnVec(x) for x in xs]
+    Y = [mc.DnVec(y) for y in ys]
+    for step in range(3 * pairs):
+        i = step % pairs
+        ys[i].fill_(float("nan"))
+        peers[i].fill_(float("nan"))
+        arr = (C.c_void_p * 1)(peers[i].data_ptr())
+        capi.check(lib.mcsparseB200SpMVPush(handle.h, 0, pa, A.d, X[i].d, pb, Y[i].d, host._DTYPE[cfg.dtype], 0,
+                                            host._ptr(buf), 1, arr, 0))
+        torch.cuda.synchronize()
+        assert torch.equal(ys[i], expect[i]) and torch.equal(peers[i], expect[i]), f"step {step}"
