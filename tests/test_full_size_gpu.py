@@ -105,3 +105,31 @@ def test_c4_full_sampled_rows(handle, device, n):
         rp = (w.row_ptr[r0:r1 + 1] - w.row_ptr[r0]).cpu()
         ref, d = oracle.spmm(rp, w.col[a0:a1].cpu(), w.val[a0:a1].cpu(), Bh, n, 2, n, 1.0, 0.0)
         assert_close(Cout[r0:r1].cpu().numpy(), ref, d, 1e-5, f"C4 n={n} rows from {r0}")
+
+
+def test_c5_full_transposed_equals_plain_product(handle, device):
+    """The 27-point stencil is symmetric, so A^T x must reproduce A x: checks the conversion at full size
+    (three radix passes over 449 M nonzeros, digit counts scanned in more than one 1024-chunk round) and
+    the converted structure against the source (the transpose of a symmetric pattern is the pattern)."""
+    from mcsparse_b200 import capi
+
+    w = workloads.generate("C5", device)
+    y_plain = _run(handle, device, w, w.x, 1.0, 0.0)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    y = torch.zeros(w.cols, dtype=w.val.dtype, device=device)
+    X, Y = mc.DnVec(w.x), mc.DnVec(y)
+    T = capi.MCSPARSE_OPERATION_TRANSPOSE
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=T), dtype=torch.uint8, device=device)
+    mc.spmv_preprocess(handle, A, X, Y, buf, op=T)
+    mc.spmv(handle, A, X, Y, buf, alpha=1.0, beta=0.0, op=T)
+    torch.cuda.synchronize()
+    # same rows, same columns in the same (ascending) order, same values: the very same sums
+    assert torch.equal(y, y_plain)
+    import ctypes as C
+
+    rows, p_ptr, p_idx, p_val = C.c_int64(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+    capi.check(capi.lib.mcsparseB200SpMVTransposedView(A.d, T, C.c_void_p(buf.data_ptr()), C.byref(rows), C.byref(p_ptr),
+                                                       C.byref(p_idx), C.byref(p_val)))
+    off_ptr, off_idx = p_ptr.value - buf.data_ptr(), p_idx.value - buf.data_ptr()
+    assert torch.equal(buf[off_ptr:off_ptr + 4 * (w.rows + 1)].view(torch.int32), w.row_ptr)
+    assert torch.equal(buf[off_idx:off_idx + 4 * w.nnz].view(torch.int32), w.col)
