@@ -357,7 +357,8 @@ def cpu_baseline(name, seconds=12.0, steps=None, warmup=1):
 def run_reference(args, rank):
     if rank != 0:
         return
-    base, dt, steps = cpu_baseline(args.workload, steps=args.steps, warmup=max(1, min(args.warmup, 3)))
+    # at least ten untimed passes: the OpenMP team and the caches are cold in a process that has done nothing else
+    base, dt, steps = cpu_baseline(args.workload, steps=args.steps, warmup=max(10, args.warmup))
     from mcsparse_b200 import workloads
 
     cfg = workloads.CONFIGS[args.workload]
