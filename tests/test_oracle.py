@@ -224,3 +224,46 @@ def test_complex_oracle_matches_golden(case):
     out, dC = oracle.spmm(gc("row_ptr"), gc("col"), gc("val"), B, B.shape[1], 2, B.shape[1], alpha, beta, C0,
                           B.shape[1], 2, base=base)
     assert_close(out, gc("C"), gc("dC"), 1e-14, case + " SpMM")
+
+
+def _random_lengths(rng, rows):
+    kind = rng.integers(0, 4)
+    if kind == 0:
+        return rng.integers(0, 4, rows)
+    if kind == 1:
+        return rng.poisson(6.0, rows)
+    if kind == 2:
+        L = rng.integers(0, 3, rows)
+        L[rng.integers(0, rows, max(1, rows // 50))] = rng.integers(100, 700)
+        return L
+    return np.where(rng.random(rows) < 0.9, 0, rng.integers(1, 40, rows))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_partition_and_transposition_invariants(seed):
+    """Properties that hold for any matrix: the merge-path partition tiles the (rows + nnz) merge list without
+    gaps, every tile start is a valid merge point; transposing twice gives the matrix back; the permutation of a
+    transposition is a permutation."""
+    rng = np.random.default_rng(1000 + seed)
+    rows, base = int(rng.integers(1, 900)), int(rng.integers(0, 2))
+    lengths = _random_lengths(rng, rows)
+    ncols = int(max(lengths.max(), 1) + rng.integers(0, 50))
+    rp, col, val = csr_from_lengths(lengths, ncols, np.float64, seed=seed, base=base)
+    nnz = col.size
+    for items in (64, 1024, 2048):
+        part = oracle.merge_path_partition(rp, nnz, items, base)
+        assert (part[0] == (0, 0)).all() and (part[-1] == (rows, nnz)).all()
+        assert (np.diff(part[:, 0]) >= 0).all() and (np.diff(part[:, 1]) >= 0).all()
+        covered = np.diff(part.sum(axis=1))
+        assert (covered[:-1] == items).all() and 0 < covered[-1] <= items if covered.size else True
+        r, k = part[:, 0], part[:, 1]
+        ends = rp[1:].astype(np.int64) - base
+        # at a tile start (r, k): every earlier row has ended by nonzero k, and row r has not ended before it
+        assert all(r[i] == 0 or ends[r[i] - 1] <= k[i] for i in range(len(r)))
+        assert all(r[i] == rows or ends[r[i]] > k[i] - 1 or k[i] == 0 for i in range(len(r)))
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, ncols, base)
+    assert sorted(perm.tolist()) == list(range(nnz))
+    b_ptr, b_idx, perm2 = oracle.csr_transpose(t_ptr, t_idx, rows, 0)
+    np.testing.assert_array_equal(b_ptr, rp.astype(np.int64) - base)
+    np.testing.assert_array_equal(b_idx, col.astype(np.int64) - base)
+    np.testing.assert_array_equal(val[perm][perm2], val)
