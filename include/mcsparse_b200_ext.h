@@ -22,6 +22,10 @@ extern "C" {
 #define MCSPARSE_B200_SPMV_TILE_ITEMS_C64 1024 /* 16-byte values (complex double): one tile size */
 #define MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 1024
 
+/* L2 bytes (MiB) that one column panel of B may occupy in the panelled SpMM (mcsparseSpMM_preprocess);
+ * the environment variable MCSPARSE_B200_SPMM_PANEL_MB overrides it, 0 turns the panels off. */
+#define MCSPARSE_B200_SPMM_PANEL_MB_DEFAULT 40
+
 /*
  * mcsparseSpMV_preprocess: same argument list as mcsparseSpMV. Runs the merge-path
  * analysis for matA into externalBuffer and records on matA that this buffer holds it, so
@@ -63,13 +67,29 @@ mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcspa
                                                 const int32_t** colInd, const void** values);
 
 /*
- * Device-side status of the SpMV calls that used externalBuffer since its last analysis: 0, or 1
- * if a thread block gave up its bounded wait (about a second of SM clocks) for the bulk copies
- * of its tile and left its rows unwritten. Synchronises the handle's stream. The reference has
- * no device-side waits and no such query.
+ * Device-side status of the SpMV calls that used externalBuffer since its last analysis (pass
+ * NULL for the built-in work area of mcsparseB200SpMVNoAlloc): 0; bit 0 set if a thread block gave
+ * up its bounded wait for the bulk copies of its tile and left its rows unwritten; bit 1 set if a
+ * wait exceeded the limit but the copies then arrived and the tile was computed (a warning).
+ * Synchronises the handle's stream. A tile that was given up is also reported without any
+ * synchronisation: the kernel sets a word in pinned host memory owned by the handle, and the next
+ * mcsparseSpMV / mcsparseB200SpMVPush / mcsparseB200SpMVNoAlloc call on that handle returns
+ * MCSPARSE_STATUS_EXECUTION_FAILED once (and clears the word) before doing anything else.
+ * The reference has no device-side waits and no such query.
  */
 mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMatDescr_t matA,
                                            void* externalBuffer, int* status);
+
+/*
+ * How long a thread block of the tiled SpMV kernels waits for the bulk copies of its tile before
+ * it reports a failure instead of spinning: smClocks SM clock cycles (default 40,000,000, about
+ * 20 ms; a healthy copy takes microseconds). After the limit the block sets the status words
+ * described above, stays resident for 256 times the limit in case its copies still land, and
+ * returns. withholdCopies != 0 is a diagnostics switch for tests of that path: the kernels then
+ * issue no bulk copy at all, so every wait runs out with nothing in flight and every tile is
+ * given up. No reference counterpart.
+ */
+mcsparseStatus_t mcsparseB200SetDeviceWaitLimit(mcsparseHandle_t handle, int64_t smClocks, int withholdCopies);
 
 /*
  * Row-block sharding of one CSR matrix over numShards GPUs, balanced by nonzeros:

@@ -89,51 +89,78 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     return OK;
 }
 
-// Tile size for this matrix: small tiles when neighbouring nonzeros rarely have neighbouring columns
-// (fewer than a quarter of 4096 sampled pairs within 8 columns). Probed once per column array
-// (one small kernel and a 4-byte copy, which synchronises the stream) and remembered on the
-// descriptor; MCSPARSE_B200_SPMV_TILE=small|large overrides. `scratch` is device memory the
-// probe may overwrite (the start of the work buffer, before the analysis writes it).
-bool probe_small_tiles(mcsparseContext* h, const int32_t* idx, int64_t nnz, int64_t rows, size_t vsize, void* scratch) {
+// Environment overrides for tuning: MCSPARSE_B200_SPMV_TILE=small|large fixes the tile size,
+// MCSPARSE_B200_SPMV_WALK=0|1 the kernel family. Returns the kind with the overrides applied.
+int apply_tile_overrides(int kind) {
     if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
-        if (e[0] == 's') return true;
-        if (e[0] == 'l') return false;
+        if (e[0] == 's') kind |= kTileSmall;
+        if (e[0] == 'l') kind &= ~kTileSmall;
     }
+    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_WALK")) {
+        if (e[0] == '1') kind |= kTileWalk;
+        if (e[0] == '0') kind &= ~kTileWalk;
+    }
+    return kind;
+}
+
+// Tile kind for this matrix. When neighbouring nonzeros rarely have neighbouring columns (fewer than
+// a quarter of 4096 sampled pairs within 8 columns) the matrix is gather-bound and gets the walk
+// kernel; otherwise the lanes-per-row kernel with the large tiles. Probed once per column array
+// (one small kernel and a 4-byte copy, which synchronises the stream) and remembered on the
+// descriptor. `scratch` is device memory the probe may overwrite (the start of the work buffer,
+// before the analysis writes it).
+int probe_tile_kind(mcsparseContext* h, const void* idx, bool wide, int64_t nnz, int64_t rows, size_t vsize,
+                    void* scratch) {
     int near = 4096;
-    if (nnz >= 2 && spmv_locality_probe(h->stream, nnz, idx, static_cast<int*>(scratch), &near) != cudaSuccess)
-        near = 4096;
-    bool small = near < 1024;
+    if (nnz >= 2) {
+        int* count = static_cast<int*>(scratch);
+        const cudaError_t e = wide ? spmv_locality_probe(h->stream, nnz, static_cast<const int64_t*>(idx), count, &near)
+                                   : spmv_locality_probe(h->stream, nnz, static_cast<const int32_t*>(idx), count, &near);
+        if (e != cudaSuccess) near = 4096;
+    }
+    int kind = near < 1024 ? (kTileWalk | kTileSmall) : kTileLarge;
+    if (wide) kind |= kTileSmall;  // 64-bit indices: one tile size
     // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
-    const int64_t large = spmv_workspace(rows, nnz, vsize, false).items_per_tile;
-    if ((rows + nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) small = true;
-    return small;
+    const int64_t large = spmv_workspace(rows, nnz, vsize, kTileLarge).items_per_tile;
+    if ((rows + nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) kind |= kTileSmall;
+    return apply_tile_overrides(kind);
 }
 
 // `idx` / `rows`: the index array and the row count the kernels will run on (for a CSC input these
 // are the row indices and the column count).
-bool choose_small_tiles(mcsparseContext* h, mcsparseSpMatDescr* A, const void* idx, int64_t rows, void* scratch) {
-    if (A->colIdxType == MCSPARSE_INDEX_64I) return true;  // one tile size for 64-bit indices
-    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
-        if (e[0] == 's') return true;
-        if (e[0] == 'l') return false;
-    }
+int choose_tile_kind(mcsparseContext* h, mcsparseSpMatDescr* A, const void* idx, int64_t rows, void* scratch) {
     std::lock_guard<std::mutex> g(A->lock);
-    if (A->probed_cols == idx && A->probed_nnz == A->nnz) return A->small_tiles;
-    A->small_tiles = probe_small_tiles(h, static_cast<const int32_t*>(idx), A->nnz, rows,
-                                       value_size(A->valueType), scratch);
+    if (A->probed_cols == idx && A->probed_nnz == A->nnz) return A->tile_kind;
+    A->tile_kind = probe_tile_kind(h, idx, A->colIdxType == MCSPARSE_INDEX_64I, A->nnz, rows, value_size(A->valueType),
+                                   scratch);
     A->probed_cols = idx;
     A->probed_nnz = A->nnz;
-    return A->small_tiles;
+    return A->tile_kind;
 }
 
-// The choice already made for this matrix, without probing (large tiles if none was made).
-bool known_small_tiles(mcsparseSpMatDescr* A) {
-    if (const char* e = std::getenv("MCSPARSE_B200_SPMV_TILE")) {
-        if (e[0] == 's') return true;
-        if (e[0] == 'l') return false;
-    }
+// The choice already made for this matrix, without probing (large tiles, lanes-per-row kernel if none was made).
+int known_tile_kind(mcsparseSpMatDescr* A) {
     std::lock_guard<std::mutex> g(A->lock);
-    return A->probed_cols == A->cols && A->probed_nnz == A->nnz && A->small_tiles;
+    if (A->probed_cols == A->cols && A->probed_nnz == A->nnz) return A->tile_kind;
+    return apply_tile_overrides(A->colIdxType == MCSPARSE_INDEX_64I ? kTileSmall : kTileLarge);
+}
+
+WaitCfg wait_cfg(const mcsparseContext* h) {
+    WaitCfg w;
+    w.limit_cycles = h->wait_cycles;
+    w.withhold = h->withhold_copies;
+    w.fault_word = h->fault_word_dev;
+    return w;
+}
+
+// A tile kernel of an earlier call on this handle gave up its bounded wait: reported once, by the
+// next compute call, as an execution failure (the word lives in pinned host memory the kernels can
+// write, so reading it needs no synchronisation).
+bool take_device_fault(mcsparseContext* h) {
+    if (h->fault_word_host == nullptr || *reinterpret_cast<volatile int*>(h->fault_word_host) == 0) return false;
+    *reinterpret_cast<volatile int*>(h->fault_word_host) = 0;
+    log_error("an earlier SpMV on this handle gave up a bounded device-side wait; its result is incomplete");
+    return true;
 }
 
 struct PushArgs {
@@ -204,9 +231,9 @@ CsrView csr_view(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseOperation_t 
 
 template <typename T, typename I>
 St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
-            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, bool small_tiles,
+            const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, int tile_kind,
             const PushArgs& push = PushArgs()) {
-    const SpmvWorkspace ws = spmv_workspace(v.m, A->nnz, sizeof(T), small_tiles, sizeof(I));
+    const SpmvWorkspace ws = spmv_workspace(v.m, A->nnz, sizeof(T), tile_kind, sizeof(I));
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
     const I* rows = static_cast<const I*>(v.ptr);
@@ -233,7 +260,7 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
     cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
                                      static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
-                                     buf, peers);
+                                     buf, peers, wait_cfg(h));
     return from_cuda(e);
 }
 
@@ -297,12 +324,13 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
     const int32_t* t_ptr = reinterpret_cast<const int32_t*>(area + L.plan.off_ptr);
     const int32_t* t_idx = reinterpret_cast<const int32_t*>(area + L.plan.off_keys[L.plan.col_slot()]);
     const T* t_val = reinterpret_cast<const T*>(area + L.plan.off_val);
-    bool cached = false, small = false, probed = false;
+    bool cached = false, probed = false;
+    int kind = kTileLarge;
     {
         std::lock_guard<std::mutex> g(A->lock);
         cached = A->trans_buffer == buffer && A->trans_ptr_src == v.ptr && A->trans_idx_src == v.idx && A->trans_nnz == nnz;
         probed = A->trans_probed_idx == v.idx && A->trans_probed_nnz == nnz;
-        small = A->trans_small_tiles;
+        kind = A->trans_tile_kind;
     }
     if (!cached) {
         {   // this buffer is about to hold the transposed matrix's partition: forget what else was recorded in it
@@ -313,14 +341,14 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
         cudaError_t e = convert_structure(h->stream, A, v, L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
         if (!probed) {  // tile size for the transposed matrix: probed once (synchronises), then remembered
-            small = probe_small_tiles(h, t_idx, nnz, v.n, sizeof(T), L.work);
+            kind = probe_tile_kind(h, t_idx, false, nnz, v.n, sizeof(T), L.work);
             std::lock_guard<std::mutex> g(A->lock);
             A->trans_probed_idx = v.idx;
             A->trans_probed_nnz = nnz;
-            A->trans_small_tiles = small;
+            A->trans_tile_kind = kind;
         }
     }
-    const SpmvWorkspace ws = spmv_workspace(v.n, nnz, sizeof(T), small);
+    const SpmvWorkspace ws = spmv_workspace(v.n, nnz, sizeof(T), kind);
     if (!cached) {
         cudaError_t e = spmv_analysis(h->stream, v.n, nnz, 0, t_ptr, ws, L.work);
         if (e != cudaSuccess) return from_cuda(e);
@@ -336,7 +364,8 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
     cudaError_t e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area, v.conjugate);
     if (e != cudaSuccess) return from_cuda(e);
     e = spmv_tiled<T, int32_t>(h->stream, v.n, nnz, 0, t_ptr, t_idx, t_val, static_cast<const T*>(X->values),
-                               static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, L.work);
+                               static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, L.work,
+                               PeerList<T>(), wait_cfg(h));
     return from_cuda(e);
 }
 
@@ -352,6 +381,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         Y->values == nullptr || A->mat_descr == nullptr)
         return BAD_POINTER;
     if (!descr_general(A->mat_descr)) return NOT_IMPL;
+    if (!preprocess_only && take_device_fault(h)) return EXEC_FAILED;
     DeviceGuard guard(h->device);
     if (aos) {
         const int64_t out_rows = opA == MCSPARSE_OPERATION_NON_TRANSPOSE ? A->row_num : A->col_num;
@@ -393,7 +423,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
             default: return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
         }
     }
-    const bool small = choose_small_tiles(h, A, view.idx, view.m, align_up_256(buffer));
+    const int small = choose_tile_kind(h, A, view.idx, view.m, align_up_256(buffer));
     const int ipt = spmv_workspace(view.m, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
     bool analyse = true;
     {
@@ -444,7 +474,8 @@ St csrmv_entry(mcsparseHandle_t h, mcsparseOperation_t transA, int m, int n, int
         void* buf = align_up_256(buffer);
         cudaError_t e = spmv_analysis(h->stream, m, nnz, descr->base, rows, ws, buf);
         if (e != cudaSuccess) return from_cuda(e);
-        return from_cuda(spmv_tiled<T, int32_t>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b, ws, buf));
+        return from_cuda(spmv_tiled<T, int32_t>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b, ws, buf,
+                                                PeerList<T>(), wait_cfg(h)));
     }
     return from_cuda(spmv_rowgroup<T>(h->stream, m, nnz, descr->base, rows, cols, vals, x, y, a, b));
 }
@@ -508,7 +539,7 @@ size_t spmm_conversion_bytes(const mcsparseSpMatDescr* A, size_t vsize, bool coo
 
 template <typename T, typename I>
 St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, mcsparseDnMatDescr* B,
-            mcsparseDnMatDescr* C, const void* alpha, const void* beta, int num_panels, const int* panel_ptr,
+            mcsparseDnMatDescr* C, const void* alpha, const void* beta, const SpmmPlan* plan, void* plan_buffer,
             void* conversion_area) {
     if (A->format != MCSPARSE_FORMAT_CSR) {
         // Convert into the buffer, then the CSR kernels on the (always 32-bit) result: a row-sorted 32-bit COO only
@@ -558,7 +589,7 @@ St spmm_run(mcsparseContext* h, mcsparseOperation_t opB, mcsparseSpMatDescr* A, 
                                 static_cast<const T*>(A->vals) + b * A->batchStride,
                                 static_cast<const T*>(B->values) + b * B->batchStride, b_rs, b_cs,
                                 static_cast<T*>(C->values) + b * C->batchStride, c_rs, c_cs, scalar_arg<T>(h, alpha),
-                                scalar_arg<T>(h, beta), single ? num_panels : 1, single ? panel_ptr : nullptr);
+                                scalar_arg<T>(h, beta), single ? plan : nullptr, single ? plan_buffer : nullptr);
         if (e != cudaSuccess) return from_cuda(e);
     }
     return OK;
@@ -602,7 +633,7 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
                               mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer,
                               const PushArgs& push, int chunks) {
     void* buf = align_up_256(buffer);
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_small_tiles(h, A, A->cols, A->row_num, buf));
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_tile_kind(h, A, A->cols, A->row_num, buf));
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
     if (h->side_stream == nullptr) {
@@ -653,7 +684,8 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
         return spmv_tiled_pipelined<T>(origin, h->side_stream, h->events, ps, chunks, A->push_chunk_tiles,
                                        A->push_chunk_rows, A->row_num, A->nnz, base, rows,
                                        static_cast<const int32_t*>(A->cols), static_cast<const T*>(A->vals),
-                                       static_cast<const T*>(X->values), static_cast<T*>(Y->values), a, b, ws, buf, peers);
+                                       static_cast<const T*>(X->values), static_cast<T*>(Y->values), a, b, ws, buf, peers,
+                                       wait_cfg(h));
     };
     // A step is some forty stream operations (launches, copies, event records and waits); issued one
     // by one they cost more host time than the step takes on the GPUs. So the sequence is captured as
@@ -787,7 +819,7 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
         return pub(BAD_POINTER);
     if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
     const SpmvWorkspace ws =
-        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_tile_kind(matA), index_size(matA));
     *itemsPerTile = ws.items_per_tile;
     *numTiles = ws.num_tiles;
     *tileStarts = static_cast<const int32_t*>(align_up_256(externalBuffer));
@@ -797,12 +829,18 @@ mcsparseStatus_t mcsparseB200SpMVPartitionView(mcsparseSpMatDescr_t matA, void* 
 mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMatDescr_t matA,
                                            void* externalBuffer, int* status) {
     if (handle == nullptr) return pub(BAD_HANDLE);
-    if (matA == nullptr || externalBuffer == nullptr || status == nullptr) return pub(BAD_POINTER);
+    if (matA == nullptr || status == nullptr) return pub(BAD_POINTER);
     if (!is_compute_type(matA->valueType)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
+    void* area = externalBuffer;
+    if (area == nullptr) {  // the built-in work area of mcsparseB200SpMVNoAlloc
+        size_t bytes = 0;
+        const cudaError_t e = spmv_static_scratch(&area, &bytes);
+        if (e != cudaSuccess) return pub(from_cuda(e));
+    }
     const SpmvWorkspace ws =
-        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_small_tiles(matA), index_size(matA));
-    const char* word = static_cast<const char*>(align_up_256(externalBuffer)) + ws.off_status;
+        spmv_workspace(matA->row_num, matA->nnz, value_size(matA->valueType), known_tile_kind(matA), index_size(matA));
+    const char* word = static_cast<const char*>(align_up_256(area)) + ws.off_status;
     cudaError_t e = cudaMemcpyAsync(status, word, sizeof(int), cudaMemcpyDeviceToHost, handle->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(handle->stream);
     return pub(from_cuda(e));
@@ -841,6 +879,7 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         vecY->values == nullptr || matA->mat_descr == nullptr)
         return pub(BAD_POINTER);
     if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
+    if (take_device_fault(handle)) return pub(EXEC_FAILED);
     DeviceGuard guard(handle->device);
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
@@ -856,8 +895,10 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         log_error(msg);
         return MCSPARSE_STATUS_INSUFFICIENT_RESOURCES;
     }
-    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType),
-                                            choose_small_tiles(handle, matA, matA->cols, matA->row_num, scratch));
+    // No probe here: the locality probe copies a word back and synchronises the stream, which this entry
+    // point must not do. A matrix that an earlier mcsparseSpMV / mcsparseSpMV_preprocess call already
+    // probed keeps its choice; any other gets the default kernel and tile size.
+    const SpmvWorkspace ws = spmv_workspace(matA->row_num, matA->nnz, value_size(computeType), known_tile_kind(matA));
     const int base = matA->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(matA->rows);
     e = spmv_analysis(handle->stream, matA->row_num, matA->nnz, base, rows, ws, scratch);
@@ -866,13 +907,23 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
         e = spmv_tiled<double, int32_t>(handle->stream, matA->row_num, matA->nnz, base, rows,
                                static_cast<const int32_t*>(matA->cols), static_cast<const double*>(matA->vals),
                                static_cast<const double*>(vecX->values), static_cast<double*>(vecY->values),
-                               scalar_arg<double>(handle, alpha), scalar_arg<double>(handle, beta), ws, scratch);
+                               scalar_arg<double>(handle, alpha), scalar_arg<double>(handle, beta), ws, scratch,
+                               PeerList<double>(), wait_cfg(handle));
     else
         e = spmv_tiled<float, int32_t>(handle->stream, matA->row_num, matA->nnz, base, rows,
                               static_cast<const int32_t*>(matA->cols), static_cast<const float*>(matA->vals),
                               static_cast<const float*>(vecX->values), static_cast<float*>(vecY->values),
-                              scalar_arg<float>(handle, alpha), scalar_arg<float>(handle, beta), ws, scratch);
+                              scalar_arg<float>(handle, alpha), scalar_arg<float>(handle, beta), ws, scratch,
+                              PeerList<float>(), wait_cfg(handle));
     return pub(from_cuda(e));
+}
+
+mcsparseStatus_t mcsparseB200SetDeviceWaitLimit(mcsparseHandle_t handle, int64_t smClocks, int withholdCopies) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (smClocks < 1) return pub(BAD_VALUE);
+    handle->wait_cycles = smClocks;
+    handle->withhold_copies = withholdCopies != 0;
+    return MCSPARSE_STATUS_SUCCESS;
 }
 
 // ----------------------------------------------------------------------------- SpMM
@@ -912,10 +963,10 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
     DeviceGuard guard(handle->device);
     const cudaError_t e =
         matA->rowIdxType == MCSPARSE_INDEX_64I
-            ? spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base,
+            ? spmm_preprocess(handle->stream, matA->row_num, matA->nnz, matA->mat_descr->base,
                               static_cast<const int64_t*>(matA->rows), static_cast<const int64_t*>(matA->cols), plan,
                               align_up_256(externalBuffer))
-            : spmm_preprocess(handle->stream, matA->row_num, matA->mat_descr->base,
+            : spmm_preprocess(handle->stream, matA->row_num, matA->nnz, matA->mat_descr->base,
                               static_cast<const int32_t*>(matA->rows), static_cast<const int32_t*>(matA->cols), plan,
                               align_up_256(externalBuffer));
     if (e != cudaSuccess) return MCSPARSE_STATUS_SUCCESS;
@@ -923,6 +974,7 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
     matA->spmm_rows = matA->rows;
     matA->spmm_cols = matA->cols;
     matA->spmm_panels = plan.num_panels;
+    matA->spmm_lanes = plan.lanes;
     matA->spmm_n = matC->col_num;
     return MCSPARSE_STATUS_SUCCESS;
 }
@@ -939,32 +991,32 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
         return pub(BAD_POINTER);
     if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
-    int panels = 1;
-    const int* panel_ptr = nullptr;
+    const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
+    const SpmmPlan* use_plan = nullptr;
+    void* plan_buffer = nullptr;
     {
         std::lock_guard<std::mutex> g(matA->lock);
-        const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
         if (matA->spmm_buffer == externalBuffer && matA->spmm_rows == matA->rows && matA->spmm_cols == matA->cols &&
-            matA->spmm_n == matC->col_num && matA->spmm_panels == plan.num_panels && plan.num_panels > 1) {
-            panels = plan.num_panels;
-            panel_ptr = static_cast<const int*>(align_up_256(externalBuffer));
+            matA->spmm_n == matC->col_num && matA->spmm_panels == plan.num_panels && matA->spmm_lanes == plan.lanes &&
+            plan.num_panels > 1) {
+            use_plan = &plan;
+            plan_buffer = align_up_256(externalBuffer);
         }
     }
     // A COO or CSC input is converted behind the (panel) plan's part of the buffer.
-    void* conversion_area =
-        static_cast<char*>(externalBuffer) + spmm_plan_for(opB, matA, matB, matC, computeType).bytes;
+    void* conversion_area = static_cast<char*>(externalBuffer) + plan.bytes;
     const bool wide = index_size(matA) == 8;
     if (computeType == MACA_C_32F)
-        return pub(wide ? spmm_run<cfloat, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
-                        : spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+        return pub(wide ? spmm_run<cfloat, int64_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area)
+                        : spmm_run<cfloat, int32_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area));
     if (computeType == MACA_C_64F)
-        return pub(wide ? spmm_run<cdouble, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
-                        : spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+        return pub(wide ? spmm_run<cdouble, int64_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area)
+                        : spmm_run<cdouble, int32_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area));
     if (computeType == MACA_R_64F)
-        return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
-                        : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
-    return pub(wide ? spmm_run<float, int64_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area)
-                    : spmm_run<float, int32_t>(handle, opB, matA, matB, matC, alpha, beta, panels, panel_ptr, conversion_area));
+        return pub(wide ? spmm_run<double, int64_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area)
+                        : spmm_run<double, int32_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area));
+    return pub(wide ? spmm_run<float, int64_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area)
+                    : spmm_run<float, int32_t>(handle, opB, matA, matB, matC, alpha, beta, use_plan, plan_buffer, conversion_area));
 }
 
 // ----------------------------------------------------------------------------- legacy entry points

@@ -20,6 +20,18 @@ mcsparseStatus_t mcsparseCreate(mcsparseHandle_t* handle) {
     if (ctx == nullptr) return MCSPARSE_STATUS_ALLOC_FAILED;
     ctx->device = dev;
     cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, dev);
+    // One word of pinned host memory that kernels can write: a tile kernel that gives up its bounded
+    // wait says so here, and the next compute call reports it without a synchronisation. Without it
+    // (allocation refused) such a failure is still recorded in the work buffer's status word.
+    void* word = nullptr;
+    if (cudaHostAlloc(&word, sizeof(int), cudaHostAllocMapped) == cudaSuccess) {
+        ctx->fault_word_host = static_cast<int*>(word);
+        *ctx->fault_word_host = 0;
+        void* dev_view = nullptr;
+        if (cudaHostGetDevicePointer(&dev_view, word, 0) == cudaSuccess) ctx->fault_word_dev = static_cast<int*>(dev_view);
+    } else {
+        cudaGetLastError();
+    }
     *handle = ctx;
     return MCSPARSE_STATUS_SUCCESS;
 }
@@ -37,6 +49,10 @@ mcsparseStatus_t mcsparseDestroy(mcsparseHandle_t handle) {
         for (auto& st : handle->peer_streams)
             if (st != nullptr) cudaStreamDestroy(st);
         if (handle->capture_stream != nullptr) cudaStreamDestroy(handle->capture_stream);
+    }
+    if (handle != nullptr && handle->fault_word_host != nullptr) {
+        DeviceGuard guard(handle->device);
+        cudaFreeHost(handle->fault_word_host);
     }
     delete handle;
     return MCSPARSE_STATUS_SUCCESS;

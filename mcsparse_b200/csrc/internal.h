@@ -32,6 +32,13 @@ struct mcsparseContext {
     cudaEvent_t fix_events[kMaxPushChunks] = {};
     cudaEvent_t peer_events[kMaxPeers] = {};
     cudaStream_t capture_stream = nullptr;  // origin stream while the step is captured as a graph
+    // Bounded device-side waits: how long a thread block waits for the bulk copies of its tile (SM clocks),
+    // and a word in pinned, device-mapped host memory that a kernel sets when it gave a tile up. The next
+    // compute call on the handle reads the word on the host (no synchronisation) and reports it.
+    long long wait_cycles = 40000000;  // about 20 ms of SM clocks
+    int withhold_copies = 0;           // diagnostics: issue no bulk copies, so that every wait runs out
+    int* fault_word_host = nullptr;
+    int* fault_word_dev = nullptr;
 };
 
 struct mcsparseMatDescr {
@@ -62,7 +69,7 @@ struct mcsparseSpMatDescr {
     // Tile size chosen by the locality probe for these column indices (probed once, then remembered).
     const void* probed_cols = nullptr;
     int64_t probed_nnz = -1;
-    bool small_tiles = false;
+    int tile_kind = 0;  // kTileSmall | kTileWalk
     // Chunk boundaries of the pipelined push (tiles and the rows they start at), read back once.
     void* push_buffer = nullptr;
     const void* push_rows_ptr = nullptr;
@@ -77,7 +84,7 @@ struct mcsparseSpMatDescr {
     int64_t trans_nnz = -1;
     const void* trans_probed_idx = nullptr;
     int64_t trans_probed_nnz = -1;
-    bool trans_small_tiles = false;
+    int trans_tile_kind = 0;
     // COO inputs: whether the row indices were found out of order (checked once per array, remembered).
     const void* coo_checked_rows = nullptr;
     int64_t coo_checked_nnz = -1;
@@ -100,6 +107,7 @@ struct mcsparseSpMatDescr {
     const void* spmm_rows = nullptr;
     const void* spmm_cols = nullptr;
     int spmm_panels = 0;
+    int spmm_lanes = 0;
     int64_t spmm_n = 0;
 };
 
@@ -149,17 +157,28 @@ struct PushStreams {
     cudaEvent_t* peer_events = nullptr;
 };
 
+// How the tile kernels wait for their bulk copies: the limit in SM clocks, the diagnostics switch that
+// withholds the copies, and the device address of the handle's host-visible fault word (may be null).
+struct WaitCfg {
+    long long limit_cycles = 40000000;
+    int withhold = 0;
+    int* fault_word = nullptr;
+};
+
 // Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
 //   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status
 // status stays 0 unless a kernel gave up a bounded wait (zeroed by the analysis kernel).
 struct SpmvWorkspace {
     int items_per_tile = 0;
+    bool walk = false;  // scattered columns: every tile takes the thread-per-merge-segment walk kernel
     int64_t num_tiles = 0;
     size_t off_carry_row = 0, off_carry_val = 0, off_status = 0, bytes = 0;
 };
 // Layout for the chosen tile size; `bytes` is always the size the small tiles would need, so that
 // mcsparseSpMV_bufferSize does not depend on the choice.
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles = false,
+// tile_kind: kTileSmall for the half-size tile, kTileWalk for the walk kernel (they combine).
+enum : int { kTileLarge = 0, kTileSmall = 1, kTileWalk = 2 };
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile_kind = kTileLarge,
                              size_t index_size = 4);
 // Counts, over 4096 evenly spaced positions j, how often |col[j + 1] - col[j]| <= 8; the count is left
 // in *device_count and copied to *host_count (synchronises the stream).
@@ -176,7 +195,7 @@ cudaError_t spmv_analysis(cudaStream_t s, int64_t m, int64_t nnz, int base, cons
 template <typename T, typename I>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col, const T* val,
                        const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                       const PeerList<T>& peers = PeerList<T>());
+                       const PeerList<T>& peers = PeerList<T>(), const WaitCfg& wait = WaitCfg());
 // Rows at which the given tiles start, copied to the host (synchronises the stream).
 cudaError_t spmv_read_tile_rows(cudaStream_t s, const void* buf, int count, const int64_t* tiles, int64_t* rows);
 // The tiles in `chunks` launches; after each, a copy kernel on `side` pushes the rows that ended in
@@ -187,7 +206,7 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
                                  const int64_t* chunk_tiles, const int64_t* chunk_rows, int64_t m, int64_t nnz,
                                  int base, const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
                                  ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                                 const PeerList<T>& peers);
+                                 const PeerList<T>& peers, const WaitCfg& wait = WaitCfg());
 template <typename T>
 cudaError_t spmv_rowgroup(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                           const int32_t* col, const T* val, const T* x, T* y, ScalarArg<T> alpha,
@@ -198,22 +217,33 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes);
 
 // Column-panel plan of an SpMM whose B does not fit in L2 (num_panels == 1: no panels). The work
 // buffer then holds int32 panel_ptr[(num_panels + 1) * m]: where each panel starts inside each row.
+// With panels the work buffer holds (256-byte aligned pieces, in this order)
+//   int32 panel_ptr[(num_panels + 1) * m]   where each panel starts inside each row of A
+//   int32 piece_pos[num_panels * m + 1]     panel-major prefix sums of the piece lengths: the piece of row r in
+//                                           panel p occupies [piece_pos[p * m + r], piece_pos[p * m + r + 1]) below
+//   int32 ccol[nnz], value cval[nnz]        A's column indices (0-based) and values regrouped panel by panel, so
+//                                           that one pass streams a contiguous range instead of a piece per row
+//   uint32 scan scratch
 struct SpmmPlan {
     int num_panels = 1;
-    int panel_cols = 0;
+    int panel_cols = 0;  // rows of B (columns of A) per panel
+    int lanes = 0;       // lanes per row of the panel kernel: the slab is lanes x 16 bytes wide
+    size_t off_pos = 0, off_ccol = 0, off_cval = 0, off_scan = 0;
     size_t bytes = 128;
 };
+long long scan_scratch_elems(long long count);
+cudaError_t exclusive_scan_u32(cudaStream_t s, unsigned* data, long long count, unsigned* sums);
 SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_size, bool row_major_operands);
 template <typename I>
-cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const I* row_ptr, const I* col, const SpmmPlan& plan,
-                            void* buf);
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col,
+                            const SpmmPlan& plan, void* buf);
 
 // Dense operand addressed as element(r, c) = ptr[r * row_stride + c * col_stride].
 template <typename T, typename I>
 cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val,
                  const T* B, int64_t b_row_stride, int64_t b_col_stride, T* C, int64_t c_row_stride,
-                 int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels = 1,
-                 const int* panel_ptr = nullptr);
+                 int64_t c_col_stride, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmmPlan* plan = nullptr,
+                 void* plan_buffer = nullptr);
 
 // y = alpha * A * x + beta * y with a real CSR matrix and complex x, y, alpha, beta; scratch: m complex numbers.
 template <typename F>

@@ -8,6 +8,7 @@
 // used in place. No temporary memory, no stream synchronisation.
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "internal.h"
 
@@ -141,22 +142,23 @@ __global__ void __launch_bounds__(kThreads)
     }
     V acc = zero_vec<V>();
     const T* const Bc = B + c0 - (long long)base * ldb;
-    // Groups of one warp may have different trip counts; width-G shuffles only need the
-    // lanes of the same group to be converged, which the group-uniform bounds guarantee.
-    for (int j = j0; j < j1; j += G) {
+    // The groups of a warp own different rows, with different lengths. Both loops run to the
+    // largest count among them with the work predicated per group: sub-warp branches would make the
+    // hardware run the groups one after the other.
+    for (int j = j0; __any_sync(0xffffffffu, j < j1); j += G) {
         int cj = 0;
         T vj = T(0);
         if (j + lane < j1) {
             cj = (int)__ldcs(col + j + lane);
             vj = ldcs(val + j + lane);
         }
-        const int cnt = min(G, j1 - j);
-        const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << ((threadIdx.x & 31) & ~(G - 1)));
-#pragma unroll 8
-        for (int q = 0; q < cnt; ++q) {
-            const int cq = __shfl_sync(gmask, cj, q, G);
-            const T vq = shfl_idx(gmask, vj, q, G);
-            if (col_ok) {
+        const int cnt = max(0, min(G, j1 - j));
+        const int maxcnt = __reduce_max_sync(0xffffffffu, cnt);
+#pragma unroll 4
+        for (int q = 0; q < maxcnt; ++q) {
+            const int cq = __shfl_sync(0xffffffffu, cj, q, G);
+            const T vq = shfl_idx(0xffffffffu, vj, q, G);
+            if (q < cnt && col_ok) {
                 const V b = *reinterpret_cast<const V*>(Bc + (long long)cq * ldb);
                 fma_vec(acc, vq, b);
             }
@@ -170,6 +172,104 @@ __global__ void __launch_bounds__(kThreads)
         } else if (j1 > j0) {  // later panels add to what the earlier ones left; C streams through L2
             __stcs(out, axpby(alpha, acc, T(1), __ldcs(out)));
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K3p: one pass of the column-panel SpMM: the nonzeros of A whose column lies in one panel of
+// rows of B, applied to one slab of G * W consecutive columns of B and C.
+//
+// Why panels and slabs. With uniform columns and a B larger than L2, the single-pass kernel
+// above fetches most B rows from HBM once per nonzero. A panel of B rows small enough to stay
+// in L2 is fetched from HBM once and then hit by every row of A; the price is that C is read and
+// rewritten once per extra panel. A narrower slab makes the same L2 bytes cover more rows of B,
+// so a slab needs fewer panels; the price is that A is read once per slab. The plan picks the
+// slab width and panel count with the least modelled HBM traffic.
+//
+// The pass reads A regrouped panel by panel (ccol / cval, built by the preprocess call): the pieces
+// of consecutive rows are adjacent, so the lane groups of a warp load one contiguous range, where
+// pieces left in place inside their rows cost a DRAM burst of 64 bytes or two per 40-byte piece.
+// G lanes own one row and the slab's G * W columns; a thread block loops over rows (grid-stride)
+// with a software pipeline, because a row piece is short (nnz / rows / panels) and one row at a time
+// would leave every load latency exposed: while the B rows of the current row are in flight, the
+// piece of the group's next row (two elements per lane) and the bounds of the row after that are
+// already being fetched, and C's old value (later panels add to it) is requested before the B rows.
+// The piece is broadcast lane by lane with shuffles; each nonzero costs one 128-bit load of B per
+// lane and W multiply-adds. Loop bounds are those of the longest piece among the warp's groups, with
+// the work predicated per group: sub-warp branches would make the hardware run the groups in turn.
+// B rows are loaded with default caching (they are the L2-resident operand); A, the bounds and C
+// are streamed (evict-first).
+// ---------------------------------------------------------------------------------------
+template <typename T, int G, bool FIRST>
+__global__ void __launch_bounds__(kThreads)
+    spmm_panel_kernel(int m, int n, const int* __restrict__ pos, const int* __restrict__ ccol,
+                      const T* __restrict__ cval, const T* __restrict__ B, long long ldb, T* __restrict__ C,
+                      long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg, int slab_c0) {
+    using V = typename VecOf<T>::type;
+    constexpr int W = VecOf<T>::W;
+    const int lane = threadIdx.x & (G - 1);
+    const long long ngroups = (long long)gridDim.x * (kThreads / G);
+    long long row0 = (blockIdx.x * (long long)kThreads + threadIdx.x) / G;
+    const int c0 = slab_c0 + lane * W;  // first column of this lane
+    const bool col_ok = c0 < n;
+    const T* const Bc = B + c0;
+    const T alpha = alpha_arg.get(), beta = beta_arg.get();
+
+    // bounds of the group's rows i, i + 1, i + 2; the first 2 G elements of the pieces of rows i, i + 1
+    int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+    long long row1 = row0 + ngroups;
+    if (row0 < m) lo0 = __ldcs(pos + row0), hi0 = __ldcs(pos + row0 + 1);
+    if (row1 < m) lo1 = __ldcs(pos + row1), hi1 = __ldcs(pos + row1 + 1);
+    int ca0 = 0, cb0 = 0;
+    T va0 = T(0), vb0 = T(0);
+    if (lo0 + lane < hi0) ca0 = __ldcs(ccol + lo0 + lane), va0 = ldcs(cval + lo0 + lane);
+    if (lo0 + G + lane < hi0) cb0 = __ldcs(ccol + lo0 + G + lane), vb0 = ldcs(cval + lo0 + G + lane);
+    while (__any_sync(0xffffffffu, row0 < m)) {
+        const bool row_ok = row0 < m;
+        const long long row2 = row1 + ngroups;
+        int lo2 = 0, hi2 = 0;
+        if (row2 < m) lo2 = __ldcs(pos + row2), hi2 = __ldcs(pos + row2 + 1);
+        int ca1 = 0, cb1 = 0;
+        T va1 = T(0), vb1 = T(0);
+        if (lo1 + lane < hi1) ca1 = __ldcs(ccol + lo1 + lane), va1 = ldcs(cval + lo1 + lane);
+        if (lo1 + G + lane < hi1) cb1 = __ldcs(ccol + lo1 + G + lane), vb1 = ldcs(cval + lo1 + G + lane);
+        V* const out = reinterpret_cast<V*>(C + row0 * ldc + c0);
+        const bool write_c = row_ok && col_ok && (FIRST || hi0 > lo0);
+        V old = zero_vec<V>();
+        if (write_c && (FIRST ? beta != T(0) : true)) old = __ldcs(out);
+
+        V acc = zero_vec<V>();
+        for (int j = lo0; __any_sync(0xffffffffu, j < hi0); j += 2 * G) {
+            if (j != lo0) {  // a piece longer than 2 G: the rest is fetched as it is needed
+                ca0 = cb0 = 0, va0 = vb0 = T(0);
+                if (j + lane < hi0) ca0 = __ldcs(ccol + j + lane), va0 = ldcs(cval + j + lane);
+                if (j + G + lane < hi0) cb0 = __ldcs(ccol + j + G + lane), vb0 = ldcs(cval + j + G + lane);
+            }
+            const int cnt = max(0, min(2 * G, hi0 - j));
+            const int maxcnt = __reduce_max_sync(0xffffffffu, cnt);
+            const int first_half = min(maxcnt, G);
+#pragma unroll 4
+            for (int q = 0; q < first_half; ++q) {
+                const int cq = __shfl_sync(0xffffffffu, ca0, q, G);
+                const T vq = shfl_idx(0xffffffffu, va0, q, G);
+                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (long long)cq * ldb));
+            }
+#pragma unroll 4
+            for (int q = G; q < maxcnt; ++q) {
+                const int cq = __shfl_sync(0xffffffffu, cb0, q - G, G);
+                const T vq = shfl_idx(0xffffffffu, vb0, q - G, G);
+                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (long long)cq * ldb));
+            }
+        }
+        if (write_c) {
+            if (FIRST)
+                __stcs(out, beta != T(0) ? axpby(alpha, acc, beta, old) : scale(alpha, acc));
+            else
+                __stcs(out, axpby(alpha, acc, T(1), old));
+        }
+        row0 = row1, row1 = row2;
+        lo0 = lo1, hi0 = hi1, lo1 = lo2, hi1 = hi2;
+        ca0 = ca1, cb0 = cb1, va0 = va1, vb0 = vb1;
     }
 }
 
@@ -203,6 +303,34 @@ __global__ void spmm_panel_ptr_kernel(int m, int base, const I* __restrict__ row
     panel_ptr[(long long)num_panels * m + r] = j1;
 }
 
+// piece_len[p * m + r] = nonzeros of row r in panel p (panel-major; one extra zero at the end so that the
+// exclusive scan leaves the total there).
+__global__ void spmm_piece_len_kernel(long long m, int num_panels, const int* __restrict__ panel_ptr,
+                                      unsigned* __restrict__ piece_len) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long count = (long long)num_panels * m;
+    if (i < count) piece_len[i] = (unsigned)(panel_ptr[i + m] - panel_ptr[i]);
+    if (i == count) piece_len[i] = 0u;
+}
+
+// Regroups one array of A (column indices made 0-based, or values) panel by panel: eight lanes copy the piece
+// of one (panel, row) from its place inside the row to piece_pos[p * m + r].
+template <typename S, typename D>
+__global__ void __launch_bounds__(256)
+    spmm_regroup_kernel(long long pieces, const int* __restrict__ panel_ptr, long long m,
+                        const int* __restrict__ piece_pos, const S* __restrict__ src, D* __restrict__ dst, int sub) {
+    const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;
+    const int lane = threadIdx.x & 7;
+    if (i >= pieces) return;
+    const int from = panel_ptr[i], len = panel_ptr[i + m] - from, to = piece_pos[i];
+    for (int e = lane; e < len; e += 8) {
+        if constexpr (std::is_integral<D>::value)
+            dst[to + e] = (D)src[from + e] - (D)sub;
+        else
+            dst[to + e] = src[from + e];
+    }
+}
+
 // Any layout, any n: one thread per C element, addressed through (row, col) strides.
 // Consecutive threads run along C's contiguous dimension.
 template <typename T, typename I>
@@ -234,77 +362,165 @@ __global__ void __launch_bounds__(kThreads)
 
 template <typename T, int G, typename I>
 cudaError_t launch_rowmajor(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val, const T* B, int64_t ldb, T* C, int64_t ldc,
-                            ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
+                            ScalarArg<T> alpha, ScalarArg<T> beta) {
     constexpr int W = VecOf<T>::W;
     const long long threads_total = m * G;
     dim3 grid((unsigned)((threads_total + kThreads - 1) / kThreads), (unsigned)((n + G * W - 1) / (G * W)));
-    if (num_panels <= 1 || panel_ptr == nullptr) {
-        spmm_rowmajor_kernel<T, G, false, I><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C,
-                                                                    ldc, alpha, beta, nullptr, nullptr, 1);
-        return cudaGetLastError();
+    spmm_rowmajor_kernel<T, G, false, I><<<grid, kThreads, 0, s>>>((int)m, (int)n, base, row_ptr, col, val, B, ldb, C,
+                                                                ldc, alpha, beta, nullptr, nullptr, 1);
+    return cudaGetLastError();
+}
+
+// All passes of the column-panel product: the values are regrouped panel by panel first (on every call: the
+// caller may have edited them in place since the preprocess call; the column indices were regrouped there),
+// then, for every slab of G * W columns, panel 0 writes C and the later panels add to it. One launch per
+// (slab, panel), in that order, so that at any time the resident thread blocks work on one panel of one slab of B.
+template <typename T, int G>
+cudaError_t launch_panels(cudaStream_t s, int64_t m, int64_t n, const T* val, const T* B, int64_t ldb, T* C,
+                          int64_t ldc, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmmPlan& plan, void* buf) {
+    constexpr int W = VecOf<T>::W;
+    static int blocks_per_sm = 0, sm_count = 0;
+    if (blocks_per_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, spmm_panel_kernel<T, G, false>, kThreads, 0);
+        if (blocks_per_sm < 1) blocks_per_sm = 1;
+        if (sm_count < 1) sm_count = 148;
     }
-    for (int p = 0; p < num_panels; ++p) {
-        spmm_rowmajor_kernel<T, G, true, I><<<grid, kThreads, 0, s>>>(
-            (int)m, (int)n, base, row_ptr, col, val, B, ldb, C, ldc, alpha, beta, panel_ptr + (size_t)p * m,
-            panel_ptr + (size_t)(p + 1) * m, p == 0);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
+    char* base_ptr = static_cast<char*>(buf);
+    const int* panel_ptr = reinterpret_cast<const int*>(base_ptr);
+    const int* pos = reinterpret_cast<const int*>(base_ptr + plan.off_pos);
+    const int* ccol = reinterpret_cast<const int*>(base_ptr + plan.off_ccol);
+    T* cval = reinterpret_cast<T*>(base_ptr + plan.off_cval);
+    const long long pieces = (long long)plan.num_panels * m;
+    spmm_regroup_kernel<T, T><<<(unsigned)((pieces * 8 + 255) / 256), 256, 0, s>>>(pieces, panel_ptr, m, pos, val, cval, 0);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const long long groups_per_block = kThreads / G;
+    const long long want = (m + groups_per_block - 1) / groups_per_block;
+    const unsigned grid = (unsigned)std::max<long long>(1, std::min<long long>(want, (long long)sm_count * blocks_per_sm));
+    for (int c0 = 0; c0 < n; c0 += G * W) {
+        for (int p = 0; p < plan.num_panels; ++p) {
+            const int* pos_p = pos + (size_t)p * m;
+            if (p == 0)
+                spmm_panel_kernel<T, G, true><<<grid, kThreads, 0, s>>>((int)m, (int)n, pos_p, ccol, cval, B, ldb, C, ldc,
+                                                                       alpha, beta, c0);
+            else
+                spmm_panel_kernel<T, G, false><<<grid, kThreads, 0, s>>>((int)m, (int)n, pos_p, ccol, cval, B, ldb, C, ldc,
+                                                                        alpha, beta, c0);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+        }
     }
     return cudaSuccess;
 }
 
 }  // namespace
 
-// L2 budget for one panel of B in MiB: MCSPARSE_B200_SPMM_PANEL_MB. Panels are off unless it is set:
-// on the 1M x 1M, 32 nonzeros per row benchmark they cut DRAM traffic from 6.9 GB to 3.4 GB (n = 64,
-// four panels) but each pass is latency-bound on its short row pieces and the total was slower
-// (1.74 ms against 1.46 ms), so the single-pass kernel stays the default.
+// L2 bytes one panel of B may occupy, in MiB: MCSPARSE_B200_SPMM_PANEL_MB (0 turns the panels off).
+// The default is what a B200 keeps resident beside the streams of A and C (measured: see the plan below).
 static long long spmm_panel_budget_bytes() {
     const char* e = std::getenv("MCSPARSE_B200_SPMM_PANEL_MB");
-    const long long mb = e ? std::atoll(e) : 0;
+    const long long mb = e ? std::atoll(e) : MCSPARSE_B200_SPMM_PANEL_MB_DEFAULT;
     return mb <= 0 ? 0 : mb << 20;
 }
+// Lanes per row forced for tuning runs (MCSPARSE_B200_SPMM_PANEL_LANES = 4, 8, 16 or 32); 0: modelled choice.
+static int spmm_forced_lanes() {
+    const char* e = std::getenv("MCSPARSE_B200_SPMM_PANEL_LANES");
+    return e ? std::atoi(e) : 0;
+}
 
+// Slab width and panel count with the least modelled HBM traffic:
+//   single pass      A + C + B * (1 + (nnz / k - 1) * miss),  miss = 1 - budget / |B|  (uniform columns: a B row is
+//                    needed nnz / k times and found in L2 with the probability that L2 holds it)
+//   slabs x panels   B + slabs * A + slabs * (2 * panels - 1) * |C slab|
+// where a slab is G lanes x 16 bytes wide, a panel holds budget / max(128, 16 G) rows of B (L2 keeps
+// whole 128-byte lines) and C's slab is written by the first panel and read and rewritten by the others.
 SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_size, bool row_major_operands) {
     SpmmPlan plan;
     const long long budget = spmm_panel_budget_bytes();
-    const long long b_bytes = (long long)k * n * (long long)value_size;
-    if (!row_major_operands || budget == 0 || m == 0 || n == 0 || b_bytes <= 2 * budget) return plan;
-    const long long panel_cols = std::max<long long>(1, budget / (n * (long long)value_size));
-    const long long panels = (k + panel_cols - 1) / panel_cols;
-    // Each extra panel re-reads and re-writes C once; worth it only while a row still brings a few
-    // nonzeros to every panel (the re-reads of B it saves are proportional to nnz).
-    if (panels < 2 || panels > 16 || nnz < 4 * (panels - 1) * m) return plan;
-    plan.num_panels = (int)panels;
-    plan.panel_cols = (int)panel_cols;
-    plan.bytes = 256 + size_t(panels + 1) * size_t(m) * 4;
+    const double b_bytes = (double)k * n * value_size;
+    if (!row_major_operands || budget == 0 || m == 0 || n == 0 || k == 0 || b_bytes <= 1.25 * budget) return plan;
+    const double a_bytes = (double)nnz * (value_size + 4), c_bytes = (double)m * n * value_size;
+    const double reuse = std::max(1.0, (double)nnz / (double)k);
+    const double miss = 1.0 - (double)budget / b_bytes;
+    const double single = a_bytes + c_bytes + b_bytes * (1.0 + (reuse - 1.0) * miss);
+    const int w = 16 / (int)value_size;
+    double best = single / 1.25;  // panels must save a quarter of the traffic to be worth their extra launches
+    const int forced = spmm_forced_lanes();
+    for (int g = 4; g <= 32; g *= 2) {
+        if (forced != 0 && g != forced) continue;
+        const long long slab_cols = (long long)g * w;
+        if (slab_cols > n && g > 4) continue;
+        const long long slabs = (n + slab_cols - 1) / slab_cols;
+        const long long panel_rows = std::max<long long>(1, budget / std::max(128, 16 * g));
+        const long long panels = (k + panel_rows - 1) / panel_rows;
+        if (panels > 32) continue;
+        const double traffic = b_bytes + slabs * a_bytes + slabs * (2.0 * panels - 1.0) * (double)m * 16.0 * g;
+        if (traffic < best || forced != 0) {
+            best = traffic;
+            plan.num_panels = (int)panels;
+            plan.panel_cols = (int)panel_rows;
+            plan.lanes = g;
+        }
+    }
+    if (plan.num_panels > 1) {
+        auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+        const size_t pieces = size_t(plan.num_panels) * size_t(m);
+        plan.off_pos = up(size_t(plan.num_panels + 1) * size_t(m) * 4);
+        plan.off_ccol = plan.off_pos + up((pieces + 1) * 4);
+        plan.off_cval = plan.off_ccol + up(size_t(nnz) * 4);
+        plan.off_scan = plan.off_cval + up(size_t(nnz) * value_size);
+        plan.bytes = 256 + plan.off_scan + up(size_t(scan_scratch_elems((long long)pieces + 1)) * 4);
+    }
     return plan;
 }
 
 template <typename I>
-cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int base, const I* row_ptr, const I* col, const SpmmPlan& plan,
-                            void* buf) {
+cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col,
+                            const SpmmPlan& plan, void* buf) {
     if (plan.num_panels <= 1) return cudaSuccess;
+    (void)nnz;
+    char* base_ptr = static_cast<char*>(buf);
+    int* panel_ptr = reinterpret_cast<int*>(base_ptr);
+    unsigned* pos = reinterpret_cast<unsigned*>(base_ptr + plan.off_pos);
+    int* ccol = reinterpret_cast<int*>(base_ptr + plan.off_ccol);
+    unsigned* scratch = reinterpret_cast<unsigned*>(base_ptr + plan.off_scan);
     spmm_panel_ptr_kernel<I><<<(unsigned)((m + 127) / 128), 128, 0, s>>>((int)m, base, row_ptr, col, plan.num_panels,
-                                                                    plan.panel_cols, static_cast<int*>(buf));
+                                                                    plan.panel_cols, panel_ptr);
+    const long long pieces = (long long)plan.num_panels * m;
+    spmm_piece_len_kernel<<<(unsigned)((pieces + 1 + 255) / 256), 256, 0, s>>>(m, plan.num_panels, panel_ptr, pos);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = exclusive_scan_u32(s, pos, pieces + 1, scratch);
+    if (e != cudaSuccess) return e;
+    spmm_regroup_kernel<I, int><<<(unsigned)((pieces * 8 + 255) / 256), 256, 0, s>>>(
+        pieces, panel_ptr, m, reinterpret_cast<const int*>(pos), col, ccol, base);
     return cudaGetLastError();
 }
 
 template <typename T, typename I>
 cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_ptr, const I* col, const T* val, const T* B, int64_t b_rs, int64_t b_cs, T* C, int64_t c_rs, int64_t c_cs,
-                 ScalarArg<T> alpha, ScalarArg<T> beta, int num_panels, const int* panel_ptr) {
+                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmmPlan* plan, void* plan_buffer) {
     if (m == 0 || n == 0) return cudaSuccess;
     constexpr int W = VecOf<T>::W;
     const bool vec_ok = b_cs == 1 && c_cs == 1 && n % W == 0 && b_rs % W == 0 && c_rs % W == 0 &&
                         ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
+    if (vec_ok && plan != nullptr && plan->num_panels > 1 && plan_buffer != nullptr) {
+        switch (plan->lanes) {
+            case 4: return launch_panels<T, 4>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);
+            case 8: return launch_panels<T, 8>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);
+            case 16: return launch_panels<T, 16>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);
+            default: return launch_panels<T, 32>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);
+        }
+    }
     if (vec_ok) {
         const int64_t lanes = n / W;
-        if (lanes <= 2) return launch_rowmajor<T, 2, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        if (lanes <= 4) return launch_rowmajor<T, 4, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        if (lanes <= 8) return launch_rowmajor<T, 8, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        if (lanes <= 16)
-            return launch_rowmajor<T, 16, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
-        return launch_rowmajor<T, 32, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta, num_panels, panel_ptr);
+        if (lanes <= 2) return launch_rowmajor<T, 2, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 4) return launch_rowmajor<T, 4, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 8) return launch_rowmajor<T, 8, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        if (lanes <= 16) return launch_rowmajor<T, 16, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
+        return launch_rowmajor<T, 32, I>(s, m, n, base, row_ptr, col, val, B, b_rs, C, c_rs, alpha, beta);
     }
     const long long total = m * n;
     spmm_strided_kernel<T, I><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, s>>>(
@@ -336,7 +552,7 @@ cudaError_t spmv_real_matrix_complex_vectors(cudaStream_t s, int64_t m, int base
     if (m == 0) return cudaSuccess;
     const ScalarArg<F> one{F(1), nullptr}, zero{F(0), nullptr};
     cudaError_t e = spmm<F, int32_t>(s, m, 2, base, row_ptr, col, val, reinterpret_cast<const F*>(x), 2, 1,
-                                     reinterpret_cast<F*>(scratch), 2, 1, one, zero, 1, nullptr);
+                                     reinterpret_cast<F*>(scratch), 2, 1, one, zero, nullptr, nullptr);
     if (e != cudaSuccess) return e;
     complex_axpby_kernel<Complex<F>><<<(unsigned)((m + 255) / 256), 256, 0, s>>>(m, alpha, scratch, beta, y);
     return cudaGetLastError();
@@ -350,8 +566,8 @@ template cudaError_t spmv_real_matrix_complex_vectors<double>(cudaStream_t, int6
 
 #define INSTANTIATE(T, I)                                                                                     \
     template cudaError_t spmm<T, I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*, const T*, const T*, \
-                                    int64_t, int64_t, T*, int64_t, int64_t, ScalarArg<T>, ScalarArg<T>, int,   \
-                                    const int*);
+                                    int64_t, int64_t, T*, int64_t, int64_t, ScalarArg<T>, ScalarArg<T>,        \
+                                    const SpmmPlan*, void*);
 INSTANTIATE(float, int32_t)
 INSTANTIATE(double, int32_t)
 INSTANTIATE(float, int64_t)
@@ -361,9 +577,9 @@ INSTANTIATE(cdouble, int32_t)
 INSTANTIATE(cfloat, int64_t)
 INSTANTIATE(cdouble, int64_t)
 #undef INSTANTIATE
-template cudaError_t spmm_preprocess<int32_t>(cudaStream_t, int64_t, int, const int32_t*, const int32_t*,
+template cudaError_t spmm_preprocess<int32_t>(cudaStream_t, int64_t, int64_t, int, const int32_t*, const int32_t*,
                                               const SpmmPlan&, void*);
-template cudaError_t spmm_preprocess<int64_t>(cudaStream_t, int64_t, int, const int64_t*, const int64_t*,
+template cudaError_t spmm_preprocess<int64_t>(cudaStream_t, int64_t, int64_t, int, const int64_t*, const int64_t*,
                                               const SpmmPlan&, void*);
 
 }  // namespace mcsp_b200

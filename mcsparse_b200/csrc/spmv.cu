@@ -119,12 +119,12 @@ __device__ __forceinline__ unsigned long long l2_evict_first_policy() {
     return policy;
 }
 
-// Waits for phase `parity` of the barrier for at most about a second of SM clocks. Returns
-// false on timeout, which the kernel reports in the status word instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
+// Waits for phase `parity` of the barrier for at most `limit` SM clocks. Returns false on timeout,
+// which the kernel reports in the status words instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity, long long limit) {
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 2000000000LL) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return true;
 }
@@ -216,6 +216,107 @@ __device__ __forceinline__ void push_tile_rows(const PeerList<T>& peers, const T
 }
 
 // ---------------------------------------------------------------------------------------
+// Staging of one tile's slice of col / val in shared memory, shared by the tile kernels.
+//
+// issue   one thread starts two bulk asynchronous copies (TMA) of the 16-byte aligned part of the
+//         slice that lies inside the arrays; they complete on the mbarrier. The few elements such
+//         a boundary would push outside the arrays (at most 3 at either end of an array, or all
+//         of a tile of at most 6 elements) are fetched with ordinary loads by warp 0.
+// finish  thread 0 waits for the barrier, for at most wait.limit_cycles SM clocks. If the limit
+//         runs out the tile is not computed: the status word of the work buffer and the handle's
+//         host-visible fault word are set and the function returns false to every thread. Copies
+//         that were issued may still land in this block's shared memory, so the block stays
+//         resident for a second, far longer limit before it gives the tile up; with the diagnostics
+//         switch wait.withhold no copy was issued and it leaves at once. A copy that completes
+//         during the second wait is used normally and only leaves a warning (status 2).
+// ---------------------------------------------------------------------------------------
+template <typename T, typename I>
+struct TileSlice {
+    int head_c, head_v;  // element nz_s + k of col / val is staged at s_col[head_c + k] / s_val[head_v + k]
+    int span_c;          // staged extent of s_col in elements (the row ends live behind it)
+    bool copies;         // a bulk copy was asked for
+};
+
+template <typename T, typename I>
+__device__ __forceinline__ TileSlice<T, I> stage_issue(int tid, int nnz, int nz_s, int nz_e, const I* __restrict__ col,
+                                                       const T* __restrict__ val, T* s_val, I* s_col,
+                                                       unsigned long long* s_mbar, const WaitCfg& wait) {
+    constexpr int GV = 16 / (int)sizeof(T);  // values per 16 bytes
+    constexpr int GC = 16 / (int)sizeof(I);  // column indices per 16 bytes
+    const int nnz_tile = nz_e - nz_s;
+    TileSlice<T, I> ts;
+    // head_c is chosen so that the element at index 0 of s_col sits on a 16-byte boundary in global
+    // memory. Likewise for val.
+    ts.head_c = (int)((reinterpret_cast<uintptr_t>(col) / sizeof(I)) + (unsigned)nz_s) & (GC - 1);
+    ts.head_v = (int)((reinterpret_cast<uintptr_t>(val) / sizeof(T)) + (unsigned)nz_s) & (GV - 1);
+    ts.span_c = (ts.head_c + nnz_tile + GC - 1) & ~(GC - 1);
+    int lo_c = nz_s - ts.head_c, hi_c = lo_c + ts.span_c;  // global element range of the col copy
+    if (lo_c < 0) lo_c += GC;
+    if (hi_c > nnz) hi_c -= GC;
+    int lo_v = nz_s - ts.head_v, hi_v = lo_v + ((ts.head_v + nnz_tile + GV - 1) & ~(GV - 1));
+    if (lo_v < 0) lo_v += GV;
+    if (hi_v > nnz) hi_v -= GV;
+    const bool copy_c = hi_c > lo_c, copy_v = hi_v > lo_v;
+    ts.copies = copy_c || copy_v;
+    if (tid == 0) mbar_init(s_mbar, 1);
+    __syncthreads();
+    if (tid == 0 && ts.copies) {
+        const unsigned long long policy = l2_evict_first_policy();
+        const uint32_t bytes_c = copy_c ? (uint32_t)(hi_c - lo_c) * (uint32_t)sizeof(I) : 0u;
+        const uint32_t bytes_v = copy_v ? (uint32_t)(hi_v - lo_v) * (uint32_t)sizeof(T) : 0u;
+        mbar_expect_tx(s_mbar, bytes_c + bytes_v);
+        if (!wait.withhold) {
+            if (copy_c) bulk_copy_g2s(s_col + (lo_c - (nz_s - ts.head_c)), col + lo_c, bytes_c, s_mbar, policy);
+            if (copy_v) bulk_copy_g2s(s_val + (lo_v - (nz_s - ts.head_v)), val + lo_v, bytes_v, s_mbar, policy);
+        }
+    }
+    // Lanes 0-15 of warp 0 handle col, lanes 16-31 val; sub-lanes 0-7 the front part, 8-15 the back.
+    if (tid < 32) {
+        const bool is_val = tid >= 16;
+        const int u = tid & 15;
+        const bool cp = is_val ? copy_v : copy_c;
+        const int lo = is_val ? lo_v : lo_c, hi = is_val ? hi_v : hi_c;
+        const int front = cp ? max(0, min(lo, nz_e) - nz_s) : nnz_tile;
+        const int back0 = cp ? max(hi, nz_s) : nz_e;
+        const int g = u < 8 ? nz_s + u : back0 + (u - 8);
+        const bool mine = u < 8 ? (u < front) : (g < nz_e);
+        if (mine) {
+            if (is_val)
+                s_val[ts.head_v + (g - nz_s)] = ldcs(val + g);
+            else
+                s_col[ts.head_c + (g - nz_s)] = __ldcs(col + g);
+        }
+    }
+    return ts;
+}
+
+// One thread polls the barrier (a whole CTA polling would crowd the shared-memory pipe that the
+// other resident CTAs need); the block barrier then publishes the copied data to everyone.
+__device__ __forceinline__ bool stage_finish(int tid, bool copies, unsigned long long* s_mbar, int* s_failed,
+                                             int* __restrict__ status, const WaitCfg& wait) {
+    if (tid == 0) {
+        int failed = 0;
+        if (copies && !mbar_wait_bounded(s_mbar, 0, wait.limit_cycles)) {  // never expected; reported, not spun on
+            failed = 1;
+            if (!wait.withhold && mbar_wait_bounded(s_mbar, 0, wait.limit_cycles * 256)) {
+                failed = 0;  // the copies did arrive: the tile is computed, the delay is only noted
+                atomicOr(status, 2);
+            }
+            if (failed) {
+                atomicOr(status, 1);
+                if (wait.fault_word != nullptr) {
+                    *reinterpret_cast<volatile int*>(wait.fault_word) = 1;
+                    __threadfence_system();
+                }
+            }
+        }
+        *s_failed = failed;
+    }
+    __syncthreads();
+    return *s_failed == 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
 //
@@ -246,13 +347,12 @@ __global__ void __launch_bounds__(THREADS)
     spmv_tile_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
-                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset) {
+                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset,
+                     WaitCfg wait) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
     constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
                                    // stride-WALK shared reads of a warp fall in distinct banks
-    constexpr int GV = 16 / (int)sizeof(T);  // values per 16 bytes
-    constexpr int GC = 16 / (int)sizeof(I);  // column indices per 16 bytes
 
     __shared__ __align__(128) T s_val[TILE + 16];   // values (then products); long-row path: row sums behind them
     __shared__ __align__(128) I s_col[TILE + 16];  // column indices, then the tile's row ends (int) behind them
@@ -274,52 +374,11 @@ __global__ void __launch_bounds__(THREADS)
     const int nnz_tile = nz_e - nz_s;
     const int tile_items = nrows + nnz_tile;
 
-    // Element nz_s + k of col is staged at s_col[head_c + k]; head_c is chosen so that the element
-    // at index 0 of s_col sits on a 16-byte boundary in global memory. Likewise for val.
-    const int head_c = (int)((reinterpret_cast<uintptr_t>(col) / sizeof(I)) + (unsigned)nz_s) & (GC - 1);
-    const int head_v = (int)((reinterpret_cast<uintptr_t>(val) / sizeof(T)) + (unsigned)nz_s) & (GV - 1);
-    const I* const colv = s_col + head_c;  // colv[k], valv[k]: k-th nonzero of the tile
-    T* const valv = s_val + head_v;
-    const int span_c = (head_c + nnz_tile + GC - 1) & ~(GC - 1);  // staged extent of s_col, in elements
-    int* const s_row_end = reinterpret_cast<int*>(s_col + span_c);  // nrows + 1 ints; nrows + nnz_tile <= TILE
-
-    // ---- phase 1: bulk copies of the 16-byte aligned part that lies inside the arrays
-    int lo_c = nz_s - head_c, hi_c = lo_c + span_c;  // global element range of the col copy
-    if (lo_c < 0) lo_c += GC;
-    if (hi_c > nnz) hi_c -= GC;
-    int lo_v = nz_s - head_v, hi_v = lo_v + ((head_v + nnz_tile + GV - 1) & ~(GV - 1));
-    if (lo_v < 0) lo_v += GV;
-    if (hi_v > nnz) hi_v -= GV;
-    const bool copy_c = hi_c > lo_c, copy_v = hi_v > lo_v;
-    if (tid == 0) mbar_init(&s_mbar, 1);
-    __syncthreads();
-    if (tid == 0 && (copy_c || copy_v)) {
-        const unsigned long long policy = l2_evict_first_policy();
-        const uint32_t bytes_c = copy_c ? (uint32_t)(hi_c - lo_c) * (uint32_t)sizeof(I) : 0u;
-        const uint32_t bytes_v = copy_v ? (uint32_t)(hi_v - lo_v) * (uint32_t)sizeof(T) : 0u;
-        mbar_expect_tx(&s_mbar, bytes_c + bytes_v);
-        if (copy_c) bulk_copy_g2s(s_col + (lo_c - (nz_s - head_c)), col + lo_c, bytes_c, &s_mbar, policy);
-        if (copy_v) bulk_copy_g2s(s_val + (lo_v - (nz_s - head_v)), val + lo_v, bytes_v, &s_mbar, policy);
-    }
-    // Elements of the tile that the aligned copies leave out: at most 3 at either end of an array
-    // (all of the tile, at most 6 elements, when no aligned group lies inside the array).
-    // Lanes 0-15 of warp 0 handle col, lanes 16-31 val; sub-lanes 0-7 the front part, 8-15 the back.
-    if (tid < 32) {
-        const bool is_val = tid >= 16;
-        const int u = tid & 15;
-        const bool cp = is_val ? copy_v : copy_c;
-        const int lo = is_val ? lo_v : lo_c, hi = is_val ? hi_v : hi_c;
-        const int front = cp ? max(0, min(lo, nz_e) - nz_s) : nnz_tile;
-        const int back0 = cp ? max(hi, nz_s) : nz_e;
-        const int g = u < 8 ? nz_s + u : back0 + (u - 8);
-        const bool mine = u < 8 ? (u < front) : (g < nz_e);
-        if (mine) {
-            if (is_val)
-                s_val[head_v + (g - nz_s)] = ldcs(val + g);
-            else
-                s_col[head_c + (g - nz_s)] = __ldcs(col + g);
-        }
-    }
+    // ---- phase 1: bulk copies of the tile's slice of col / val, edge elements by ordinary loads
+    const TileSlice<T, I> ts = stage_issue<T, I>(tid, nnz, nz_s, nz_e, col, val, s_val, s_col, &s_mbar, wait);
+    const I* const colv = s_col + ts.head_c;  // colv[k], valv[k]: k-th nonzero of the tile
+    T* const valv = s_val + ts.head_v;
+    int* const s_row_end = reinterpret_cast<int*>(s_col + ts.span_c);  // nrows + 1 ints; nrows + nnz_tile <= TILE
 
     // Row ends in tile-local nonzero coordinates; entry nrows is the row left open.
     // Alongside: the longest piece of a row inside this tile, which selects the phase-2 path.
@@ -334,19 +393,10 @@ __global__ void __launch_bounds__(THREADS)
     }
     maxlen = __reduce_max_sync(0xffffffffu, maxlen);
     if ((tid & 31) == 0) s_warp_maxlen[tid >> 5] = maxlen;
-    // One thread polls the barrier (a whole CTA polling would crowd the shared-memory pipe that the
-    // other resident CTAs need); the block barrier then publishes the copied data to everyone.
-    if (tid == 0) {
-        int failed = 0;
-        if ((copy_c || copy_v) && !mbar_wait_bounded(&s_mbar, 0)) {  // never expected; reported, not spun on
-            atomicExch(status, 1);
-            mbar_wait_bounded(&s_mbar, 0);  // second bounded wait for the copies before giving the tile up
-            failed = 1;
-        }
-        s_failed = failed;
+    if (!stage_finish(tid, ts.copies, &s_mbar, &s_failed, status, wait)) {
+        if (tid == 0) carry_row[t] = m;  // a tile that was given up leaves no carry for the fix-up
+        return;
     }
-    __syncthreads();
-    if (s_failed) return;
 
     // ---- phase 2
     maxlen = 0;
@@ -502,6 +552,171 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// K1w: tiled SpMV for matrices with scattered columns (every x gather is its own 32-byte sector).
+//
+// On such matrices the limit is not HBM but the one request per clock that an SM can send to L2:
+// a random gather is one request, so the kernel is built to keep that port busy and to spend as
+// little else of the L1 data pipe as it can. Same tiles, staging and carries as K1, but one path
+// for every tile and no products written back to shared memory:
+//   - each thread owns WALK consecutive merge items of the tile (found by a merge-path search over
+//     the staged row ends; WALK is odd, so the stride-WALK shared reads of a warp hit distinct banks);
+//   - it reads its nonzeros' columns, issues all its x gathers at once, multiplies by the staged
+//     values in registers, and then walks its items: a product adds to the running sum, a row end
+//     stores the sum of the row piece seen by this thread;
+//   - the piece of a row that was still open at the end of a thread is carried to the thread where
+//     the row ends by a warp-shuffle segmented scan and, across the warps, in a fixed order.
+// Per nonzero that is two conflict-free shared loads, one gather and one multiply-add; empty rows,
+// rows of one nonzero and rows of a hundred thousand go through the same code.
+// ---------------------------------------------------------------------------------------
+template <typename T, int THREADS, int IPT, bool PUSH, typename I>
+__global__ void __launch_bounds__(THREADS)
+    spmv_walk_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
+                     const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
+                     ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
+                     T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset,
+                     WaitCfg wait) {
+    constexpr int TILE = THREADS * IPT;
+    constexpr int NWARPS = THREADS / 32;
+    constexpr int WALK = IPT + 1;
+    static_assert(WALK % 2 == 1, "the walk stride must be odd");
+
+    __shared__ __align__(128) T s_val[TILE + 16];  // values; the row sums behind them
+    __shared__ __align__(128) I s_col[TILE + 16];  // column indices, then the tile's row ends (int) behind them
+    __shared__ __align__(8) unsigned long long s_mbar;
+    __shared__ int s_k0[THREADS];  // first nonzero of every thread's segment
+    __shared__ int s_warp_row[NWARPS];
+    __shared__ T s_warp_sum[NWARPS];
+    __shared__ int s_failed;
+
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x + tile_offset;
+    const int2 s0 = tile_starts[t];
+    const int2 s1 = tile_starts[t + 1];
+    const int row_s = s0.x, nz_s = s0.y;
+    const int nrows = s1.x - s0.x;
+    const int nz_e = s1.y;
+    const int nnz_tile = nz_e - nz_s;
+    const int tile_items = nrows + nnz_tile;
+
+    const TileSlice<T, I> ts = stage_issue<T, I>(tid, nnz, nz_s, nz_e, col, val, s_val, s_col, &s_mbar, wait);
+    const I* const colv = s_col + ts.head_c;
+    const T* const valv = s_val + ts.head_v;
+    int* const s_row_end = reinterpret_cast<int*>(s_col + ts.span_c);  // nrows + 1 ints; nrows + nnz_tile <= TILE
+    T* const s_y = s_val + ts.head_v + nnz_tile;                        // s_y[i]: row row_s + i, i in [0, nrows]
+
+    // Row ends in tile-local nonzero coordinates; entry nrows belongs to the row left open.
+    for (int i = tid; i <= nrows; i += THREADS) {
+        const int r = row_s + i;
+        const int e = (r < m) ? (int)__ldg(row_ptr + r + 1) - base : nz_e;
+        s_row_end[i] = min(e, nz_e) - nz_s;
+    }
+    if (!stage_finish(tid, ts.copies, &s_mbar, &s_failed, status, wait)) {
+        if (tid == 0) carry_row[t] = m;  // a tile that was given up leaves no carry for the fix-up
+        return;
+    }
+
+    // Where this thread's segment starts: diagonal d0 of the merge of row ends and nonzeros
+    // (a row end equal to a nonzero index comes first, as in the tile partition).
+    const int d0 = min(tid * WALK, tile_items);
+    const int d1 = min(d0 + WALK, tile_items);
+    int lo = max(d0 - nnz_tile, 0), hi = min(d0, nrows);
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s_row_end[mid] <= d0 - mid - 1)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    int r = lo;              // tile-local row the segment starts in
+    const int k0 = d0 - lo;  // tile-local nonzero it starts at
+    s_k0[tid] = k0;
+    if (tid == 0) s_y[nrows] = T(0);  // the open row only ever receives carries
+    __syncthreads();
+    const int k1 = (tid + 1 < THREADS) ? s_k0[tid + 1] : nnz_tile;
+    const int cnt = k1 - k0;      // nonzeros of this thread, 0 ... WALK
+    const int r1 = d1 - k1;       // row its segment ends in (that row stays open)
+
+    // All gathers of the thread are in flight before the first product is formed.
+    const T* const xb = x - base;
+    T p[WALK];
+#pragma unroll
+    for (int j = 0; j < WALK; ++j) {
+        p[j] = T(0);
+        if (j < cnt) p[j] = ldg(xb + colv[k0 + j]);
+    }
+#pragma unroll
+    for (int j = 0; j < WALK; ++j)
+        if (j < cnt) p[j] = valv[k0 + j] * p[j];
+
+    int end = s_row_end[r];
+    T sum = T(0);
+#pragma unroll
+    for (int j = 0; j < WALK; ++j) {
+        if (j < cnt) {
+            while (k0 + j >= end) {  // rows that end before this nonzero (empty rows included)
+                s_y[r] = sum;
+                sum = T(0);
+                ++r;
+                end = s_row_end[r];
+            }
+            sum += p[j];
+        }
+    }
+    while (r < r1) {  // row ends behind the thread's last nonzero
+        s_y[r] = sum;
+        sum = T(0);
+        ++r;
+    }
+
+    // Segmented reduction of the per-thread carries (key = r, value = sum): the carry of a thread
+    // belongs to the row that is open at its end.
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const T up = shfl_up(sum, d);
+        const int ru = __shfl_up_sync(0xffffffffu, r, d);
+        if (lane >= d && ru == r) sum += up;
+    }
+    const int rn = __shfl_down_sync(0xffffffffu, r, 1);
+    __syncthreads();  // all direct row sums are in s_y
+    if (lane == 31) {
+        s_warp_row[warp] = r;
+        s_warp_sum[warp] = sum;
+    } else if (rn != r) {
+        s_y[r] += sum;  // the run of threads holding row r ends inside this warp: single writer
+    }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) s_y[s_warp_row[w]] += s_warp_sum[w];
+    }
+    __syncthreads();
+
+    const T alpha = alpha_arg.get();
+    const T beta = beta_arg.get();
+    for (int i = tid; i < nrows; i += THREADS) {
+        T v = alpha * s_y[i];
+        if (beta != T(0)) v = mad(beta, y[row_s + i], v);
+        y[row_s + i] = v;
+        if constexpr (PUSH) s_y[i] = v;  // only this thread touches s_y[i] here
+    }
+    if constexpr (PUSH) {
+        const T open_sum = s_y[nrows];
+        __syncthreads();
+        push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        if (tid == 0) {
+            carry_row[t] = row_s + nrows;
+            carry_val[t] = open_sum;
+        }
+        return;
+    }
+    if (tid == 0) {
+        carry_row[t] = row_s + nrows;
+        carry_val[t] = s_y[nrows];
+    }
+}
+
 // Copies local rows [r0, r1) of y to the same global rows of every peer's y with 128-bit stores
 // aligned on the destination (NVLink carries large aligned writes near its peak; scattered 8-byte
 // stores reach about half of it). Runs on a side stream while later tiles are still computing.
@@ -548,7 +763,7 @@ __global__ void spmv_carry_fixup_kernel(int m, long long num_tiles, const int* _
     long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (t >= num_tiles) return;
     const int r = carry_row[t];
-    if (r >= m) return;
+    if (r < 0 || r >= m) return;
     if (t > 0 && carry_row[t - 1] == r) return;
     T sum = carry_val[t];
     for (long long u = t + 1; u < num_tiles && carry_row[u] == r; ++u) sum += carry_val[u];
@@ -623,10 +838,11 @@ static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int 
     return ws;
 }
 
-SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, bool small_tiles, size_t index_size) {
+SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile_kind, size_t index_size) {
     const int small = tile_items(value_size, true);
     const int large = index_size == 8 ? small : tile_items(value_size, false);  // 64-bit indices: one tile size
-    SpmvWorkspace ws = spmv_layout(m, nnz, value_size, small_tiles ? small : large);
+    SpmvWorkspace ws = spmv_layout(m, nnz, value_size, (tile_kind & kTileSmall) ? small : large);
+    ws.walk = (tile_kind & kTileWalk) != 0;
     ws.bytes = spmv_layout(m, nnz, value_size, small).bytes;
     return ws;
 }
@@ -667,27 +883,39 @@ template <typename T, bool PUSH, typename I>
 static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, int64_t m, int64_t nnz, int base,
                                 const I* row_ptr, const I* col, const T* val, const T* x, T* y,
                                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                                const PeerList<T>& peers) {
+                                const PeerList<T>& peers, const WaitCfg& wait) {
     char* base_ptr = static_cast<char*>(buf);
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
-    if (ws.items_per_tile == kThreads * TileCfg<T, I>::kLarge)
-        spmv_tile_kernel<T, kThreads, TileCfg<T, I>::kLarge, PUSH, I><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
-            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
-            (int)tile0);
-    else
-        spmv_tile_kernel<T, kThreads, TileCfg<T, I>::kSmall, PUSH, I><<<(unsigned)count, kThreads, tuning_pad_smem(), s>>>(
-            (int)m, (int)nnz, base, row_ptr, col, val, x, y, alpha, beta, starts, carry_row, carry_val, status, peers,
-            (int)tile0);
+    constexpr int kL = TileCfg<T, I>::kLarge, kS = TileCfg<T, I>::kSmall;
+    const bool large = ws.items_per_tile == kThreads * kL;
+    const unsigned grid = (unsigned)count;
+    const size_t pad = tuning_pad_smem();
+#define MCSP_LAUNCH_TILES(KERNEL, IPT)                                                                              \
+    KERNEL<T, kThreads, IPT, PUSH, I><<<grid, kThreads, pad, s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, \
+                                                                  alpha, beta, starts, carry_row, carry_val,       \
+                                                                  status, peers, (int)tile0, wait)
+    if (ws.walk) {
+        if (large)
+            MCSP_LAUNCH_TILES(spmv_walk_kernel, kL);
+        else
+            MCSP_LAUNCH_TILES(spmv_walk_kernel, kS);
+    } else {
+        if (large)
+            MCSP_LAUNCH_TILES(spmv_tile_kernel, kL);
+        else
+            MCSP_LAUNCH_TILES(spmv_tile_kernel, kS);
+    }
+#undef MCSP_LAUNCH_TILES
     return cudaGetLastError();
 }
 
 template <typename T, typename I>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col, const T* val,
                        const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                       const PeerList<T>& peers) {
+                       const PeerList<T>& peers, const WaitCfg& wait) {
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
@@ -696,7 +924,7 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I
     if constexpr (std::is_floating_point<T>::value) {  // the row push exists for the real types only
         if (peers.count > 0) {
             cudaError_t e = launch_tiles<T, true, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha,
-                                                     beta, ws, buf, peers);
+                                                     beta, ws, buf, peers, wait);
             if (e != cudaSuccess) return e;
             spmv_carry_fixup_kernel<T, true><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y,
                                                                       alpha, peers);
@@ -706,7 +934,7 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I
         return cudaErrorInvalidValue;
     }
     cudaError_t e = launch_tiles<T, false, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws,
-                                              buf, peers);
+                                              buf, peers, wait);
     if (e != cudaSuccess) return e;
     spmv_carry_fixup_kernel<T, false><<<fix_grid, 256, 0, s>>>((int)m, ws.num_tiles, carry_row, carry_val, y, alpha,
                                                                peers);
@@ -744,7 +972,7 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
                                  int chunks, const int64_t* chunk_tiles, const int64_t* chunk_rows, int64_t m, int64_t nnz,
                                  int base, const int32_t* row_ptr, const int32_t* col, const T* val, const T* x, T* y,
                                  ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                                 const PeerList<T>& peers) {
+                                 const PeerList<T>& peers, const WaitCfg& wait) {
     if (ws.num_tiles == 0) return cudaSuccess;
     char* base_ptr = static_cast<char*>(buf);
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
@@ -756,7 +984,7 @@ cudaError_t spmv_tiled_pipelined(cudaStream_t s, cudaStream_t side, cudaEvent_t*
         const int64_t t0 = chunk_tiles[c], t1 = chunk_tiles[c + 1];
         if (t1 > t0)
             e = launch_tiles<T, false, int32_t>(s, t0, t1 - t0, m, nnz, base, row_ptr, col, val, x, y, alpha, beta, ws, buf,
-                                                none);
+                                                none, wait);
         if (e == cudaSuccess) e = cudaEventRecord(events[c], s);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(side, events[c], 0);
         if (e == cudaSuccess && t1 > t0) {
@@ -856,7 +1084,7 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
 #define INSTANTIATE_TI(T, I)                                                                                  \
     template cudaError_t spmv_tiled<T, I>(cudaStream_t, int64_t, int64_t, int, const I*, const I*, const T*,    \
                                           const T*, T*, ScalarArg<T>, ScalarArg<T>, const SpmvWorkspace&,      \
-                                          void*, const PeerList<T>&);
+                                          void*, const PeerList<T>&, const WaitCfg&);
 #define INSTANTIATE(T)                                                                                         \
     INSTANTIATE_TI(T, int32_t)                                                                                 \
     INSTANTIATE_TI(T, int64_t)                                                                                 \
@@ -866,7 +1094,8 @@ cudaError_t spmv_static_scratch(void** ptr, size_t* bytes) {
                                                  int, const int64_t*,                                          \
                                                  const int64_t*, int64_t, int64_t, int, const int32_t*,        \
                                                  const int32_t*, const T*, const T*, T*, ScalarArg<T>,         \
-                                                 ScalarArg<T>, const SpmvWorkspace&, void*, const PeerList<T>&);
+                                                 ScalarArg<T>, const SpmvWorkspace&, void*, const PeerList<T>&, \
+                                                 const WaitCfg&);
 INSTANTIATE(float)
 INSTANTIATE(double)
 INSTANTIATE_TI(cfloat, int32_t)

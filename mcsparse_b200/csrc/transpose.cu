@@ -266,6 +266,17 @@ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 }  // namespace
 
+// In-place exclusive prefix sum of `count` unsigned values; `sums` is scratch of scan_scratch_elems(count) words.
+long long scan_scratch_elems(long long count) { return (count + kScanChunk - 1) / kScanChunk; }
+cudaError_t exclusive_scan_u32(cudaStream_t s, unsigned* data, long long count, unsigned* sums) {
+    if (count <= 0) return cudaSuccess;
+    const long long chunks = scan_scratch_elems(count);
+    scan_chunk_sums_kernel<<<(unsigned)chunks, kScanThreads, 0, s>>>(data, count, sums);
+    scan_sums_kernel<<<1, kScanThreads, 0, s>>>(sums, chunks);
+    scan_apply_kernel<<<(unsigned)chunks, kScanThreads, 0, s>>>(data, count, sums);
+    return cudaGetLastError();
+}
+
 TransposePlan transpose_plan(int64_t m, int64_t n, int64_t nnz, size_t value_size) {
     (void)m;
     TransposePlan p;

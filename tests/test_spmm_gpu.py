@@ -206,14 +206,18 @@ def test_legacy_csrmm2(handle, device, dtype, trans_b):
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("beta", [0.0, 0.5])
 @pytest.mark.parametrize("shuffle_rows", [False, True])
-def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, monkeypatch):
-    """With a small L2 budget the preprocess call splits the product into column panels; the result must
-    not change. Rows whose columns are not sorted are handled whole by the first panel."""
+@pytest.mark.parametrize("lanes", ["model", "4", "8", "16", "32"])
+def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, lanes, monkeypatch):
+    """With a small L2 budget the preprocess call splits the product into column slabs and panels; the
+    result must not change, whatever the slab width (modelled, or forced to 4 ... 32 lanes per row).
+    Rows whose columns are not sorted are handled whole by the first panel."""
     monkeypatch.setenv("MCSPARSE_B200_SPMM_PANEL_MB", "1")
+    if lanes != "model":
+        monkeypatch.setenv("MCSPARSE_B200_SPMM_PANEL_LANES", lanes)
     rng = np.random.default_rng(3)
-    m, k, n = 3000, 10000, 64
+    m, k, n = 3000, 10000, (128 if lanes == "32" else 64)  # 32 lanes of fp32 are a slab of 128 columns
     lengths = rng.integers(12, 40, size=m).tolist()
-    lengths[5], lengths[17] = 0, 1
+    lengths[5], lengths[17], lengths[40] = 0, 1, 700  # an empty row, a single nonzero, pieces longer than the lane group
     rp, col, val = csr_from_lengths(lengths, k, dtype, seed=14)
     if shuffle_rows:
         for r in range(0, m, 7):
@@ -226,8 +230,11 @@ def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, monkeypat
     A = mc.CsrMatrix(m, k, t[0], t[1], t[2])
     Bm, Cm = mc.DnMat(t[3], k, n, n), mc.DnMat(t[4], m, n, n)
     size = mc.spmm_buffer_size(handle, A, Bm, Cm)
-    panels = -(-k // ((1 << 20) // (n * np.dtype(dtype).itemsize)))
-    assert size == 256 + (panels + 1) * m * 4
+    # the buffer holds (panels + 1) offsets and panels piece positions per row, and A regrouped panel by panel
+    assert size > 2 * m * 4 + col.size * (4 + np.dtype(dtype).itemsize)
+    if lanes != "model":  # a panel holds budget / max(128, 16 * lanes) rows of B
+        panels = -(-k // ((1 << 20) // max(128, 16 * int(lanes))))
+        assert size > (2 * panels + 1) * m * 4 + col.size * (4 + np.dtype(dtype).itemsize)
     buf = torch.empty(size, dtype=torch.uint8, device=device)
     mc.spmm_preprocess(handle, A, Bm, Cm, buf)
     mc.spmm(handle, A, Bm, Cm, buf, alpha=1.25, beta=beta)

@@ -44,11 +44,13 @@ def run_spmv(handle, device, rp, col, val, x, y0, alpha, beta, base=0, preproces
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("base", [0, 1])
 @pytest.mark.parametrize("beta", [0.0, -0.75])
-@pytest.mark.parametrize("tile", ["auto", "small", "large"])
+@pytest.mark.parametrize("tile", ["auto", "small", "large", "walk-small", "walk-large"])
 @pytest.mark.parametrize("name", sorted(ADVERSARIAL_LENGTHS))
 def test_spmv_adversarial_shapes(handle, device, name, dtype, base, beta, tile, monkeypatch):
-    if tile != "auto":
-        monkeypatch.setenv("MCSPARSE_B200_SPMV_TILE", tile)  # force one of the two tile sizes
+    if tile != "auto":  # force one of the two kernel families and one of the two tile sizes
+        monkeypatch.setenv("MCSPARSE_B200_SPMV_WALK", "1" if tile.startswith("walk") else "0")
+        tile = tile.replace("walk-", "")
+        monkeypatch.setenv("MCSPARSE_B200_SPMV_TILE", tile)
     lengths = ADVERSARIAL_LENGTHS[name]
     ncols = max(max(lengths), 1) + 17
     rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=11, base=base)
@@ -365,3 +367,45 @@ def test_host_pipeline_matches_oracle(handle, device, beta):
         ref, d = oracle.spmv(rp, col, val, x.numpy(), 2.0, beta, v)
         assert_close(y.numpy(), ref, d, TOL[np.dtype(dtype)], "host pipeline")
     pipe.close()
+
+
+@pytest.mark.parametrize("walk", ["0", "1"])
+def test_bounded_wait_returns_error_status(device, walk, monkeypatch):
+    """A tile kernel whose bulk copies never complete gives up after the handle's wait limit instead of
+    spinning: with the diagnostics switch that withholds the copies (nothing is in flight), every tile
+    reports through the buffer's status word and through the next call on the handle, the kernel returns
+    cleanly, and the same handle computes correctly once the switch is off again."""
+    monkeypatch.setenv("MCSPARSE_B200_SPMV_WALK", walk)
+    h = mc.Handle()
+    try:
+        dtype = np.float64
+        lengths = [5, 0, 300, 17] * 40
+        rp, col, val = csr_from_lengths(lengths, 400, dtype, seed=21)
+        x = np.random.default_rng(8).uniform(-1, 1, 400).astype(dtype)
+        d_rp, d_col, d_val = (torch.from_numpy(a).to(device) for a in (rp, col, val))
+        d_x = torch.from_numpy(x).to(device)
+        d_y = torch.full((len(lengths),), 7.0, dtype=torch.float64, device=device)
+        A = mc.CsrMatrix(len(lengths), 400, d_rp, d_col, d_val)
+        X, Y = mc.DnVec(d_x), mc.DnVec(d_y)
+        buf = torch.empty(mc.spmv_buffer_size(h, A, X, Y), dtype=torch.uint8, device=device)
+        capi.check(lib.mcsparseB200SetDeviceWaitLimit(h.h, 100000, 1))  # 50 microseconds of SM clocks, copies withheld
+        mc.spmv(h, A, X, Y, buf)  # asynchronous: the call itself succeeds
+        torch.cuda.synchronize()  # ... and the kernel returns by itself
+        status = C.c_int(-1)
+        capi.check(lib.mcsparseB200SpMVGetStatus(h.h, A.d, C.c_void_p(buf.data_ptr()), C.byref(status)))
+        assert status.value & 1
+        assert torch.all(d_y == 7.0)  # the tiles that gave up wrote nothing
+        capi.check(lib.mcsparseB200SetDeviceWaitLimit(h.h, 40000000, 0))
+        with pytest.raises(capi.McsparseError) as err:  # reported once by the next compute call, without a sync
+            mc.spmv(h, A, X, Y, buf)
+        assert err.value.status == capi.MCSPARSE_STATUS_EXECUTION_FAILED
+        mc.spmv_preprocess(h, A, X, Y, buf)  # a new analysis clears the buffer's status word
+        mc.spmv(h, A, X, Y, buf)
+        torch.cuda.synchronize()
+        capi.check(lib.mcsparseB200SpMVGetStatus(h.h, A.d, C.c_void_p(buf.data_ptr()), C.byref(status)))
+        assert status.value == 0
+        ref, d = oracle.spmv(rp, col, val, x, 1.0, 0.0)
+        assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], "after the switch is off")
+        assert lib.mcsparseB200SetDeviceWaitLimit(h.h, 0, 0) == capi.MCSPARSE_STATUS_INVALID_VALUE
+    finally:
+        h.close()
