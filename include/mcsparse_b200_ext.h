@@ -24,7 +24,7 @@ extern "C" {
 
 /* L2 bytes (MiB) that one column panel of B may occupy in the panelled SpMM (mcsparseSpMM_preprocess);
  * the environment variable MCSPARSE_B200_SPMM_PANEL_MB overrides it, 0 turns the panels off. */
-#define MCSPARSE_B200_SPMM_PANEL_MB_DEFAULT 40
+#define MCSPARSE_B200_SPMM_PANEL_MB_DEFAULT 48
 
 /*
  * mcsparseSpMV_preprocess: same argument list as mcsparseSpMV. Runs the merge-path

@@ -109,16 +109,21 @@ int apply_tile_overrides(int kind) {
 // (one small kernel and a 4-byte copy, which synchronises the stream) and remembered on the
 // descriptor. `scratch` is device memory the probe may overwrite (the start of the work buffer,
 // before the analysis writes it).
-int probe_tile_kind(mcsparseContext* h, const void* idx, bool wide, int64_t nnz, int64_t rows, size_t vsize,
-                    void* scratch) {
-    int near = 4096;
+int probe_tile_kind(mcsparseContext* h, const void* ptr, const void* idx, bool wide, int64_t nnz, int64_t rows,
+                    size_t vsize, void* scratch) {
+    int counts[2] = {4096, 0};  // {neighbouring columns, long rows}
     if (nnz >= 2) {
-        int* count = static_cast<int*>(scratch);
-        const cudaError_t e = wide ? spmv_locality_probe(h->stream, nnz, static_cast<const int64_t*>(idx), count, &near)
-                                   : spmv_locality_probe(h->stream, nnz, static_cast<const int32_t*>(idx), count, &near);
-        if (e != cudaSuccess) near = 4096;
+        int* dev = static_cast<int*>(scratch);
+        const cudaError_t e =
+            wide ? spmv_locality_probe(h->stream, rows, nnz, static_cast<const int64_t*>(ptr), static_cast<const int64_t*>(idx), dev, counts)
+                 : spmv_locality_probe(h->stream, rows, nnz, static_cast<const int32_t*>(ptr), static_cast<const int32_t*>(idx), dev, counts);
+        if (e != cudaSuccess) counts[0] = 4096, counts[1] = 0;
     }
-    int kind = near < 1024 ? (kTileWalk | kTileSmall) : kTileLarge;
+    // Scattered columns: the half-size tile. Scattered columns and rows of very different lengths (two or more of
+    // the sampled rows beyond 256 nonzeros): the walk kernel, which does not care about row lengths; rows of
+    // similar, moderate length are faster with lanes per row.
+    int kind = counts[0] < 1024 ? kTileSmall : kTileLarge;
+    if (counts[0] < 1024 && counts[1] >= 2) kind |= kTileWalk;
     if (wide) kind |= kTileSmall;  // 64-bit indices: one tile size
     // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
     const int64_t large = spmv_workspace(rows, nnz, vsize, kTileLarge).items_per_tile;
@@ -128,11 +133,12 @@ int probe_tile_kind(mcsparseContext* h, const void* idx, bool wide, int64_t nnz,
 
 // `idx` / `rows`: the index array and the row count the kernels will run on (for a CSC input these
 // are the row indices and the column count).
-int choose_tile_kind(mcsparseContext* h, mcsparseSpMatDescr* A, const void* idx, int64_t rows, void* scratch) {
+int choose_tile_kind(mcsparseContext* h, mcsparseSpMatDescr* A, const void* ptr, const void* idx, int64_t rows,
+                     void* scratch) {
     std::lock_guard<std::mutex> g(A->lock);
     if (A->probed_cols == idx && A->probed_nnz == A->nnz) return A->tile_kind;
-    A->tile_kind = probe_tile_kind(h, idx, A->colIdxType == MCSPARSE_INDEX_64I, A->nnz, rows, value_size(A->valueType),
-                                   scratch);
+    A->tile_kind = probe_tile_kind(h, ptr, idx, A->colIdxType == MCSPARSE_INDEX_64I, A->nnz, rows,
+                                   value_size(A->valueType), scratch);
     A->probed_cols = idx;
     A->probed_nnz = A->nnz;
     return A->tile_kind;
@@ -341,7 +347,7 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
         cudaError_t e = convert_structure(h->stream, A, v, L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
         if (!probed) {  // tile size for the transposed matrix: probed once (synchronises), then remembered
-            kind = probe_tile_kind(h, t_idx, false, nnz, v.n, sizeof(T), L.work);
+            kind = probe_tile_kind(h, t_ptr, t_idx, false, nnz, v.n, sizeof(T), L.work);
             std::lock_guard<std::mutex> g(A->lock);
             A->trans_probed_idx = v.idx;
             A->trans_probed_nnz = nnz;
@@ -423,7 +429,9 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
             default: return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
         }
     }
-    const int small = choose_tile_kind(h, A, view.idx, view.m, align_up_256(buffer));
+    // (a COO matrix has row indices, not offsets, in view.ptr: its row lengths are not sampled)
+    const int small = choose_tile_kind(h, A, A->format == MCSPARSE_FORMAT_COO ? nullptr : view.ptr, view.idx, view.m,
+                                       align_up_256(buffer));
     const int ipt = spmv_workspace(view.m, A->nnz, value_size(computeType), small, index_size(A)).items_per_tile;
     bool analyse = true;
     {
@@ -633,7 +641,7 @@ St spmv_push_pipelined(mcsparseContext* h, mcsparseSpMatDescr* A, mcsparseDnVecD
                               mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer,
                               const PushArgs& push, int chunks) {
     void* buf = align_up_256(buffer);
-    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_tile_kind(h, A, A->cols, A->row_num, buf));
+    const SpmvWorkspace ws = spmv_workspace(A->row_num, A->nnz, sizeof(T), choose_tile_kind(h, A, A->rows, A->cols, A->row_num, buf));
     const int base = A->mat_descr->base;
     const int32_t* rows = static_cast<const int32_t*>(A->rows);
     if (h->side_stream == nullptr) {

@@ -180,10 +180,12 @@ struct SpmvWorkspace {
 enum : int { kTileLarge = 0, kTileSmall = 1, kTileWalk = 2 };
 SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile_kind = kTileLarge,
                              size_t index_size = 4);
-// Counts, over 4096 evenly spaced positions j, how often |col[j + 1] - col[j]| <= 8; the count is left
-// in *device_count and copied to *host_count (synchronises the stream).
+// host_count[0]: over 4096 evenly spaced positions j, how often |col[j + 1] - col[j]| <= 8; host_count[1]: how many
+// of 4096 evenly spaced rows hold more than 256 nonzeros. The counts are left in device_count[0..1] and copied
+// to host_count (synchronises the stream).
 template <typename I>
-cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const I* col, int* device_count, int* host_count);
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t m, int64_t nnz, const I* row_ptr, const I* col, int* device_count,
+                                int* host_count);
 inline void* align_up_256(void* p) {
     return reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255));
 }

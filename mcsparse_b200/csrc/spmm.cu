@@ -17,6 +17,9 @@ namespace mcsp_b200 {
 namespace {
 
 constexpr int kThreads = 256;
+#ifndef MCSP_PANEL_MIN_BLOCKS
+#define MCSP_PANEL_MIN_BLOCKS 4  // at most 64 registers: measured best (5 blocks of 48 registers ran 15 % slower)
+#endif
 
 template <typename T>
 struct VecOf;
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(kThreads)
 // are streamed (evict-first).
 // ---------------------------------------------------------------------------------------
 template <typename T, int G, bool FIRST>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
     spmm_panel_kernel(int m, int n, const int* __restrict__ pos, const int* __restrict__ ccol,
                       const T* __restrict__ cval, const T* __restrict__ B, long long ldb, T* __restrict__ C,
                       long long ldc, ScalarArg<T> alpha_arg, ScalarArg<T> beta_arg, int slab_c0) {
@@ -213,6 +216,7 @@ __global__ void __launch_bounds__(kThreads)
     const int c0 = slab_c0 + lane * W;  // first column of this lane
     const bool col_ok = c0 < n;
     const T* const Bc = B + c0;
+    const unsigned ldb32 = (unsigned)ldb;  // the launcher checks that every element offset into B fits 32 bits
     const T alpha = alpha_arg.get(), beta = beta_arg.get();
 
     // bounds of the group's rows i, i + 1, i + 2; the first 2 G elements of the pieces of rows i, i + 1
@@ -252,13 +256,13 @@ __global__ void __launch_bounds__(kThreads)
             for (int q = 0; q < first_half; ++q) {
                 const int cq = __shfl_sync(0xffffffffu, ca0, q, G);
                 const T vq = shfl_idx(0xffffffffu, va0, q, G);
-                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (long long)cq * ldb));
+                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32));
             }
 #pragma unroll 4
             for (int q = G; q < maxcnt; ++q) {
                 const int cq = __shfl_sync(0xffffffffu, cb0, q - G, G);
                 const T vq = shfl_idx(0xffffffffu, vb0, q - G, G);
-                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (long long)cq * ldb));
+                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32));
             }
         }
         if (write_c) {
@@ -387,6 +391,9 @@ cudaError_t launch_panels(cudaStream_t s, int64_t m, int64_t n, const T* val, co
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, spmm_panel_kernel<T, G, false>, kThreads, 0);
         if (blocks_per_sm < 1) blocks_per_sm = 1;
         if (sm_count < 1) sm_count = 148;
+        // Tuning: MCSPARSE_B200_SPMM_PANEL_BLOCKS caps the resident thread blocks per SM of a pass.
+        if (const char* v = std::getenv("MCSPARSE_B200_SPMM_PANEL_BLOCKS"))
+            blocks_per_sm = std::max(1, std::min(blocks_per_sm, std::atoi(v)));
     }
     char* base_ptr = static_cast<char*>(buf);
     const int* panel_ptr = reinterpret_cast<const int*>(base_ptr);
@@ -506,7 +513,9 @@ cudaError_t spmm(cudaStream_t s, int64_t m, int64_t n, int base, const I* row_pt
     constexpr int W = VecOf<T>::W;
     const bool vec_ok = b_cs == 1 && c_cs == 1 && n % W == 0 && b_rs % W == 0 && c_rs % W == 0 &&
                         ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
-    if (vec_ok && plan != nullptr && plan->num_panels > 1 && plan_buffer != nullptr) {
+    // (the pass kernel addresses B with 32-bit element offsets: rows of B x leading dimension must fit)
+    const bool fits32 = plan != nullptr && (unsigned long long)plan->num_panels * plan->panel_cols * (unsigned long long)b_rs < (1ull << 32);
+    if (vec_ok && fits32 && plan->num_panels > 1 && plan_buffer != nullptr) {
         switch (plan->lanes) {
             case 4: return launch_panels<T, 4>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);
             case 8: return launch_panels<T, 8>(s, m, n, val, B, b_rs, C, c_rs, alpha, beta, *plan, plan_buffer);

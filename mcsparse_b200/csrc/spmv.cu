@@ -36,23 +36,31 @@ struct TileCfg {
     static constexpr int kLarge = sizeof(I) == 8 ? kSmall : tile_items(sizeof(T), false) / kThreads;
 };
 
-// Column locality probe: 1024 threads x 4 samples.
+// Structure probe: 1024 threads x 4 samples. count[0]: how many of 4096 evenly spaced pairs of neighbouring
+// nonzeros have columns within 8 of each other; count[1]: how many of 4096 evenly spaced rows are longer
+// than 256 nonzeros.
 template <typename I>
-__global__ void locality_probe_kernel(long long nnz, const I* __restrict__ col, int* __restrict__ count) {
-    __shared__ int s_count;
-    if (threadIdx.x == 0) s_count = 0;
+__global__ void locality_probe_kernel(long long m, long long nnz, const I* __restrict__ row_ptr,
+                                      const I* __restrict__ col, int* __restrict__ count) {
+    __shared__ int s_near, s_long;
+    if (threadIdx.x == 0) s_near = s_long = 0;
     __syncthreads();
-    int local = 0;
+    int near = 0, longer = 0;
     for (int q = 0; q < 4; ++q) {
-        const long long j = ((long long)(threadIdx.x * 4 + q) * (nnz - 1)) / 4096;
-        if (j + 1 < nnz) {
+        const long long u = threadIdx.x * 4 + q;
+        const long long j = (u * (nnz - 1)) / 4096;
+        if (nnz >= 2 && j + 1 < nnz) {
             const long long d = (long long)__ldg(col + j + 1) - (long long)__ldg(col + j);
-            local += (d <= 8 && d >= -8);
+            near += (d <= 8 && d >= -8);
         }
+        const long long r = (u * m) / 4096;
+        if (row_ptr != nullptr && r < m && (m >= 4096 || (u * m) % 4096 < m))  // each row at most once
+            longer += ((long long)__ldg(row_ptr + r + 1) - (long long)__ldg(row_ptr + r)) > 256;
     }
-    atomicAdd(&s_count, local);
+    atomicAdd(&s_near, near);
+    atomicAdd(&s_long, longer);
     __syncthreads();
-    if (threadIdx.x == 0) *count = s_count;
+    if (threadIdx.x == 0) count[0] = s_near, count[1] = s_long;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -848,10 +856,11 @@ SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile
 }
 
 template <typename I>
-cudaError_t spmv_locality_probe(cudaStream_t s, int64_t nnz, const I* col, int* device_count, int* host_count) {
-    locality_probe_kernel<I><<<1, 1024, 0, s>>>(nnz, col, device_count);
+cudaError_t spmv_locality_probe(cudaStream_t s, int64_t m, int64_t nnz, const I* row_ptr, const I* col, int* device_count,
+                                int* host_count) {
+    locality_probe_kernel<I><<<1, 1024, 0, s>>>(m, nnz, row_ptr, col, device_count);
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaMemcpyAsync(host_count, device_count, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_count, device_count, 2 * sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return e;
 }
@@ -1111,8 +1120,10 @@ template cudaError_t spmv_analysis<int32_t>(cudaStream_t, int64_t, int64_t, int,
                                             void*);
 template cudaError_t spmv_analysis<int64_t>(cudaStream_t, int64_t, int64_t, int, const int64_t*, const SpmvWorkspace&,
                                             void*);
-template cudaError_t spmv_locality_probe<int32_t>(cudaStream_t, int64_t, const int32_t*, int*, int*);
-template cudaError_t spmv_locality_probe<int64_t>(cudaStream_t, int64_t, const int64_t*, int*, int*);
+template cudaError_t spmv_locality_probe<int32_t>(cudaStream_t, int64_t, int64_t, const int32_t*, const int32_t*, int*,
+                                                  int*);
+template cudaError_t spmv_locality_probe<int64_t>(cudaStream_t, int64_t, int64_t, const int64_t*, const int64_t*, int*,
+                                                  int*);
 #undef INSTANTIATE
 #undef INSTANTIATE_TI
 
