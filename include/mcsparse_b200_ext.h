@@ -149,6 +149,24 @@ mcsparseStatus_t mcsparseB200SpMVPushMulticast(mcsparseHandle_t handle, mcsparse
                                                int64_t rowOffset);
 
 /*
+ * Orders the GPUs of a row-sharded step on the device, without a collective. Every rank owns a flag area of
+ * MCSPARSE_B200_PEER_FLAG_INTS 32-bit integers in peer-mapped memory, zeroed once: slot p (p < numPeers)
+ * belongs to the rank's p-th peer, integer MCSPARSE_B200_PEER_FLAG_STATUS is a status word. The call
+ * enqueues one small kernel on the handle's stream, after whatever moved this rank's rows (in stream
+ * order): it stores `epoch` into remoteSlots[p], this rank's slot inside peer p's flag area, with release
+ * semantics at system scope, and then waits until every slot of localFlags has reached `epoch` (acquire),
+ * i.e. until every peer's rows of that step are in this GPU's memory. Epochs must grow from step to step
+ * (compared modulo 2^32). The wait is bounded (fifty times the handle's device wait limit, about a second):
+ * when it runs out the kernel sets bit 0 of the status word and the handle's fault word and returns, and the
+ * next compute call on the handle reports MCSPARSE_STATUS_EXECUTION_FAILED. The waiting kernels of the ranks
+ * run on different GPUs; never run two ranks of one job on the same GPU. No reference counterpart.
+ */
+#define MCSPARSE_B200_PEER_FLAG_INTS 16
+#define MCSPARSE_B200_PEER_FLAG_STATUS 8
+mcsparseStatus_t mcsparseB200PeerSignalWait(mcsparseHandle_t handle, int numPeers, void* const* remoteSlots,
+                                            void* localFlags, int epoch);
+
+/*
  * Device buffers that other processes on the same node can map (one process per GPU):
  * PeerAlloc/PeerFree allocate with the plain CUDA allocator; PeerExport fills a 64-byte
  * handle that another process passes to PeerOpen to obtain an address valid on its current

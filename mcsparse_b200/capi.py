@@ -21,6 +21,7 @@ MCSPARSE_STATUS_INTERNAL_ERROR = 7
 MCSPARSE_STATUS_NOT_SUPPORTED = 10
 MCSPARSE_STATUS_INSUFFICIENT_RESOURCES = 11
 NOALLOC_SCRATCH_BYTES = 16 << 20
+PEER_FLAG_INTS, PEER_FLAG_STATUS = 16, 8
 # operations
 MCSPARSE_OPERATION_NON_TRANSPOSE = 0
 MCSPARSE_OPERATION_TRANSPOSE = 1
@@ -131,6 +132,7 @@ PROTOTYPES = {
     "mcsparseB200SpMVNoAlloc": (_i, _SPMV_ARGS),
     "mcsparseB200SpMVPush": (_i, _SPMV_ARGS + [_vp, _i, _pvp, _i64]),
     "mcsparseB200SpMVPushMulticast": (_i, _SPMV_ARGS + [_vp, _vp, _i64]),
+    "mcsparseB200PeerSignalWait": (_i, [_vp, _i, _pvp, _vp, _i]),
     "mcsparseB200PeerAlloc": (_i, [_pvp, _sz]),
     "mcsparseB200PeerFree": (_i, [_vp]),
     "mcsparseB200PeerExport": (_i, [_vp, _vp]),

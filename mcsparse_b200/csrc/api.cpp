@@ -174,6 +174,7 @@ struct PushArgs {
     void* const* y = nullptr;
     int64_t row_offset = 0;
     bool multicast = false;  // y[0] is a multicast address reaching every GPU
+    bool bulk = false;       // rows leave through bulk copies from shared memory
 };
 
 size_t index_size(const mcsparseSpMatDescr* A) { return A->rowIdxType == MCSPARSE_INDEX_64I ? 8 : 4; }
@@ -262,6 +263,7 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
     peers.count = push.count;
     peers.row_offset = push.row_offset;
     peers.multicast = push.multicast;
+    peers.bulk = push.bulk;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
     cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
@@ -1197,6 +1199,15 @@ mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation
     push.count = numPeers;
     push.y = peerY;
     push.row_offset = rowOffset;
+    // The in-kernel push hands the finished rows to the TMA unit (bulk copies from shared memory) when every
+    // destination has the same alignment modulo 16 bytes; MCSPARSE_B200_PUSH_STORE=lsu keeps ordinary stores.
+    {
+        const char* e = std::getenv("MCSPARSE_B200_PUSH_STORE");
+        bool bulk = !(e != nullptr && e[0] == 'l') && numPeers > 0;
+        for (int p = 1; p < numPeers; ++p)
+            bulk = bulk && ((reinterpret_cast<uintptr_t>(peerY[p]) ^ reinterpret_cast<uintptr_t>(peerY[0])) & 15) == 0;
+        push.bulk = bulk;
+    }
     const int chunks = push_chunks_setting(numPeers);
     if (chunks == 0 || numPeers == 0)
         return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
@@ -1228,6 +1239,26 @@ mcsparseStatus_t mcsparseB200SpMVPushMulticast(mcsparseHandle_t handle, mcsparse
     push.row_offset = rowOffset;
     push.multicast = true;
     return pub(spmv_entry(handle, opA, alpha, matA, vecX, beta, vecY, computeType, externalBuffer, false, push));
+}
+
+mcsparseStatus_t mcsparseB200PeerSignalWait(mcsparseHandle_t handle, int numPeers, void* const* remoteSlots,
+                                            void* localFlags, int epoch) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (numPeers < 0 || numPeers > PeerList<float>::kMax) return pub(BAD_SIZE);
+    if (numPeers == 0) return MCSPARSE_STATUS_SUCCESS;
+    if (remoteSlots == nullptr || localFlags == nullptr) return pub(BAD_POINTER);
+    int* slots[PeerList<float>::kMax] = {};
+    for (int p = 0; p < numPeers; ++p) {
+        if (remoteSlots[p] == nullptr) return pub(BAD_POINTER);
+        slots[p] = static_cast<int*>(remoteSlots[p]);
+    }
+    if (take_device_fault(handle)) return pub(EXEC_FAILED);
+    DeviceGuard guard(handle->device);
+    int* local = static_cast<int*>(localFlags);
+    // Peers finish their step at slightly different times: the limit is fifty times the copy-wait limit
+    // (about a second of SM clocks by default).
+    return pub(from_cuda(peer_signal_wait(handle->stream, numPeers, slots, local, epoch, handle->wait_cycles * 50,
+                                          local + MCSPARSE_B200_PEER_FLAG_STATUS, handle->fault_word_dev)));
 }
 
 mcsparseStatus_t mcsparseB200PeerAlloc(void** devPtr, size_t bytes) {

@@ -146,6 +146,7 @@ struct PeerList {
     static constexpr int kMax = 7;
     int count = 0;
     bool multicast = false;
+    bool bulk = false;  // finished rows leave through bulk copies from shared memory (all y[p] congruent modulo 16)
     long long row_offset = 0;
     T* y[kMax] = {};
 };
@@ -293,6 +294,10 @@ cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* h
 template <typename T>
 cudaError_t transpose_values(cudaStream_t s, int64_t nnz, const T* val, const TransposePlan& plan, void* buf,
                              bool conjugate = false);
+// Signals `epoch` into remote_slots[p] (p < count <= 7) and waits, for at most `limit` SM clocks per peer, until
+// local_slots[p] has reached it; a wait that runs out sets bit 0 of *status and the fault word.
+cudaError_t peer_signal_wait(cudaStream_t s, int count, int* const* remote_slots, const int* local_slots, int epoch,
+                             long long limit, int* status, int* fault_word);
 cudaError_t shard_row_bounds(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* row_ptr,
                              int num_shards, int64_t* bounds_host);
 cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int64_t first_row, int64_t num_rows,

@@ -58,6 +58,36 @@ __global__ void coo_row_offsets_kernel(long long m, long long nnz, int base, con
     offsets[r] = (int)lo + base;
 }
 
+// Orders the GPUs of a row-sharded step without a collective: lane p tells peer p "my rows of step `epoch`
+// are in your memory" by storing the epoch into that peer's flag slot for this rank (a release at system
+// scope: the kernel runs after the kernels and copies that moved the rows, in stream order), then lane q
+// waits until peer q's epoch has arrived in this GPU's own slots (acquire at system scope). The wait is
+// bounded: when `limit` SM clocks pass without the flag, the lane records it in the status word (and in the
+// handle's host-visible fault word) and the kernel returns. Epochs only grow; slots are never reset.
+struct PeerFlags {
+    int* remote[7];  // remote[p]: peer p's slot for this rank
+};
+__global__ void peer_signal_wait_kernel(int count, PeerFlags flags, const int* local_slots, int epoch, long long limit,
+                                        int* status, int* fault_word) {
+    const int p = threadIdx.x;
+    if (p >= count) return;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.remote[p]), "r"(epoch) : "memory");
+    const long long t0 = clock64();
+    for (;;) {
+        int seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(local_slots + p) : "memory");
+        if (seen - epoch >= 0) break;
+        if (clock64() - t0 > limit) {
+            atomicOr(status, 1);
+            if (fault_word != nullptr) {
+                *reinterpret_cast<volatile int*>(fault_word) = 1;
+                __threadfence_system();
+            }
+            break;
+        }
+    }
+}
+
 }  // namespace
 
 cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
@@ -85,6 +115,16 @@ cudaError_t shard_local_row_offsets(cudaStream_t s, const int32_t* row_ptr, int6
     const int threads = 256;
     shard_local_row_offsets_kernel<<<(unsigned)((num_rows + 1 + threads - 1) / threads), threads, 0, s>>>(
         row_ptr, first_row, num_rows, base, local);
+    return cudaGetLastError();
+}
+
+cudaError_t peer_signal_wait(cudaStream_t s, int count, int* const* remote_slots, const int* local_slots, int epoch,
+                             long long limit, int* status, int* fault_word) {
+    if (count <= 0) return cudaSuccess;
+    if (count > 7) return cudaErrorInvalidValue;
+    PeerFlags f;
+    for (int p = 0; p < 7; ++p) f.remote[p] = p < count ? remote_slots[p] : nullptr;
+    peer_signal_wait_kernel<<<1, 32, 0, s>>>(count, f, local_slots, epoch, limit, status, fault_word);
     return cudaGetLastError();
 }
 

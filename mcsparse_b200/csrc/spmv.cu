@@ -223,6 +223,60 @@ __device__ __forceinline__ void push_tile_rows(const PeerList<T>& peers, const T
     }
 }
 
+// Misalignment, in elements, of the peers' address of local row `row0` against 16 bytes (the same for every
+// peer when the bulk push is on): rows staged for the bulk push start at this offset of a 16-byte aligned area.
+template <typename T>
+__device__ __forceinline__ int push_misalign(const PeerList<T>& peers, long long row0) {
+    constexpr int VW = 16 / (int)sizeof(T);
+    if (!peers.bulk) return 0;
+    return (int)((reinterpret_cast<uintptr_t>(peers.y[0] + peers.row_offset + row0) / sizeof(T)) & (VW - 1));
+}
+
+// Same job as push_tile_rows with the bulk of the bytes moved by the TMA unit instead of the load/store
+// unit: the finished rows sit in shared memory, placed so that the value bound for the first 16-byte
+// aligned destination address is itself 16-byte aligned (vals[i] = row row0 + i; the caller offsets its
+// staging area by the destination's misalignment), and one thread starts one bulk copy shared -> global
+// per peer. Peer stores issued by the load/store unit queue behind NVLink in the same path as the x
+// gathers and stall the SM's other thread blocks; bulk stores wait in the TMA unit instead, so the tiles
+// that are still computing keep their loads flowing and the transfer overlaps the computation.
+// All destinations must share their alignment modulo 16 bytes (the host checks). Every thread of the
+// block calls this after writing its rows; the block may not touch the staged rows until it returns.
+template <typename T, int THREADS>
+__device__ __forceinline__ void push_tile_rows_bulk(const PeerList<T>& peers, const T* vals, long long row0, int n,
+                                                    int tid) {
+    constexpr int VW = 16 / (int)sizeof(T);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this thread's rows, for the bulk copies
+    __syncthreads();
+    T* const dst0 = peers.y[0] + peers.row_offset + row0;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(dst0) / sizeof(T)) & (VW - 1));
+    const int head = min(n, (VW - mis) & (VW - 1));
+    const int nvec = (n - head) / VW;
+    const int tail0 = head + nvec * VW;
+    if (tid == 0 && nvec > 0) {
+        const uint32_t src = smem_addr(vals + head);
+        const uint32_t bytes = (uint32_t)nvec * 16u;
+#pragma unroll
+        for (int p = 0; p < PeerList<T>::kMax; ++p)
+            if (p < peers.count)
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                                 peers.y[p] + peers.row_offset + row0 + head),
+                             "r"(src), "r"(bytes)
+                             : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    // the few rows before the first and after the last aligned group: ordinary stores by the last threads
+    const int u = THREADS - 1 - tid;
+#pragma unroll
+    for (int p = 0; p < PeerList<T>::kMax; ++p) {
+        if (p < peers.count) {
+            T* const dst = peers.y[p] + peers.row_offset + row0;
+            if (u < head) dst[u] = vals[u];
+            if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
+        }
+    }
+    if (tid == 0 && nvec > 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staged rows were read
+}
+
 // ---------------------------------------------------------------------------------------
 // Staging of one tile's slice of col / val in shared memory, shared by the tile kernels.
 //
@@ -370,7 +424,7 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ int s_warp_maxlen[NWARPS];
     __shared__ int s_failed;
     constexpr int PUSHCAP = PUSH ? 512 : 1;  // finished rows of a short-row tile staged for the push
-    __shared__ T s_push[PUSHCAP];
+    __shared__ __align__(16) T s_push[PUSHCAP + 4];
 
     const int tid = threadIdx.x;
     const int t = blockIdx.x + tile_offset;  // a launch may cover a sub-range of the tiles
@@ -418,6 +472,7 @@ __global__ void __launch_bounds__(THREADS)
     const T alpha = alpha_arg.get();
     const T beta = beta_arg.get();
 
+    const int push_mis = PUSH ? push_misalign(peers, row_s) : 0;
     if (short_rows) {
         const int G = 1 << lgG;
         const int ngroups = THREADS >> lgG;
@@ -448,7 +503,7 @@ __global__ void __launch_bounds__(THREADS)
                     y[row_s + i] = v;
                     if constexpr (PUSH) {
                         if (nrows <= PUSHCAP)
-                            s_push[i] = v;
+                            s_push[push_mis + i] = v;
                         else
                             push_to_peers(peers, row_s + i, v);
                     }
@@ -460,15 +515,20 @@ __global__ void __launch_bounds__(THREADS)
         }
         if constexpr (PUSH) {
             if (nrows <= PUSHCAP) {  // block-uniform
-                __syncthreads();
-                push_tile_rows<T, THREADS>(peers, s_push, row_s, nrows, tid);
+                if (peers.bulk) {
+                    push_tile_rows_bulk<T, THREADS>(peers, s_push + push_mis, row_s, nrows, tid);
+                } else {
+                    __syncthreads();
+                    push_tile_rows<T, THREADS>(peers, s_push, row_s, nrows, tid);
+                }
             }
         }
         return;
     }
 
     // ---- long rows: products in place, merge walk, segmented reduction of the carries
-    T* const s_y = valv + nnz_tile;  // s_y[i]: row row_s + i, i in [0, nrows]
+    // s_y[i]: row row_s + i, i in [0, nrows]; with the bulk push, placed for 16-byte aligned copies
+    T* const s_y = (PUSH && peers.bulk) ? s_val + ((ts.head_v + nnz_tile + 3) & ~3) + push_mis : valv + nnz_tile;
     {
         // Lane-consecutive nonzeros; all of a thread's gathers are issued before the first product.
         T xv[IPT];
@@ -546,8 +606,12 @@ __global__ void __launch_bounds__(THREADS)
     }
     if constexpr (PUSH) {
         const T open_sum = s_y[nrows];
-        __syncthreads();
-        push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        if (peers.bulk) {
+            push_tile_rows_bulk<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        } else {
+            __syncthreads();
+            push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        }
         if (tid == 0) {
             carry_row[t] = row_s + nrows;
             carry_val[t] = open_sum;
@@ -611,7 +675,9 @@ __global__ void __launch_bounds__(THREADS)
     const I* const colv = s_col + ts.head_c;
     const T* const valv = s_val + ts.head_v;
     int* const s_row_end = reinterpret_cast<int*>(s_col + ts.span_c);  // nrows + 1 ints; nrows + nnz_tile <= TILE
-    T* const s_y = s_val + ts.head_v + nnz_tile;                        // s_y[i]: row row_s + i, i in [0, nrows]
+    // s_y[i]: row row_s + i, i in [0, nrows]; with the bulk push, placed for 16-byte aligned copies
+    T* const s_y = (PUSH && peers.bulk) ? s_val + ((ts.head_v + nnz_tile + 3) & ~3) + push_misalign(peers, row_s)
+                                        : s_val + ts.head_v + nnz_tile;
 
     // Row ends in tile-local nonzero coordinates; entry nrows belongs to the row left open.
     for (int i = tid; i <= nrows; i += THREADS) {
@@ -711,8 +777,12 @@ __global__ void __launch_bounds__(THREADS)
     }
     if constexpr (PUSH) {
         const T open_sum = s_y[nrows];
-        __syncthreads();
-        push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        if (peers.bulk) {
+            push_tile_rows_bulk<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        } else {
+            __syncthreads();
+            push_tile_rows<T, THREADS>(peers, s_y, row_s, nrows, tid);
+        }
         if (tid == 0) {
             carry_row[t] = row_s + nrows;
             carry_val[t] = open_sum;

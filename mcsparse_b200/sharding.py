@@ -68,10 +68,16 @@ class PeerVector:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         itemsize = torch.empty(0, dtype=dtype).element_size()
         p = C.c_void_p()
-        check(lib.mcsparseB200PeerAlloc(C.byref(p), max(numel, 1) * itemsize), "mcsparseB200PeerAlloc")
+        # behind the vector (256-byte aligned): the flag area of mcsparseB200PeerSignalWait
+        self.flag_offset = (max(numel, 1) * itemsize + 255) & ~255
+        check(lib.mcsparseB200PeerAlloc(C.byref(p), self.flag_offset + capi.PEER_FLAG_INTS * 4), "mcsparseB200PeerAlloc")
         self.ptr = p.value
-        self.tensor = torch.as_tensor(_DeviceArray(self.ptr, numel, dtype), device=torch.device("cuda", torch.cuda.current_device()))
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.tensor = torch.as_tensor(_DeviceArray(self.ptr, numel, dtype), device=device)
         self.tensor.zero_()
+        self.flags = torch.as_tensor(_DeviceArray(self.ptr + self.flag_offset, capi.PEER_FLAG_INTS, torch.int32), device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize()
         handle = C.create_string_buffer(64)
         check(lib.mcsparseB200PeerExport(C.c_void_p(self.ptr), handle), "mcsparseB200PeerExport")
         handles = [None] * self.world
@@ -83,6 +89,11 @@ class PeerVector:
             mapped = C.c_void_p()
             check(lib.mcsparseB200PeerOpen(C.create_string_buffer(raw, 64), C.byref(mapped)), "mcsparseB200PeerOpen")
             self.peer_ptrs[g] = mapped.value
+        # slot of source rank g inside a rank r's flag area: g's position among r's peers in rank order
+        peers = sorted(self.peer_ptrs)
+        self.remote_slots = (C.c_void_p * max(len(peers), 1))(*[
+            self.peer_ptrs[g] + self.flag_offset + 4 * (self.rank if self.rank < g else self.rank - 1) for g in peers])
+        dist.barrier(group=group)  # every rank's flag area is zeroed before anyone signals into it
 
     def close(self):
         torch.cuda.synchronize()
@@ -93,6 +104,7 @@ class PeerVector:
         dist.barrier(group=self.group)
         if self.ptr:
             self.tensor = None
+            self.flags = None
             lib.mcsparseB200PeerFree(C.c_void_p(self.ptr))
             self.ptr = 0
 
@@ -164,6 +176,13 @@ class ShardedSpmv:
         self.n_peers = len(ptrs)
         self.peer_array = (C.c_void_p * max(self.n_peers, 1))(*ptrs)
         self.token = torch.zeros(1, dtype=torch.int32, device=x.device)
+        import os
+
+        # After the push the GPUs are ordered by per-peer arrival flags written and awaited on the device
+        # (mcsparseB200PeerSignalWait); MCSPARSE_B200_PUSH_SYNC=collective uses a 4-byte all-reduce instead,
+        # as the multicast variant always does (its vector comes from another allocator).
+        self.sync_flags = self.mode == "peer" and os.environ.get("MCSPARSE_B200_PUSH_SYNC", "flags") != "collective"
+        self.epoch = 0
 
     def compute(self, alpha=1.0, beta=0.0):
         """Launches the local SpMV with the push of finished rows to the peers (asynchronous)."""
@@ -189,7 +208,13 @@ class ShardedSpmv:
         rank's kernel has finished and therefore all pushes into this GPU's y have landed."""
         self.compute(alpha, beta)
         if self.world > 1:
-            dist.all_reduce(self.token, group=self.group)
+            if self.sync_flags:
+                self.epoch = (self.epoch + 1) & 0x7FFFFFFF
+                check(lib.mcsparseB200PeerSignalWait(self.h.h, self.n_peers, self.y.remote_slots,
+                                                     C.c_void_p(self.y.ptr + self.y.flag_offset), self.epoch),
+                      "mcsparseB200PeerSignalWait")
+            else:
+                dist.all_reduce(self.token, group=self.group)
 
     def close(self):
         self.y.close()

@@ -48,12 +48,24 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, name, factor, chunks, out, mode="peer"):
+def _worker(rank, world, port, name, factor, chunks, out, mode="peer", store="bulk", sync="flags"):
+    """One rank of a two-GPU run. A comparison that fails is recorded in out[rank] and the rank still walks
+    through every barrier and the tear-down of its peer mappings (job.close()), so that the other rank is
+    never left waiting and no memory stays bound to a multicast object; the parent asserts on `out`."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), MCSPARSE_B200_PUSH_CHUNKS=str(chunks),
-                      MCSPARSE_B200_PUSH_MODE=mode)
+                      MCSPARSE_B200_PUSH_MODE=mode, MCSPARSE_B200_PUSH_STORE=store, MCSPARSE_B200_PUSH_SYNC=sync)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    errors = []
+
+    def check(fn):
+        try:
+            fn()
+        except AssertionError as e:
+            errors.append(str(e)[:500])
+
+    job = None
     try:
         cfg = workloads.scaled(name, factor)
         lengths = workloads.row_lengths(cfg, dev)
@@ -66,7 +78,7 @@ def _worker(rank, world, port, name, factor, chunks, out, mode="peer"):
         alpha, beta = 1.5, 0.5
         ref, d = oracle.spmv(whole.row_ptr, whole.col, whole.val, whole.x, alpha, beta, whole.y0)
 
-        # product path: rows pushed to the peers by the kernel, one tiny collective to order the GPUs
+        # product path: rows pushed to the peers by the kernel, then the GPUs are ordered
         try:
             job = sharding.ShardedSpmv(h, A, w.x, r0, cfg.rows)
         except RuntimeError as e:  # no multicast mapping on this system: the same on every rank
@@ -74,7 +86,7 @@ def _worker(rank, world, port, name, factor, chunks, out, mode="peer"):
                 raise
             out[rank] = f"skipped: {e}"
             return
-        assert job.mode == mode
+        check(lambda: _assert(job.mode == mode, "push mode"))
         for _ in range(2):  # second step: the work buffer and the peer mappings are reused
             job.y.tensor.fill_(float("nan"))
             job.y_local.copy_(w.y0)
@@ -82,7 +94,8 @@ def _worker(rank, world, port, name, factor, chunks, out, mode="peer"):
             dist.barrier()
             job.step(alpha, beta)
             torch.cuda.synchronize()
-            assert_close(job.y.tensor.cpu().numpy(), ref, d, TOL[cfg.dtype], f"push, rank {rank}")
+            got = job.y.tensor.cpu().numpy()
+            check(lambda: assert_close(got, ref, d, TOL[cfg.dtype], f"push, rank {rank}"))
         dist.barrier()
 
         # baseline path: local SpMV, then a ragged NCCL all-gather
@@ -94,17 +107,26 @@ def _worker(rank, world, port, name, factor, chunks, out, mode="peer"):
         mc.spmv(h, A, X, Y, buf, alpha=alpha, beta=beta)
         sharding.all_gather_ragged([y_full[bounds[g]:bounds[g + 1]] for g in range(world)], y_loc)
         torch.cuda.synchronize()
-        assert_close(y_full.cpu().numpy(), ref, d, TOL[cfg.dtype], f"all-gather, rank {rank}")
-        assert torch.equal(y_full, job.y.tensor)  # both assemblies hold the very same bits
-        job.close()
-        out[rank] = 1
+        check(lambda: assert_close(y_full.cpu().numpy(), ref, d, TOL[cfg.dtype], f"all-gather, rank {rank}"))
+        check(lambda: _assert(torch.equal(y_full, job.y.tensor), "both assemblies hold the very same bits"))
+        out[rank] = "; ".join(errors) if errors else 1
     finally:
-        dist.destroy_process_group()
+        try:
+            if job is not None:
+                job.close()  # two barriers inside: peers are unmapped before anyone frees
+        finally:
+            dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("chunks", [0, 4])  # 0: rows stored to the peers by the tile kernel; 4: pipelined row copies
+def _assert(cond, what):
+    assert cond, what
+
+
+# chunks 0: rows stored to the peers by the tile kernel (bulk copies from shared memory, or ordinary stores);
+# 4: pipelined row copies. The GPUs are ordered by device-side arrival flags, or by a 4-byte all-reduce.
+@pytest.mark.parametrize("chunks,store,sync", [(0, "bulk", "flags"), (0, "lsu", "collective"), (4, "bulk", "flags")])
 @pytest.mark.parametrize("name,factor", [("C5", 512), ("C3", 256)])
-def test_sharded_spmv_push_and_allgather_two_gpus(name, factor, chunks):
+def test_sharded_spmv_push_and_allgather_two_gpus(name, factor, chunks, store, sync):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     port = _free_port()
@@ -112,8 +134,8 @@ def test_sharded_spmv_push_and_allgather_two_gpus(name, factor, chunks):
     os.environ.update(env)
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(2, port, name, factor, chunks, out), nprocs=2, join=True)
-        assert sorted(out.keys()) == [0, 1]
+        mp.spawn(_worker, args=(2, port, name, factor, chunks, out, "peer", store, sync), nprocs=2, join=True)
+        assert dict(out) == {0: 1, 1: 1}
 
 
 @pytest.mark.parametrize("name,factor", [("C5", 512), ("C3", 256)])
@@ -126,24 +148,27 @@ def test_sharded_spmv_multicast_push_two_gpus(name, factor):
         out = mgr.dict()
         mp.spawn(_worker, args=(2, port, name, factor, 0, out, "multicast"), nprocs=2, join=True)
         assert sorted(out.keys()) == [0, 1]
-        if any(isinstance(v, str) for v in out.values()):
+        if any(isinstance(v, str) and v.startswith("skipped") for v in out.values()):
             pytest.skip(str(out[0]))
+        assert dict(out) == {0: 1, 1: 1}
 
 
-@pytest.mark.parametrize("chunks", [0, 1, 4, 8])
+@pytest.mark.parametrize("chunks,store", [(0, "bulk"), (0, "lsu"), (1, "bulk"), (4, "bulk"), (8, "bulk")])
+@pytest.mark.parametrize("offset", [5, 8])
 @pytest.mark.parametrize("name,factor", [("C3", 256), ("C5", 512), ("C2", 512)])
-def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor, chunks, monkeypatch):
+def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor, chunks, store, offset,
+                                                          monkeypatch):
     """One-GPU stand-in for a peer: the push destination is another buffer on the same device. The
     pushed copy, the local result and plain mcsparseSpMV must agree bit for bit, with the pushed
     rows landing at rowOffset + row."""
     from mcsparse_b200 import host
 
     monkeypatch.setenv("MCSPARSE_B200_PUSH_CHUNKS", str(chunks))
+    monkeypatch.setenv("MCSPARSE_B200_PUSH_STORE", store)
     cfg = workloads.scaled(name, factor)
     w = workloads.generate(cfg, device)
     A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
     y_plain, y_push = w.y0.clone(), w.y0.clone()
-    offset = 5
     peer = torch.full((w.rows + 2 * offset,), float("nan"), dtype=cfg.dtype, device=device)
     X, Y1, Y2 = mc.DnVec(w.x), mc.DnVec(y_plain), mc.DnVec(y_push)
     buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y1), dtype=torch.uint8, device=device)
@@ -191,3 +216,33 @@ def test_pipelined_push_replays_with_alternating_vectors(handle, device, monkeyp
                                             host._ptr(buf), 1, arr, 0))
         torch.cuda.synchronize()
         assert torch.equal(ys[i], expect[i]) and torch.equal(peers[i], expect[i]), f"step {step}"
+
+
+def test_peer_signal_wait_loopback_and_bounded_wait(device):
+    """mcsparseB200PeerSignalWait on one GPU. Loopback: the "remote" slot is this rank's own slot, so the
+    kernel's signal satisfies its own wait. Then a slot that nothing sets: the wait runs out after the
+    handle's limit, the kernel returns by itself, the status word and the next compute call report it."""
+    h = mc.Handle()
+    try:
+        flags = torch.zeros(capi.PEER_FLAG_INTS, dtype=torch.int32, device=device)
+        slot0 = (C.c_void_p * 1)(flags.data_ptr())
+        for epoch in (1, 2, 7):
+            capi.check(lib.mcsparseB200PeerSignalWait(h.h, 1, slot0, C.c_void_p(flags.data_ptr()), epoch))
+            torch.cuda.synchronize()
+            assert flags[0].item() == epoch and flags[capi.PEER_FLAG_STATUS].item() == 0
+        # signal goes to a slot elsewhere, the awaited slot 0 stays at 7 < 8: bounded wait, about 0.5 ms
+        capi.check(lib.mcsparseB200SetDeviceWaitLimit(h.h, 20000, 0))
+        other = torch.zeros(1, dtype=torch.int32, device=device)
+        elsewhere = (C.c_void_p * 1)(other.data_ptr())
+        capi.check(lib.mcsparseB200PeerSignalWait(h.h, 1, elsewhere, C.c_void_p(flags.data_ptr()), 8))
+        torch.cuda.synchronize()
+        assert other.item() == 8 and flags[capi.PEER_FLAG_STATUS].item() == 1
+        assert lib.mcsparseB200PeerSignalWait(h.h, 1, slot0, C.c_void_p(flags.data_ptr()), 9) == \
+            capi.MCSPARSE_STATUS_EXECUTION_FAILED  # reported once, by the next call on the handle
+        capi.check(lib.mcsparseB200PeerSignalWait(h.h, 1, slot0, C.c_void_p(flags.data_ptr()), 9))
+        torch.cuda.synchronize()
+        assert flags[0].item() == 9
+        assert lib.mcsparseB200PeerSignalWait(h.h, 8, slot0, C.c_void_p(flags.data_ptr()), 1) == \
+            capi.MCSPARSE_STATUS_INVALID_VALUE
+    finally:
+        h.close()
