@@ -36,8 +36,13 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) of one spmv_tile_kernel launch divided by its algorithmic bytes, from the ncu
 # captures summarised under profiles/ (taken at reduced scale and scaled by the units processed).
-TRAFFIC_RATIO = {"C5": 0.985}
+TRAFFIC_RATIO = {"C5": 0.985, "C2": 0.99, "C3": 0.99, "C4_n64": 3.8}
 FALLBACK_HBM_GBS = 6650.0
+
+
+def PUSH_CHUNKS_DEFAULT(world):
+    """Chunks of the pipelined row push the library chooses for `world` GPUs (0: the tile kernel pushes)."""
+    return 4 if 2 <= world <= 4 else 0
 METRIC = "csr_spmv_spmm_algorithmic_hbm_throughput"
 UNIT = "GB/s"
 
@@ -169,10 +174,16 @@ class SpmvJob:
             self.y.copy_(w.y0)
         self.parts = [self.y_full[bounds[g]:bounds[g + 1]] for g in range(world)]
         self.bytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, self.total_nnz, self.vsize, cfg.beta, index_size=isize)
-        self.local_bytes = workloads.algorithmic_bytes(w.rows, w.cols, w.nnz, self.vsize, cfg.beta, index_size=isize)
+        # what this rank's kernel must move: of x only the span of columns its row block touches (a block of a
+        # stencil reaches one plane beyond itself; a block of a random matrix reaches all of x)
+        span = int((w.col.max() - w.col.min()).item()) + 1 if w.nnz else 0
+        self.local_bytes = workloads.algorithmic_bytes(w.rows, min(w.cols, span), w.nnz, self.vsize, cfg.beta,
+                                                       index_size=isize)
         self.flops = 2 * self.total_nnz
-        # tile kernel + carry fix-up; with one peer the step is pipelined: 4 tile launches + 4 fix-ups
-        self.launches_per_step = 8 if 2 <= world <= 4 else 2
+        # tile kernel + carry fix-up; sharded: per chunk a tile launch and a fix-up (pipelined push), or one of each
+        # (rows pushed by the tile kernel), and the kernel that orders the GPUs
+        chunks = int(os.environ.get("MCSPARSE_B200_PUSH_CHUNKS", PUSH_CHUNKS_DEFAULT(world)))
+        self.launches_per_step = 2 if world == 1 else (2 * chunks if chunks else 2) + 1
 
     def compute(self):
         """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""
@@ -290,6 +301,27 @@ def time_steps(torch, fn, steps, warmup, flush_buf=None, barrier=None):
     return total, per
 
 
+def gather_rate(torch, handle, device, elem_bytes=4, count=1 << 26, table_elems=1 << 24):
+    """Gathers per second this GPU sustains on unrelated elements (mcsparseB200GatherProbe, timed here with
+    events): the second roofline of an SpMV whose columns are scattered."""
+    import ctypes as C
+
+    from mcsparse_b200 import capi
+
+    idx = torch.randint(0, table_elems, (count,), dtype=torch.int32, device=device)
+    table = torch.zeros(table_elems, dtype=torch.float64 if elem_bytes == 8 else torch.float32, device=device)
+    blocks = 148 * 8
+    out = torch.empty(blocks * 256, dtype=table.dtype, device=device)
+
+    def fn():
+        capi.check(capi.lib.mcsparseB200GatherProbe(handle.h, C.c_void_p(idx.data_ptr()), count,
+                                                    C.c_void_p(table.data_ptr()), elem_bytes,
+                                                    C.c_void_p(out.data_ptr()), blocks))
+
+    total, _ = time_steps(torch, fn, 5, 3)
+    return count / (total / 5 * 1e-3)
+
+
 def measure_job(torch, job, steps, warmup, peak, flush_buf):
     flush = flush_buf if job.bytes < 4 * L2_BYTES else None
     total, per = time_steps(torch, job.compute, steps, warmup, flush)
@@ -306,14 +338,18 @@ def measure_job(torch, job, steps, warmup, peak, flush_buf):
     return out
 
 
-def cpu_baseline(name, seconds=12.0, steps=None, warmup=1):
-    """Times the OpenMP CSR kernel of oracle/ on a bounded row block of the workload (host cores)."""
+def cpu_baseline(name, seconds=12.0, steps=None, step_seconds=0.3):
+    """Times the OpenMP CSR kernel of oracle/ on a bounded row block of the workload, on all the host cores
+    this process may use. Warm-up is by time (3 s: the OpenMP team and the caches are cold in a process that
+    has done nothing else). With `steps`, a step is as many passes as fill `step_seconds`; otherwise passes
+    are repeated for about `seconds`. Returns (cpu_baseline dict, seconds per pass, steps, passes per step)."""
     import numpy as np
     import torch
 
     from mcsparse_b200 import workloads
     from oracle import oracle
 
+    cores = oracle.use_host_cores()
     cfg = workloads.CONFIGS[name]
     target_nnz = 40_000_000
     lengths_mean = {"C1": 5, "C2": 16, "C3": 12, "C4": 32, "C5": 27}[name]
@@ -338,37 +374,64 @@ def cpu_baseline(name, seconds=12.0, steps=None, warmup=1):
         fn = lambda: oracle.baseline_spmm(rp, col, val, B, n, cfg.alpha, cfg.beta, Cm)
         nbytes = workloads.algorithmic_bytes(rows, cfg.rows, w.nnz, vsize, cfg.beta, dense_cols=n)
         desc = f"rows [0, {rows}) of {name} ({w.nnz} nnz), B {cfg.rows} x {n}"
-    for _ in range(warmup):
+    t_end = time.perf_counter() + 3.0
+    passes = 0
+    while time.perf_counter() < t_end or passes < 3:
         fn()
+        passes += 1
     t = time.perf_counter()
     fn()
-    one = time.perf_counter() - t
+    one = max(time.perf_counter() - t, 1e-6)
     if steps is None:
-        steps = int(min(20000, max(3, seconds / max(one, 1e-6))))  # about `seconds` of CPU work
+        per_step, steps_run = 1, int(min(20000, max(3, seconds / one)))
+    else:
+        per_step, steps_run = max(1, int(round(step_seconds / one))), steps
     t = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(steps_run * per_step):
         fn()
-    dt = (time.perf_counter() - t) / steps
-    return {"value": round(nbytes / dt / 1e9, 2), "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-            "sample": f"{desc}; {steps} passes, {dt * 1e3:.2f} ms each",
-            "gflops": round(2 * w.nnz * (1 if cfg.op == "spmv" else cfg.dense_cols[0]) / dt / 1e9, 2)}, dt, steps
+    dt = (time.perf_counter() - t) / (steps_run * per_step)
+    return {"value": round(nbytes / dt / 1e9, 2), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{desc}; {steps_run} steps of {per_step} passes, {dt * 1e3:.2f} ms per pass, after 3 s of warm-up",
+            "gflops": round(2 * w.nnz * (1 if cfg.op == "spmv" else cfg.dense_cols[0]) / dt / 1e9, 2)}, dt, steps_run, per_step
+
+
+def workload_config(name, scale, world, rows, total_nnz, alpha, beta, algorithmic_bytes, flushed):
+    """The `config` object of a bench line: the same for the GPU arm and the reference arm of one workload."""
+    return {"workload": workload_label(name) + ("" if scale == 1 else f" / {scale}"), "rows": rows, "nnz": total_nnz,
+            "alpha": alpha, "beta": beta, "index_base": 0,
+            "sharding": "replicas only (N=1)" if world == 1 else
+            f"{world} nnz-balanced row blocks, x replicated, y rows moved to every GPU over NVLink while the product "
+            "runs, GPUs ordered by device-side arrival flags",
+            "l2": "L2 flushed between steps" if flushed else "inputs exceed L2",
+            "algorithmic_bytes": algorithmic_bytes}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    # at least ten untimed passes: the OpenMP team and the caches are cold in a process that has done nothing else
-    base, dt, steps = cpu_baseline(args.workload, steps=args.steps, warmup=max(10, args.warmup))
+    import torch
+
     from mcsparse_b200 import workloads
 
+    base, dt, steps, per_step = cpu_baseline(args.workload, steps=args.steps)
     cfg = workloads.CONFIGS[args.workload]
+    # the full workload's figures, for the config object (the timed sample is described in cpu_baseline.sample)
+    total_nnz = int(workloads.row_lengths(cfg, "cpu").sum().item())
+    vsize = cfg.dtype.itemsize
+    if cfg.op == "spmv":
+        nbytes = workloads.algorithmic_bytes(cfg.rows, cfg.rows, total_nnz, vsize, cfg.beta)
+        local = workloads.algorithmic_bytes(cfg.rows // args.gpus, cfg.rows, total_nnz // args.gpus, vsize, cfg.beta)
+        config = workload_config(args.workload, 1, args.gpus, cfg.rows, total_nnz, cfg.alpha, cfg.beta, nbytes,
+                                 local < 4 * L2_BYTES)
+    else:
+        config = {"workload": workload_label("C4"), "dense_cols": args.dense_cols}
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f64" if cfg.dtype.itemsize == 8 else "f32",
-        "data": "synthetic",
-        "config": {"workload": workload_label(args.workload), "note": "OpenMP C CSR kernel of oracle/ on host cores; "
-                   "the mcSparse reference has no CPU path and builds only with the MetaX toolchain"},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64" if vsize == 8 else "f32",
+        "data": "synthetic", "config": config,
+        "note": "OpenMP C CSR kernel of oracle/ on the host cores (the mcSparse reference has no CPU path and builds "
+                f"only with the MetaX toolchain); a step is {per_step} passes over the sample, ms_per_step is one pass",
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -383,6 +446,34 @@ def workload_label(name):
         "C4": "C4 CSR SpMM fp32 Poisson(32) rows n=1048576, B row-major 64/128 columns",
         "C5": "C5 CSR SpMV fp64 27-point stencil 256^3",
     }[name]
+
+
+def parity_sample(torch, job, blocks=6, block_rows=1024):
+    """Checks row blocks spread over the whole (assembled) y of this rank against the CPU oracle: the rows of
+    every shard are sampled, so at N > 1 rows that arrived from the peers are checked as well.
+    Returns (rows checked, all within tolerance, largest error in units of tolerance * d)."""
+    import numpy as np
+
+    from mcsparse_b200 import workloads
+    from oracle import oracle
+
+    cfg = job.cfg
+    x = job.w.x.cpu()
+    tol = 1e-12 if job.vsize == 8 else 1e-5
+    y_all = job.y_full
+    checked, ok, worst = 0, True, 0.0
+    for b in range(blocks):
+        r0 = min(cfg.rows - 1, (cfg.rows * b) // blocks + 17 * b)
+        r1 = min(cfg.rows, r0 + block_rows)
+        w = workloads.generate(cfg, "cpu", row_range=(r0, r1), with_dense=False)
+        y0 = workloads.dense_values(cfg, "cpu", r1 - r0, 51, first=r0) if cfg.beta != 0 else None
+        ref, d = oracle.spmv(w.row_ptr, w.col, w.val, x, cfg.alpha, cfg.beta, y0)
+        got = y_all[r0:r1].cpu().numpy().astype(np.float64)
+        ratio = np.abs(got - ref) / (tol * d + 1e-300)
+        worst = max(worst, float(ratio.max()) if ratio.size else 0.0)
+        ok = ok and bool((ratio <= 1.0).all())
+        checked += r1 - r0
+    return checked, ok, worst
 
 
 def run_gpu(args, rank, world, local_rank):
@@ -440,10 +531,20 @@ def run_gpu(args, rank, world, local_rank):
         push_total, _ = time_steps(torch, lambda: job.sharded.compute(job.cfg.alpha, job.cfg.beta), k, args.warmup,
                                    flush, barrier)
         ag_ms, push_ms = ag_total / k, push_total / k
-    t = torch.tensor([total_ms, statistics.mean(per_compute), ag_ms, push_ms], dtype=torch.float64, device=device)
+    # parity of the result the timed steps left (beta == 0 for the sharded workloads: every step gives the same y;
+    # with beta != 0 one fresh step from y0 is run for the check)
+    if job.cfg.beta != 0:
+        job.y.copy_(job.w.y0)
+        job.step()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    p_rows, p_ok, p_worst = parity_sample(torch, job)
+    t = torch.tensor([total_ms, statistics.mean(per_compute), ag_ms, push_ms, 0.0 if p_ok else 1.0, p_worst],
+                     dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, compute_ms, ag_ms, push_ms = t.tolist()
+    total_ms, compute_ms, ag_ms, push_ms, p_bad, p_worst = t.tolist()
     ms_per_step = total_ms / args.steps
     value = job.bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -503,6 +604,31 @@ def run_gpu(args, rank, world, local_rank):
     e2e_ms, e2e_serial_ms = (v / e2e_steps for v in t.tolist())
     x_up = x_host.numel() + (job.cfg.rows if job.cfg.beta != 0 else 0)  # elements uploaded per step, all ranks
 
+    # the other sharded configuration (the power-law matrix) on the same GPUs: the step with the row push, the
+    # local kernels alone, and the oracle check of the assembled y
+    c3 = None
+    if world > 1 and args.workload == "C5" and args.scale == 1 and not args.headline_only and not args.quick:
+        j3 = SpmvJob("C3", device, rank, world, h)
+        k = max(10, args.steps // 4)
+        _, per3 = time_steps(torch, j3.compute, k, args.warmup, None, barrier)
+        tot3, _ = time_steps(torch, j3.step, k, args.warmup, None, barrier)
+        torch.cuda.synchronize()
+        barrier()
+        rows3, ok3, worst3 = parity_sample(torch, j3)
+        t3 = torch.tensor([tot3 / k, statistics.mean(per3), 0.0 if ok3 else 1.0, worst3], dtype=torch.float64,
+                          device=device)
+        dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+        step3, comp3, bad3, worst3 = t3.tolist()
+        c3 = {"workload": workload_label("C3"), "n_gpus": world, "ms_per_step": round(step3, 5),
+              "kernel_only_ms": round(comp3, 5), "gbs": round(j3.bytes / (step3 * 1e-3) / 1e9, 1),
+              "frac_of_measured_hbm_per_gpu": round(j3.bytes / (step3 * 1e-3) / 1e9 / peak / world, 4),
+              "nvlink_lower_bound_ms": round((world - 1) / world * j3.cfg.rows * j3.vsize / 770e9 * 1e3, 5),
+              "bytes": j3.bytes, "nnz": j3.total_nnz,
+              "parity": {"checked_rows": rows3, "ok": bad3 == 0.0, "worst_error_over_tolerance": round(worst3, 4)}}
+        j3.sharded.close()
+        del j3
+        torch.cuda.empty_cache()
+
     if rank == 0:
         local_gbs = job.local_bytes / (compute_ms * 1e-3) / 1e9
         line = {
@@ -510,29 +636,34 @@ def run_gpu(args, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f64" if job.vsize == 8 else "f32",
             "data": "synthetic",
-            "config": {"workload": workload_label(args.workload) + ("" if args.scale == 1 else f" / {args.scale}"), "rows": job.cfg.rows, "nnz": job.total_nnz,
-                       "alpha": job.cfg.alpha, "beta": job.cfg.beta, "index_base": 0,
-                       "sharding": "replicas only (N=1)" if world == 1 else
-                       f"{world} nnz-balanced row blocks, x replicated, y rows pushed to every GPU by the kernel over "
-                       "NVLink peer stores + one 4-byte NCCL all-reduce per step to order the GPUs",
-                       "l2": "inputs exceed L2" if flush is None else "L2 flushed between steps",
-                       "algorithmic_bytes": job.bytes},
+            "config": workload_config(args.workload, args.scale, world, job.cfg.rows, job.total_nnz, job.cfg.alpha,
+                                      job.cfg.beta, job.bytes, flush is not None),
             "gflops": round(job.flops / (ms_per_step * 1e-3) / 1e9, 1),
             "roofline": {"bound": "hbm", "achieved": round(local_gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(local_gbs / peak, 4),
+                         # DRAM bytes per launch from the ncu capture under profiles/ (N = 1 only: nothing was captured
+                         # on a shard)
                          "traffic": (round(TRAFFIC_RATIO[args.workload] * job.local_bytes)
-                                     if args.workload in TRAFFIC_RATIO and args.scale == 1 else None),
+                                     if args.workload in TRAFFIC_RATIO and args.scale == 1 and world == 1 else None),
+                         "accounting": ("per-rank bytes: the rank's rows of A and y, and the span of x its columns touch"
+                                        + ("; a fraction above 1 would be an accounting error" if local_gbs > peak else "")),
                          "peak_kind": peak_kind,
                          "frac_of_nominal_8tbs": round(local_gbs / 8000.0, 4),
                          "kernel": "spmv_tile_kernel (+ carry fix-up) per rank", "ms": round(compute_ms, 5)},
-            "e2e": {"value": round(job.bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": UNIT,
+            # e2e.value: one product at a time (what a solver whose next x depends on this y gets); the
+            # pipelined figure needs independent products and is reported beside it
+            "e2e": {"value": round(job.bytes / (e2e_serial_ms * 1e-3) / 1e9, 1), "unit": UNIT,
                     "h2d_bytes_per_step": x_up * job.vsize, "d2h_bytes_per_step": job.cfg.rows * job.vsize,
-                    "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
-                    "mode": f"{depth} independent products in flight (HostSpmvPipeline): upload of one overlaps "
-                            "download of the previous; bytes are totals over all ranks",
-                    "serial_ms_per_step": round(e2e_serial_ms, 4),
-                    "serial_value": round(job.bytes / (e2e_serial_ms * 1e-3) / 1e9, 1),
+                    "ms_per_step": round(e2e_serial_ms, 4), "steps": e2e_steps,
+                    "mode": "one product at a time through HostSpmvPipeline (depth 1): x up, product, y down, "
+                            "then the next; bytes are totals over all ranks",
+                    "pipelined_value": round(job.bytes / (e2e_ms * 1e-3) / 1e9, 1),
+                    "pipelined_ms_per_step": round(e2e_ms, 4),
+                    "pipelined_mode": f"{depth} independent products in flight: the upload of one overlaps the "
+                                      "download of the previous (only for products that do not depend on each other)",
                     "equals_device_resident_result_bitwise": pipe_ok},
+            "parity": {"checked_rows": p_rows, "ok": p_bad == 0.0, "worst_error_over_tolerance": round(p_worst, 4),
+                       "against": "CPU oracle on row blocks spread over the whole assembled y, on every rank"},
             "gpu_launches": job.launches_per_step * args.steps,
             "multi_gpu": None if world == 1 else {
                 "kernel_only_ms": round(compute_ms, 5), "push_kernels_ms": round(push_ms, 5),
@@ -542,15 +673,26 @@ def run_gpu(args, rank, world, local_rank):
             "clocks": clocks.summary(),
         }
         if world == 1 and args.scale == 1:
-            base, _, _ = cpu_baseline(args.workload)
+            base = cpu_baseline(args.workload)[0]
             line["cpu_baseline"] = base
         if world == 1 and args.scale == 1 and not args.headline_only:
             extra = {}
             del job
             torch.cuda.empty_cache()
+            # second roofline of the scattered-column matrices: one L2 sector request per nonzero
+            rate = gather_rate(torch, h, device)
+            line["gather_rate"] = {"gathers_per_s": round(rate), "per_sm_per_clock_at_1965_mhz": round(rate / 148 / 1.965e9, 3),
+                                   "probe": "mcsparseB200GatherProbe: 2^26 random fp32 gathers from a 64 MiB table"}
             for name in ("C1", "C2", "C3"):
                 j = SpmvJob(name, device, 0, 1, h)
                 extra[name] = measure_job(torch, j, 100, 5, peak, flush_buf)
+                if name in ("C2", "C3"):  # every nonzero gathers an unrelated element of x
+                    bound_ms = j.total_nnz / rate * 1e3
+                    extra[name].update({"gather_bound_ms": round(bound_ms, 5),
+                                        "frac_of_gather_bound": round(bound_ms / extra[name]["ms_per_step"], 4),
+                                        "hbm_frac_at_gather_bound": round(j.bytes / (bound_ms * 1e-3) / 1e9 / peak, 4)})
+                if name in TRAFFIC_RATIO:
+                    extra[name]["traffic"] = round(TRAFFIC_RATIO[name] * j.bytes)
                 del j
                 torch.cuda.empty_cache()
             # the headline matrix with 64-bit indices, and with complex double values (bytes counted accordingly)
@@ -569,9 +711,14 @@ def run_gpu(args, rank, world, local_rank):
             for n in (64, 128):
                 j = SpmmJob("C4", n, device, h)
                 extra[f"C4_n{n}"] = measure_job(torch, j, 30, 3, peak, flush_buf)
+                extra[f"C4_n{n}"]["work_buffer_bytes"] = j.panel_buffer_bytes
+                if f"C4_n{n}" in TRAFFIC_RATIO:
+                    extra[f"C4_n{n}"]["traffic"] = round(TRAFFIC_RATIO[f"C4_n{n}"] * j.bytes)
                 del j
                 torch.cuda.empty_cache()
             line["configs"] = extra
+        if c3 is not None:
+            line["configs"] = {"C3": c3}
         print(json.dumps(line), flush=True)
     if world > 1:
         job.sharded.close()

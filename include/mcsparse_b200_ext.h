@@ -92,6 +92,19 @@ mcsparseStatus_t mcsparseB200SpMVGetStatus(mcsparseHandle_t handle, mcsparseSpMa
 mcsparseStatus_t mcsparseB200SetDeviceWaitLimit(mcsparseHandle_t handle, int64_t smClocks, int withholdCopies);
 
 /*
+ * Measures the second roofline of CSR SpMV on this GPU: the rate at which the SMs can gather unrelated
+ * elements. `blocks` thread blocks of 256 threads read indices[0 .. count) (device, 16-byte aligned, values
+ * below the table's length) with coalesced loads, gather table[indices[i]] (elements of elemBytes = 4 or 8)
+ * and leave one partial sum per thread in partialSums (blocks * 256 elements). A gather of an element whose
+ * neighbours are not wanted costs one 32-byte sector request to L2, and an SM issues about one such request
+ * per clock, whatever the element size and however the load is written; an SpMV with scattered columns makes
+ * one per nonzero, so nnz / (gathers per second) bounds its time from below beside bytes / HBM bandwidth.
+ * The caller times the launch (bench.py does). Asynchronous on the handle's stream. No reference counterpart.
+ */
+mcsparseStatus_t mcsparseB200GatherProbe(mcsparseHandle_t handle, const int32_t* indices, int64_t count,
+                                         const void* table, int elemBytes, void* partialSums, int blocks);
+
+/*
  * Row-block sharding of one CSR matrix over numShards GPUs, balanced by nonzeros:
  * bounds[g] = first row r with rowOffsets[r] - base >= floor(g * nnz / numShards),
  * bounds[0] = 0, bounds[numShards] = rows. rowOffsets is device memory; bounds is host

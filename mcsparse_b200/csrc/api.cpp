@@ -928,6 +928,16 @@ mcsparseStatus_t mcsparseB200SpMVNoAlloc(mcsparseHandle_t handle, mcsparseOperat
     return pub(from_cuda(e));
 }
 
+mcsparseStatus_t mcsparseB200GatherProbe(mcsparseHandle_t handle, const int32_t* indices, int64_t count, const void* table,
+                                         int elemBytes, void* partialSums, int blocks) {
+    if (handle == nullptr) return pub(BAD_HANDLE);
+    if (indices == nullptr || table == nullptr || partialSums == nullptr) return pub(BAD_POINTER);
+    if (count < 0 || blocks < 1 || (elemBytes != 4 && elemBytes != 8)) return pub(BAD_VALUE);
+    if ((reinterpret_cast<uintptr_t>(indices) & 15) != 0) return pub(BAD_VALUE);
+    DeviceGuard guard(handle->device);
+    return pub(from_cuda(gather_probe(handle->stream, indices, count, table, elemBytes, partialSums, blocks)));
+}
+
 mcsparseStatus_t mcsparseB200SetDeviceWaitLimit(mcsparseHandle_t handle, int64_t smClocks, int withholdCopies) {
     if (handle == nullptr) return pub(BAD_HANDLE);
     if (smClocks < 1) return pub(BAD_VALUE);

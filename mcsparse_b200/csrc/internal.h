@@ -187,6 +187,10 @@ SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile
 template <typename I>
 cudaError_t spmv_locality_probe(cudaStream_t s, int64_t m, int64_t nnz, const I* row_ptr, const I* col, int* device_count,
                                 int* host_count);
+// Launches the gather-rate probe: `blocks` thread blocks of 256 threads gather table[idx[i]] for i < count and
+// leave one partial sum per thread in `out` (blocks * 256 elements of elem_bytes = 4 or 8).
+cudaError_t gather_probe(cudaStream_t s, const int32_t* idx, int64_t count, const void* table, int elem_bytes, void* out,
+                         int blocks);
 inline void* align_up_256(void* p) {
     return reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 255) & ~uintptr_t(255));
 }

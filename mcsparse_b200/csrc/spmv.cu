@@ -30,6 +30,14 @@ constexpr int tile_items(size_t value_size, bool small) {
            : value_size == 8 ? (small ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F64)
                              : MCSPARSE_B200_SPMV_TILE_ITEMS_C64;
 }
+// Thread blocks per SM the tile kernels are compiled for: as many as their shared memory admits, at most 8
+// (256 threads x 8 = all the SM's threads). Without it the push variants, which keep the peer list live, take
+// 40 registers and lose a quarter of the resident blocks.
+constexpr int tile_min_blocks(size_t value_size, size_t index_size, int threads, int ipt) {
+    const size_t smem = size_t(threads) * ipt * (value_size + index_size) + 6144;
+    const size_t fit = (227u * 1024u) / smem;
+    return fit >= 8 ? 8 : (fit < 1 ? 1 : (int)fit);
+}
 template <typename T, typename I>
 struct TileCfg {
     static constexpr int kSmall = tile_items(sizeof(T), true) / kThreads;
@@ -61,6 +69,26 @@ __global__ void locality_probe_kernel(long long m, long long nnz, const I* __res
     atomicAdd(&s_long, longer);
     __syncthreads();
     if (threadIdx.x == 0) count[0] = s_near, count[1] = s_long;
+}
+
+// Gather-rate probe: every thread loads 8 indices (two coalesced 128-bit loads), gathers the 8 table
+// elements they name and adds them up. With indices that are spread over a table larger than L1 this
+// measures how many independent 32-byte sectors per second the SMs can request from L2, which is the
+// bound of an SpMV whose columns are scattered (one x gather per nonzero, one sector each).
+template <typename T>
+__global__ void __launch_bounds__(256) gather_probe_kernel(const int* __restrict__ idx, long long count,
+                                                           const T* __restrict__ table, T* __restrict__ out) {
+    const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    T acc = T(0);
+    for (long long b = t * 4; b + 4 * nthreads + 3 < count; b += nthreads * 8) {
+        const int4 a = __ldcs(reinterpret_cast<const int4*>(idx + b));
+        const int4 c = __ldcs(reinterpret_cast<const int4*>(idx + b + 4 * nthreads));
+        const T v0 = ldg(table + a.x), v1 = ldg(table + a.y), v2 = ldg(table + a.z), v3 = ldg(table + a.w);
+        const T v4 = ldg(table + c.x), v5 = ldg(table + c.y), v6 = ldg(table + c.z), v7 = ldg(table + c.w);
+        acc += ((v0 + v1) + (v2 + v3)) + ((v4 + v5) + (v6 + v7));
+    }
+    out[t] = acc;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -175,9 +203,8 @@ __device__ __forceinline__ void push_to_peers(const PeerList<T>& peers, long lon
         multicast_store(peers.y[0] + peers.row_offset + row, v);
         return;
     }
-#pragma unroll
-    for (int p = 0; p < PeerList<T>::kMax; ++p)
-        if (p < peers.count) peers.y[p][peers.row_offset + row] = v;
+#pragma unroll 1
+    for (int p = 0; p < peers.count; ++p) peers.y[p][peers.row_offset + row] = v;  // a loop: this path is rare
 }
 
 __device__ __forceinline__ void store_vec16(float* dst, const float* v) {
@@ -255,20 +282,18 @@ __device__ __forceinline__ void push_tile_rows_bulk(const PeerList<T>& peers, co
     if (tid == 0 && nvec > 0) {
         const uint32_t src = smem_addr(vals + head);
         const uint32_t bytes = (uint32_t)nvec * 16u;
-#pragma unroll
-        for (int p = 0; p < PeerList<T>::kMax; ++p)
-            if (p < peers.count)
-                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
-                                 peers.y[p] + peers.row_offset + row0 + head),
-                             "r"(src), "r"(bytes)
-                             : "memory");
+        for (int p = 0; p < peers.count; ++p)
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                             peers.y[p] + peers.row_offset + row0 + head),
+                         "r"(src), "r"(bytes)
+                         : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
-    // the few rows before the first and after the last aligned group: ordinary stores by the last threads
-    const int u = THREADS - 1 - tid;
-#pragma unroll
-    for (int p = 0; p < PeerList<T>::kMax; ++p) {
-        if (p < peers.count) {
+    // the few rows before the first and after the last aligned group: ordinary stores by the last warp
+    // (the other warps have nothing left to do here: the peer loop is kept out of their instruction stream)
+    if (tid >= THREADS - 32 && (head > 0 || tail0 < n)) {
+        const int u = THREADS - 1 - tid;
+        for (int p = 0; p < peers.count; ++p) {
             T* const dst = peers.y[p] + peers.row_offset + row0;
             if (u < head) dst[u] = vals[u];
             if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
@@ -405,7 +430,7 @@ __device__ __forceinline__ bool stage_finish(int tid, bool copies, unsigned long
 // No atomics on the data path: every addition has a fixed place, so results are reproducible.
 // ---------------------------------------------------------------------------------------
 template <typename T, int THREADS, int IPT, bool PUSH, typename I>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
     spmv_tile_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
@@ -423,7 +448,7 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_warp_maxlen[NWARPS];
     __shared__ int s_failed;
-    constexpr int PUSHCAP = PUSH ? 512 : 1;  // finished rows of a short-row tile staged for the push
+    constexpr int PUSHCAP = PUSH ? 128 : 1;  // finished rows of a short-row tile staged for the push
     __shared__ __align__(16) T s_push[PUSHCAP + 4];
 
     const int tid = threadIdx.x;
@@ -642,7 +667,7 @@ __global__ void __launch_bounds__(THREADS)
 // rows of one nonzero and rows of a hundred thousand go through the same code.
 // ---------------------------------------------------------------------------------------
 template <typename T, int THREADS, int IPT, bool PUSH, typename I>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
     spmv_walk_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
@@ -933,6 +958,17 @@ cudaError_t spmv_locality_probe(cudaStream_t s, int64_t m, int64_t nnz, const I*
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_count, device_count, 2 * sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return e;
+}
+
+cudaError_t gather_probe(cudaStream_t s, const int32_t* idx, int64_t count, const void* table, int elem_bytes, void* out,
+                         int blocks) {
+    if (elem_bytes == 8)
+        gather_probe_kernel<double><<<blocks, 256, 0, s>>>(idx, count, static_cast<const double*>(table),
+                                                           static_cast<double*>(out));
+    else
+        gather_probe_kernel<float><<<blocks, 256, 0, s>>>(idx, count, static_cast<const float*>(table),
+                                                          static_cast<float*>(out));
+    return cudaGetLastError();
 }
 
 template <typename I>

@@ -288,6 +288,15 @@ int baseline_num_threads(void) {
 #endif
 }
 
+/* Size of the OpenMP team of the baseline kernels (a launcher may have exported OMP_NUM_THREADS=1). */
+void baseline_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline int baseline_threads_in_region(void) {
 #ifdef _OPENMP
     return omp_get_num_threads();

@@ -166,6 +166,14 @@ def num_threads():
     return lib().baseline_num_threads()
 
 
+def use_host_cores():
+    """Sizes the OpenMP team of the baseline kernels to the cores this process may run on, whatever
+    OMP_NUM_THREADS says (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers)."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().baseline_set_threads(cores)
+    return num_threads()
+
+
 def baseline_spmv(row_ptr, col, val, x, alpha, beta, y, base=0):
     """Native-precision OpenMP y = alpha A x + beta y, in place on the numpy array y."""
     ct = C.c_float if val.dtype == np.float32 else C.c_double
