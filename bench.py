@@ -42,7 +42,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 def PUSH_CHUNKS_DEFAULT(world):
     """Chunks of the pipelined row push the library chooses for `world` GPUs (0: the tile kernel pushes)."""
-    return 4 if 2 <= world <= 4 else 0
+    return 4 if world == 2 else 0
 METRIC = "csr_spmv_spmm_algorithmic_hbm_throughput"
 UNIT = "GB/s"
 
@@ -183,7 +183,8 @@ class SpmvJob:
         # tile kernel + carry fix-up; sharded: per chunk a tile launch and a fix-up (pipelined push), or one of each
         # (rows pushed by the tile kernel), and the kernel that orders the GPUs
         chunks = int(os.environ.get("MCSPARSE_B200_PUSH_CHUNKS", PUSH_CHUNKS_DEFAULT(world)))
-        self.launches_per_step = 2 if world == 1 else (2 * chunks if chunks else 2) + 1
+        # (one launch when the push crew of the tile launch also adds the carries)
+        self.launches_per_step = 2 if world == 1 else (2 * chunks if chunks else 1) + 1
 
     def compute(self):
         """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""

@@ -175,6 +175,7 @@ struct PushArgs {
     int64_t row_offset = 0;
     bool multicast = false;  // y[0] is a multicast address reaching every GPU
     bool bulk = false;       // rows leave through bulk copies from shared memory
+    bool crew = false;       // rows are moved by the push crew of the tile launch
 };
 
 size_t index_size(const mcsparseSpMatDescr* A) { return A->rowIdxType == MCSPARSE_INDEX_64I ? 8 : 4; }
@@ -264,6 +265,10 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
     peers.row_offset = push.row_offset;
     peers.multicast = push.multicast;
     peers.bulk = push.bulk;
+    // the crew copies whole 16-byte groups from the local y: it must sit at the peers' alignment
+    peers.crew = push.crew && push.count > 0 &&
+                 ((reinterpret_cast<uintptr_t>(Y->values) ^
+                   (reinterpret_cast<uintptr_t>(push.y[0]) + size_t(push.row_offset) * sizeof(T))) & 15) == 0;
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
     cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
@@ -624,17 +629,15 @@ St csrmm_entry(mcsparseHandle_t h, mcsparseOperation_t transA, mcsparseOperation
                              scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta)));
 }
 
-// How mcsparseB200SpMVPush moves finished rows to the peers. Measured on B200 / NVSwitch with the
-// 27-point stencil: with up to three peers, computing the tiles in 4 launches and copying each
-// chunk's rows with the copy engines (one stream per destination) while the next chunk computes is
-// fastest (two GPUs 0.573 against 0.656 ms, four GPUs 0.370 against 0.405 ms); with seven peers the
-// variant whose tile kernel stores every finished row to all peers itself (0 chunks) was the faster
-// one when the copies still shared one stream, and stays the default there until the
-// per-destination streams are measured at that size.
-// MCSPARSE_B200_PUSH_CHUNKS overrides the choice (0 ... 8), read on every call.
+// How mcsparseB200SpMVPush moves finished rows to the peers. Measured on B200 / NVSwitch (27-point stencil,
+// ms per step at 2 / 4 / 8 GPUs): with one peer, computing the tiles in 4 launches and copying each chunk's rows
+// with the copy engines while the next chunk computes is fastest (0.577 against 0.625); with more peers the copy
+// engines fall behind (0.418 at 4 GPUs, 0.54 at 8) and the single launch whose push crew moves the rows with bulk
+// copies wins (0.339 at 4 GPUs, 0.239 at 8). MCSPARSE_B200_PUSH_CHUNKS overrides the choice (0 ... 8: 0 is the
+// single launch), read on every call.
 int push_chunks_setting(int num_peers) {
     const char* e = std::getenv("MCSPARSE_B200_PUSH_CHUNKS");
-    const int c = e ? std::atoi(e) : (num_peers <= 3 ? 4 : 0);
+    const int c = e ? std::atoi(e) : (num_peers <= 1 ? 4 : 0);
     return c < 0 ? 0 : (c > kMaxPushChunks ? kMaxPushChunks : c);
 }
 
@@ -1209,14 +1212,18 @@ mcsparseStatus_t mcsparseB200SpMVPush(mcsparseHandle_t handle, mcsparseOperation
     push.count = numPeers;
     push.y = peerY;
     push.row_offset = rowOffset;
-    // The in-kernel push hands the finished rows to the TMA unit (bulk copies from shared memory) when every
-    // destination has the same alignment modulo 16 bytes; MCSPARSE_B200_PUSH_STORE=lsu keeps ordinary stores.
+    // How finished rows leave (MCSPARSE_B200_PUSH_STORE): "crew" (default): thread blocks of the tile launch that
+    // compute nothing copy them with bulk copies (TMA) while the tiles compute; "bulk": every tile block hands its
+    // rows to the TMA unit itself; "lsu": every tile block stores them with ordinary stores. The first two need all
+    // destinations at the same alignment modulo 16 bytes and fall back to "lsu" otherwise.
     {
         const char* e = std::getenv("MCSPARSE_B200_PUSH_STORE");
-        bool bulk = !(e != nullptr && e[0] == 'l') && numPeers > 0;
+        bool aligned = numPeers > 0;
         for (int p = 1; p < numPeers; ++p)
-            bulk = bulk && ((reinterpret_cast<uintptr_t>(peerY[p]) ^ reinterpret_cast<uintptr_t>(peerY[0])) & 15) == 0;
-        push.bulk = bulk;
+            aligned = aligned && ((reinterpret_cast<uintptr_t>(peerY[p]) ^ reinterpret_cast<uintptr_t>(peerY[0])) & 15) == 0;
+        const char mode = e != nullptr ? e[0] : 'c';
+        push.bulk = aligned && mode != 'l';
+        push.crew = aligned && mode == 'c';
     }
     const int chunks = push_chunks_setting(numPeers);
     if (chunks == 0 || numPeers == 0)

@@ -147,6 +147,7 @@ struct PeerList {
     int count = 0;
     bool multicast = false;
     bool bulk = false;  // finished rows leave through bulk copies from shared memory (all y[p] congruent modulo 16)
+    bool crew = false;  // finished rows are moved by the launch's push crew (all y[p] and the local y congruent modulo 16)
     long long row_offset = 0;
     T* y[kMax] = {};
 };
@@ -166,14 +167,26 @@ struct WaitCfg {
     int* fault_word = nullptr;
 };
 
+// The push crew of a sharded tile launch: the first `pushers` thread blocks compute no tile; they wait for
+// chunks of `tiles_per_chunk` consecutive tiles to finish (done[c] counts them; zeroed before the launch) and
+// copy the rows that ended in a finished chunk from the local y to every peer with bulk copies.
+struct CrewCfg {
+    int pushers = 0;
+    int tiles_per_chunk = 64;
+    int num_chunks = 0;
+    int* done = nullptr;
+};
+constexpr int kCrewTilesPerChunk = 64;
+
 // Layout of the SpMV work buffer (all offsets from the 256-byte aligned start):
-//   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status
+//   int32 pairs tile_starts[num_tiles + 1] | int32 carry_row[num_tiles] | T carry_val[num_tiles] | int32 status |
+//   int32 chunk_done[ceil(num_tiles / kCrewTilesPerChunk)]
 // status stays 0 unless a kernel gave up a bounded wait (zeroed by the analysis kernel).
 struct SpmvWorkspace {
     int items_per_tile = 0;
     bool walk = false;  // scattered columns: every tile takes the thread-per-merge-segment walk kernel
     int64_t num_tiles = 0;
-    size_t off_carry_row = 0, off_carry_val = 0, off_status = 0, bytes = 0;
+    size_t off_carry_row = 0, off_carry_val = 0, off_status = 0, off_done = 0, bytes = 0;
 };
 // Layout for the chosen tile size; `bytes` is always the size the small tiles would need, so that
 // mcsparseSpMV_bufferSize does not depend on the choice.

@@ -195,6 +195,18 @@ __device__ __forceinline__ void multicast_store_vec16(double* dst, const double*
                  : "memory");
 }
 
+// peers.y[p] for a p that is not a compile-time constant. Indexing the array directly would make the compiler
+// copy the whole kernel parameter to local memory at the start of every thread (80 bytes x every thread of every
+// tile block: measured a quarter of the kernel's time); a chain of selects keeps it in the constant bank.
+template <typename T>
+__device__ __forceinline__ T* peer_ptr(const PeerList<T>& peers, int p) {
+    T* q = peers.y[0];
+#pragma unroll
+    for (int i = 1; i < PeerList<T>::kMax; ++i)
+        if (p == i) q = peers.y[i];
+    return q;
+}
+
 // (Write-through and streaming cache operators on the peer stores were measured and change
 // nothing: 0.645 ms per step at two GPUs with any of them.)
 template <typename T>
@@ -204,7 +216,7 @@ __device__ __forceinline__ void push_to_peers(const PeerList<T>& peers, long lon
         return;
     }
 #pragma unroll 1
-    for (int p = 0; p < peers.count; ++p) peers.y[p][peers.row_offset + row] = v;  // a loop: this path is rare
+    for (int p = 0; p < peers.count; ++p) peer_ptr(peers, p)[peers.row_offset + row] = v;  // a loop: this path is rare
 }
 
 __device__ __forceinline__ void store_vec16(float* dst, const float* v) {
@@ -284,7 +296,7 @@ __device__ __forceinline__ void push_tile_rows_bulk(const PeerList<T>& peers, co
         const uint32_t bytes = (uint32_t)nvec * 16u;
         for (int p = 0; p < peers.count; ++p)
             asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
-                             peers.y[p] + peers.row_offset + row0 + head),
+                             peer_ptr(peers, p) + peers.row_offset + row0 + head),
                          "r"(src), "r"(bytes)
                          : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -294,7 +306,7 @@ __device__ __forceinline__ void push_tile_rows_bulk(const PeerList<T>& peers, co
     if (tid >= THREADS - 32 && (head > 0 || tail0 < n)) {
         const int u = THREADS - 1 - tid;
         for (int p = 0; p < peers.count; ++p) {
-            T* const dst = peers.y[p] + peers.row_offset + row0;
+            T* const dst = peer_ptr(peers, p) + peers.row_offset + row0;
             if (u < head) dst[u] = vals[u];
             if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = vals[tail0 + (u - VW)];
         }
@@ -404,6 +416,176 @@ __device__ __forceinline__ bool stage_finish(int tid, bool copies, unsigned long
 }
 
 // ---------------------------------------------------------------------------------------
+// Push crew: the thread blocks of a sharded tile launch that move finished rows to the peers.
+//
+// The tile blocks of such a launch compute exactly as on one GPU and only count themselves off
+// (done[chunk] += 1 after their rows are written). A crew block takes the chunks c = blockIdx.x,
+// blockIdx.x + pushers, ...: it waits (bounded) until all tiles of the chunk have counted off, then
+// copies the rows that ended in the chunk from the local y to the same global rows of every peer's y:
+// one thread runs a two-stage pipeline of bulk copies (TMA) global -> shared -> the peers' global
+// memory, a second warp stores the few rows before and after the 16-byte aligned middle. The copies use
+// neither registers nor the load/store unit, and a crew block holds one of the SM's block slots, not
+// the SM: the NVLink transfer runs beside the computation instead of stretching every tile block.
+// Rows that take a carry from an earlier tile are final only after the fix-up kernel, which pushes them again.
+// `vals` is shared memory of at least 2 * piece_elems elements, 16-byte aligned; the local y and all
+// peers' y share their alignment modulo 16 bytes (checked on the host).
+// ---------------------------------------------------------------------------------------
+constexpr int kCrewStages = 4;  // pieces of a crew block in flight
+// Polls with relaxed loads that bypass L1. An acquire at GPU scope would invalidate the SM's L1 on every poll,
+// and with it the x lines that the tile blocks sharing the SM live on; nothing the crew reads afterwards can be
+// stale in L1 instead: the rows are fetched by bulk copies and by ld.global.cg, both served by L2, where the
+// tile blocks' stores were before their release of the counter.
+__device__ __forceinline__ bool chunk_wait_bounded(const int* counter, int want, long long limit) {
+    const long long t0 = clock64();
+    for (;;) {
+        int seen;
+        asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+        if (seen >= want) return true;
+        if (clock64() - t0 > limit) return false;
+        __nanosleep(500);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void crew_report_failure(int* status, const WaitCfg& wait) {
+    atomicOr(status, 1);
+    if (wait.fault_word != nullptr) {
+        *reinterpret_cast<volatile int*>(wait.fault_word) = 1;
+        __threadfence_system();
+    }
+}
+
+template <typename T>
+__device__ void push_crew(const CrewCfg& crew, const PeerList<T>& peers, const int2* __restrict__ tile_starts,
+                          long long num_tiles, T* __restrict__ y, const int* __restrict__ carry_row,
+                          const T* __restrict__ carry_val, T alpha, T* vals, int piece_elems,
+                          unsigned long long* bars, int* __restrict__ status, const WaitCfg& wait) {
+    constexpr int VW = 16 / (int)sizeof(T);
+    const int tid = threadIdx.x;
+    if (tid >= 32) return;  // one warp: all lanes finish the chunk's rows, lane 0 runs the bulk copies
+    const long long limit = wait.limit_cycles * 50;  // a chunk is ready when the tiles ahead of it have run
+    if (tid == 0)
+        for (int st = 0; st < kCrewStages; ++st) mbar_init(bars + st, 1);
+    constexpr int NS = kCrewStages;
+    uint32_t parity = 0u;  // bit s: phase of stage s's barrier
+    bool dead = false;     // lane 0: a bulk load never arrived; the block stops at the next chunk
+    for (int c = blockIdx.x; c < crew.num_chunks; c += crew.pushers) {
+        const long long t0 = (long long)c * crew.tiles_per_chunk;
+        const long long t1 = min(t0 + crew.tiles_per_chunk, num_tiles);
+        // this chunk's tiles, and the chunk before (its last tiles hold the carries of this chunk's first rows)
+        int give_up = 0;
+        if (tid == 0) {
+            give_up = dead || !chunk_wait_bounded(crew.done + c, (int)(t1 - t0), limit) ||
+                      (c > 0 && !chunk_wait_bounded(crew.done + c - 1, crew.tiles_per_chunk, limit));
+            if (give_up && !dead) crew_report_failure<T>(status, wait);  // never finished: reported, not waited for
+        }
+        if (__shfl_sync(0xffffffffu, give_up, 0)) return;  // nothing of this block is in flight here
+        // Carries: a tile's first row, if it ends in the tile, also takes what earlier tiles left for it, summed in
+        // tile order exactly as spmv_carry_fixup_range_kernel does (same bits). Everything is read through L2
+        // (ld.global.cg): L1 may hold lines of these arrays from before their tiles had written them.
+        long long oldest = c > 0 ? t0 - crew.tiles_per_chunk : 0;  // first tile known to have finished
+        for (long long tt = t0 + tid; tt < t1; tt += 32) {
+            if (tt == 0) continue;
+            const int r = tile_starts[tt].x;
+            if (tile_starts[tt + 1].x <= r) continue;  // no row ends in this tile
+            long long u = tt - 1;                      // carry_row[tt - 1] == r by construction
+            bool ok = true;
+            while (u > 0) {
+                if (u - 1 < oldest) {  // the run reaches into a still older chunk: it must have finished too
+                    const long long q = (u - 1) / crew.tiles_per_chunk;
+                    if (!chunk_wait_bounded(crew.done + q, crew.tiles_per_chunk, limit)) {
+                        ok = false;
+                        break;
+                    }
+                    oldest = q * crew.tiles_per_chunk;
+                }
+                if (__ldcg(carry_row + u - 1) != r) break;
+                --u;
+            }
+            if (!ok) {
+                crew_report_failure<T>(status, wait);
+                continue;
+            }
+            T sum = __ldcg(carry_val + u);
+            for (++u; u < tt; ++u) sum += __ldcg(carry_val + u);
+            y[r] = mad(alpha, sum, __ldcg(y + r));
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");  // this lane's stores, and the tiles', before the bulk loads
+        __syncwarp();
+        const long long r0 = tile_starts[t0].x, r1 = tile_starts[t1].x;  // rows that ended in the chunk
+        if (r1 <= r0) continue;
+        const T* const src = y + r0;
+        const int n = (int)(r1 - r0);
+        const int mis = (int)((reinterpret_cast<uintptr_t>(src) / sizeof(T)) & (VW - 1));
+        const int head = min(n, (VW - mis) & (VW - 1));
+        const int nvec = (n - head) / VW;
+        const int tail0 = head + nvec * VW;
+        if (tid >= 1 && tid <= 2 * VW) {  // edges: at most VW - 1 rows at either end, by lanes 1 ... 2 VW
+            const int u = tid - 1;
+            for (int p = 0; p < peers.count; ++p) {
+                T* const dst = peer_ptr(peers, p) + peers.row_offset + r0;
+                if (u < head) dst[u] = __ldcg(src + u);
+                if (u >= VW && u - VW < n - tail0) dst[tail0 + (u - VW)] = __ldcg(src + tail0 + (u - VW));
+            }
+        }
+        if (tid != 0 || nvec == 0) continue;
+        // lane 0: pieces of the aligned middle through NS stages: up to NS - 1 loads in flight while one piece leaves
+        asm volatile("fence.proxy.async;" ::: "memory");  // the tiles' ordinary stores, before the bulk loads
+        const unsigned long long policy = l2_evict_first_policy();
+        const int total = nvec * VW;
+        const int pieces = (total + piece_elems - 1) / piece_elems;
+        auto load = [&](int k) {
+            const int st = k % NS, e0 = k * piece_elems, cnt = min(piece_elems, total - e0);
+            mbar_expect_tx(bars + st, (uint32_t)cnt * (uint32_t)sizeof(T));
+            bulk_copy_g2s(vals + st * piece_elems, src + head + e0, (uint32_t)cnt * (uint32_t)sizeof(T), bars + st, policy);
+        };
+        for (int k = 0; k < min(pieces, NS - 1); ++k) load(k);
+        bool failed = false;
+        for (int k = 0; k < pieces; ++k) {
+            const int st = k % NS;
+            const uint32_t ph = (parity >> st) & 1u;
+            if (!mbar_wait_bounded(bars + st, ph, wait.limit_cycles) &&
+                !mbar_wait_bounded(bars + st, ph, wait.limit_cycles * 256)) {
+                failed = true;
+                break;
+            }
+            parity ^= 1u << st;
+            const int e0 = k * piece_elems, cnt = min(piece_elems, total - e0);
+            const uint32_t sm = smem_addr(vals + st * piece_elems);
+            for (int p = 0; p < peers.count; ++p)
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                                 peer_ptr(peers, p) + peers.row_offset + r0 + head + e0),
+                             "r"(sm), "r"((uint32_t)cnt * (uint32_t)sizeof(T))
+                             : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            if (k + NS - 1 < pieces) {
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // piece k - 1 has left its stage
+                load(k + NS - 1);
+            }
+        }
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (failed) {  // a bulk load that never arrived
+            crew_report_failure<T>(status, wait);
+            dead = true;
+        }
+        // (lanes 1 ... 31 wait for lane 0 at the shuffle of the next chunk, and leave with it)
+    }
+}
+
+// A tile block of a launch with a push crew counts itself off once its rows are in global memory.
+template <bool CREW>
+__device__ __forceinline__ void tile_count_off(const CrewCfg& crew, int t, int tid) {
+    if constexpr (CREW) {
+        if (crew.tiles_per_chunk == 0) return;
+        __syncthreads();  // every thread's stores to y are issued
+        // A release without the acquire half: a full fence here would invalidate the SM's L1 at the end of every
+        // tile and take the x lines of the other resident tiles with it.
+        if (tid == 0)
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(crew.done + t / crew.tiles_per_chunk) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // K1: tiled SpMV. Block t owns merge items [t * TILE, (t + 1) * TILE): `nrows` row ends and
 // `nnz_tile` nonzeros (nrows + nnz_tile = TILE except in the last tile).
 //
@@ -429,13 +611,13 @@ __device__ __forceinline__ bool stage_finish(int tid, bool copies, unsigned long
 // before HBM does, so the kernel is organised to spend few L1 wavefronts per nonzero.
 // No atomics on the data path: every addition has a fixed place, so results are reproducible.
 // ---------------------------------------------------------------------------------------
-template <typename T, int THREADS, int IPT, bool PUSH, typename I>
-__global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
+template <typename T, int THREADS, int IPT, bool PUSH, typename I, bool CREW = false>
+__global__ void __launch_bounds__(THREADS, (PUSH || CREW) ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
     spmv_tile_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
                      T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset,
-                     WaitCfg wait) {
+                     WaitCfg wait, CrewCfg crew) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
     constexpr int WALK = IPT + 1;  // merge items per thread in the long-row walk: odd, so that the
@@ -444,6 +626,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
     __shared__ __align__(128) T s_val[TILE + 16];   // values (then products); long-row path: row sums behind them
     __shared__ __align__(128) I s_col[TILE + 16];  // column indices, then the tile's row ends (int) behind them
     __shared__ __align__(8) unsigned long long s_mbar;
+    __shared__ __align__(8) unsigned long long s_mbar_crew[CREW ? kCrewStages : 1];
     __shared__ int s_warp_row[NWARPS];  // long-row path: last carry of each warp
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_warp_maxlen[NWARPS];
@@ -452,7 +635,14 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
     __shared__ __align__(16) T s_push[PUSHCAP + 4];
 
     const int tid = threadIdx.x;
-    const int t = blockIdx.x + tile_offset;  // a launch may cover a sub-range of the tiles
+    if constexpr (CREW) {
+        if ((int)blockIdx.x < crew.pushers) {  // this block belongs to the push crew: it computes no tile
+            push_crew<T>(crew, peers, tile_starts, (long long)gridDim.x - crew.pushers, y, carry_row, carry_val,
+                         alpha_arg.get(), s_val, (TILE / kCrewStages) & ~3, &s_mbar_crew[0], status, wait);
+            return;
+        }
+    }
+    const int t = (int)blockIdx.x - (CREW ? crew.pushers : 0) + tile_offset;  // a launch may cover a sub-range of the tiles
     const int2 s0 = tile_starts[t];
     const int2 s1 = tile_starts[t + 1];
     const int row_s = s0.x, nz_s = s0.y;
@@ -482,6 +672,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
     if ((tid & 31) == 0) s_warp_maxlen[tid >> 5] = maxlen;
     if (!stage_finish(tid, ts.copies, &s_mbar, &s_failed, status, wait)) {
         if (tid == 0) carry_row[t] = m;  // a tile that was given up leaves no carry for the fix-up
+        tile_count_off<CREW>(crew, t, tid);  // (the crew must not wait for it; the failure is already reported)
         return;
     }
 
@@ -548,6 +739,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
                 }
             }
         }
+        tile_count_off<CREW>(crew, t, tid);
         return;
     }
 
@@ -647,6 +839,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
         carry_row[t] = row_s + nrows;
         carry_val[t] = s_y[nrows];
     }
+    tile_count_off<CREW>(crew, t, tid);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -666,13 +859,13 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
 // Per nonzero that is two conflict-free shared loads, one gather and one multiply-add; empty rows,
 // rows of one nonzero and rows of a hundred thousand go through the same code.
 // ---------------------------------------------------------------------------------------
-template <typename T, int THREADS, int IPT, bool PUSH, typename I>
-__global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
+template <typename T, int THREADS, int IPT, bool PUSH, typename I, bool CREW = false>
+__global__ void __launch_bounds__(THREADS, (PUSH || CREW) ? tile_min_blocks(sizeof(T), sizeof(I), THREADS, IPT) : 0)
     spmv_walk_kernel(int m, int nnz, int base, const I* __restrict__ row_ptr, const I* __restrict__ col,
                      const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, ScalarArg<T> alpha_arg,
                      ScalarArg<T> beta_arg, const int2* __restrict__ tile_starts, int* __restrict__ carry_row,
                      T* __restrict__ carry_val, int* __restrict__ status, PeerList<T> peers, int tile_offset,
-                     WaitCfg wait) {
+                     WaitCfg wait, CrewCfg crew) {
     constexpr int TILE = THREADS * IPT;
     constexpr int NWARPS = THREADS / 32;
     constexpr int WALK = IPT + 1;
@@ -681,13 +874,21 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
     __shared__ __align__(128) T s_val[TILE + 16];  // values; the row sums behind them
     __shared__ __align__(128) I s_col[TILE + 16];  // column indices, then the tile's row ends (int) behind them
     __shared__ __align__(8) unsigned long long s_mbar;
+    __shared__ __align__(8) unsigned long long s_mbar_crew[CREW ? kCrewStages : 1];
     __shared__ int s_k0[THREADS];  // first nonzero of every thread's segment
     __shared__ int s_warp_row[NWARPS];
     __shared__ T s_warp_sum[NWARPS];
     __shared__ int s_failed;
 
     const int tid = threadIdx.x;
-    const int t = blockIdx.x + tile_offset;
+    if constexpr (CREW) {
+        if ((int)blockIdx.x < crew.pushers) {  // this block belongs to the push crew: it computes no tile
+            push_crew<T>(crew, peers, tile_starts, (long long)gridDim.x - crew.pushers, y, carry_row, carry_val,
+                         alpha_arg.get(), s_val, (TILE / kCrewStages) & ~3, &s_mbar_crew[0], status, wait);
+            return;
+        }
+    }
+    const int t = (int)blockIdx.x - (CREW ? crew.pushers : 0) + tile_offset;
     const int2 s0 = tile_starts[t];
     const int2 s1 = tile_starts[t + 1];
     const int row_s = s0.x, nz_s = s0.y;
@@ -712,6 +913,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
     }
     if (!stage_finish(tid, ts.copies, &s_mbar, &s_failed, status, wait)) {
         if (tid == 0) carry_row[t] = m;  // a tile that was given up leaves no carry for the fix-up
+        tile_count_off<CREW>(crew, t, tid);  // (the crew must not wait for it; the failure is already reported)
         return;
     }
 
@@ -818,6 +1020,7 @@ __global__ void __launch_bounds__(THREADS, PUSH ? tile_min_blocks(sizeof(T), siz
         carry_row[t] = row_s + nrows;
         carry_val[t] = s_y[nrows];
     }
+    tile_count_off<CREW>(crew, t, tid);
 }
 
 // Copies local rows [r0, r1) of y to the same global rows of every peer's y with 128-bit stores
@@ -831,7 +1034,7 @@ __global__ void __launch_bounds__(512) push_rows_kernel(PeerList<T> peers, const
     const int p = blockIdx.y;  // one grid row of CTAs per destination: all peers are written concurrently
     const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     const long long nthreads = (long long)gridDim.x * blockDim.x;
-    T* const dst = peers.y[p] + peers.row_offset;
+    T* const dst = peer_ptr(peers, p) + peers.row_offset;
     const long long mis = (long long)((reinterpret_cast<uintptr_t>(dst + r0) / sizeof(T)) & (VW - 1));
     long long v0 = r0 + ((VW - mis) & (VW - 1));  // first row whose destination is 16-byte aligned
     if (v0 > r1) v0 = r1;
@@ -937,7 +1140,8 @@ static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int 
     ws.off_carry_row = up(size_t(ws.num_tiles + 1) * 8);
     ws.off_carry_val = ws.off_carry_row + up(size_t(ws.num_tiles) * 4);
     ws.off_status = ws.off_carry_val + up(size_t(ws.num_tiles) * value_size);
-    ws.bytes = ws.off_status + 256;
+    ws.off_done = ws.off_status + 256;
+    ws.bytes = ws.off_done + up(size_t(ws.num_tiles / kCrewTilesPerChunk + 1) * 4);
     return ws;
 }
 
@@ -994,11 +1198,11 @@ static size_t tuning_pad_smem() {
 }
 
 // One launch of the tile kernel over tiles [tile0, tile0 + count), for the tile size of `ws`.
-template <typename T, bool PUSH, typename I>
+template <typename T, bool PUSH, typename I, bool CREW = false>
 static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, int64_t m, int64_t nnz, int base,
                                 const I* row_ptr, const I* col, const T* val, const T* x, T* y,
                                 ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
-                                const PeerList<T>& peers, const WaitCfg& wait) {
+                                const PeerList<T>& peers, const WaitCfg& wait, const CrewCfg& crew = CrewCfg()) {
     char* base_ptr = static_cast<char*>(buf);
     const int2* starts = reinterpret_cast<const int2*>(base_ptr);
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
@@ -1006,12 +1210,12 @@ static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, in
     int* status = reinterpret_cast<int*>(base_ptr + ws.off_status);
     constexpr int kL = TileCfg<T, I>::kLarge, kS = TileCfg<T, I>::kSmall;
     const bool large = ws.items_per_tile == kThreads * kL;
-    const unsigned grid = (unsigned)count;
+    const unsigned grid = (unsigned)(count + (CREW ? crew.pushers : 0));
     const size_t pad = tuning_pad_smem();
-#define MCSP_LAUNCH_TILES(KERNEL, IPT)                                                                              \
-    KERNEL<T, kThreads, IPT, PUSH, I><<<grid, kThreads, pad, s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, \
-                                                                  alpha, beta, starts, carry_row, carry_val,       \
-                                                                  status, peers, (int)tile0, wait)
+#define MCSP_LAUNCH_TILES(KERNEL, IPT)                                                                                   \
+    KERNEL<T, kThreads, IPT, PUSH, I, CREW><<<grid, kThreads, pad, s>>>((int)m, (int)nnz, base, row_ptr, col, val, x, y, \
+                                                                        alpha, beta, starts, carry_row, carry_val,       \
+                                                                        status, peers, (int)tile0, wait, crew)
     if (ws.walk) {
         if (large)
             MCSP_LAUNCH_TILES(spmv_walk_kernel, kL);
@@ -1027,6 +1231,14 @@ static cudaError_t launch_tiles(cudaStream_t s, int64_t tile0, int64_t count, in
     return cudaGetLastError();
 }
 
+// Thread blocks of the push crew of a sharded tile launch: MCSPARSE_B200_PUSH_CREW, default 96 (two thirds of the SMs
+// lend one of their eight block slots; each block keeps up to four pieces of 2-4 KB in flight).
+static int push_crew_blocks() {
+    const char* e = std::getenv("MCSPARSE_B200_PUSH_CREW");
+    const int v = e ? std::atoi(e) : 96;
+    return v < 1 ? 1 : (v > 592 ? 592 : v);
+}
+
 template <typename T, typename I>
 cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I* row_ptr, const I* col, const T* val,
                        const T* x, T* y, ScalarArg<T> alpha, ScalarArg<T> beta, const SpmvWorkspace& ws, void* buf,
@@ -1036,6 +1248,25 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I
     int* carry_row = reinterpret_cast<int*>(base_ptr + ws.off_carry_row);
     T* carry_val = reinterpret_cast<T*>(base_ptr + ws.off_carry_val);
     const unsigned fix_grid = (unsigned)((ws.num_tiles + 255) / 256);
+    if constexpr (std::is_floating_point<T>::value && sizeof(I) == 4) {
+        if (peers.count > 0 && peers.crew && !peers.multicast) {
+            // the tiles compute as on one GPU; a crew of thread blocks in the same launch moves the finished rows
+            CrewCfg crew;
+            crew.pushers = push_crew_blocks();
+            crew.tiles_per_chunk = kCrewTilesPerChunk;
+            crew.num_chunks = (int)((ws.num_tiles + kCrewTilesPerChunk - 1) / kCrewTilesPerChunk);
+            crew.done = reinterpret_cast<int*>(base_ptr + ws.off_done);
+            if (const char* dbg = std::getenv("MCSPARSE_B200_CREW_DEBUG")) {  // tuning: 1 no count-off, no pushing; 2 no pushing
+                crew.num_chunks = 0;
+                if (dbg[0] == '1') crew.tiles_per_chunk = 0;
+            }
+            cudaError_t e = cudaMemsetAsync(crew.done, 0, size_t(crew.num_chunks) * 4, s);
+            if (e != cudaSuccess) return e;
+            // (no fix-up kernel: the crew adds the carries of a chunk's rows before it copies them)
+            return launch_tiles<T, false, I, true>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha, beta,
+                                                   ws, buf, peers, wait, crew);
+        }
+    }
     if constexpr (std::is_floating_point<T>::value) {  // the row push exists for the real types only
         if (peers.count > 0) {
             cudaError_t e = launch_tiles<T, true, I>(s, 0, ws.num_tiles, m, nnz, base, row_ptr, col, val, x, y, alpha,

@@ -48,7 +48,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, name, factor, chunks, out, mode="peer", store="bulk", sync="flags"):
+def _worker(rank, world, port, name, factor, chunks, out, mode="peer", store="crew", sync="flags"):
     """One rank of a two-GPU run. A comparison that fails is recorded in out[rank] and the rank still walks
     through every barrier and the tear-down of its peer mappings (job.close()), so that the other rank is
     never left waiting and no memory stays bound to a multicast object; the parent asserts on `out`."""
@@ -124,7 +124,8 @@ def _assert(cond, what):
 
 # chunks 0: rows stored to the peers by the tile kernel (bulk copies from shared memory, or ordinary stores);
 # 4: pipelined row copies. The GPUs are ordered by device-side arrival flags, or by a 4-byte all-reduce.
-@pytest.mark.parametrize("chunks,store,sync", [(0, "bulk", "flags"), (0, "lsu", "collective"), (4, "bulk", "flags")])
+@pytest.mark.parametrize("chunks,store,sync", [(0, "crew", "flags"), (0, "bulk", "flags"), (0, "lsu", "collective"),
+                                               (4, "crew", "flags")])
 @pytest.mark.parametrize("name,factor", [("C5", 512), ("C3", 256)])
 def test_sharded_spmv_push_and_allgather_two_gpus(name, factor, chunks, store, sync):
     if torch.cuda.device_count() < 2:
@@ -153,7 +154,7 @@ def test_sharded_spmv_multicast_push_two_gpus(name, factor):
         assert dict(out) == {0: 1, 1: 1}
 
 
-@pytest.mark.parametrize("chunks,store", [(0, "bulk"), (0, "lsu"), (1, "bulk"), (4, "bulk"), (8, "bulk")])
+@pytest.mark.parametrize("chunks,store", [(0, "crew"), (0, "bulk"), (0, "lsu"), (1, "crew"), (4, "crew"), (8, "crew")])
 @pytest.mark.parametrize("offset", [5, 8])
 @pytest.mark.parametrize("name,factor", [("C3", 256), ("C5", 512), ("C2", 512)])
 def test_push_to_a_second_local_buffer_matches_plain_spmv(handle, device, name, factor, chunks, store, offset,
