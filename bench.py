@@ -323,6 +323,35 @@ def gather_rate(torch, handle, device, elem_bytes=4, count=1 << 26, table_elems=
     return count / (total / 5 * 1e-3)
 
 
+def reference_kernel_ms(torch, job, steps=3):
+    """Device time of the mcSparse reference's own CSR kernel on this job's operands, where the checker library
+    oracle/_ref/libmcsp_refkernels.so was built from the reference tree (else None): the reference's kernel source,
+    its launch shape, compiled for sm_100a; launched from here, outside the product. SpMM gets the column-major
+    copy of B that the reference kernel requires (its own transpose step is not timed)."""
+    import ctypes as C
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libmcsp_refkernels.so")
+    if not os.path.exists(path):
+        return None
+    ref = C.CDLL(path)
+    w = job.w
+    P = lambda t: C.c_void_p(t.data_ptr())
+    f64 = w.val.dtype == torch.float64
+    ct = C.c_double if f64 else C.c_float
+    if isinstance(job, SpmmJob):
+        n = job.n
+        Bt = w.B[n].t().contiguous()  # column-major B with ldb = rows of B
+        Cm = torch.zeros_like(job.C)
+        fn = lambda: ref.ref_csr_spmm_f32(w.rows, n, C.c_float(1.0), C.c_float(0.0), P(w.row_ptr), P(w.col), P(w.val),
+                                          P(Bt), w.cols, P(Cm), n, 0, 2)
+    else:
+        y = torch.zeros(w.rows, dtype=w.val.dtype, device=w.val.device)
+        call = ref.ref_csr_spmv_f64 if f64 else ref.ref_csr_spmv_f32
+        fn = lambda: call(w.rows, ct(job.cfg.alpha), ct(job.cfg.beta), P(w.row_ptr), P(w.col), P(w.val), P(w.x), P(y), 0)
+    total, per = time_steps(torch, fn, steps, 1)
+    return round(min(per), 5)
+
+
 def measure_job(torch, job, steps, warmup, peak, flush_buf):
     flush = flush_buf if job.bytes < 4 * L2_BYTES else None
     total, per = time_steps(torch, job.compute, steps, warmup, flush)
@@ -678,6 +707,7 @@ def run_gpu(args, rank, world, local_rank):
             line["cpu_baseline"] = base
         if world == 1 and args.scale == 1 and not args.headline_only:
             extra = {}
+            line["reference_kernel_ms"] = reference_kernel_ms(torch, job)  # the reference's kernel on the headline matrix
             del job
             torch.cuda.empty_cache()
             # second roofline of the scattered-column matrices: one L2 sector request per nonzero
@@ -694,6 +724,8 @@ def run_gpu(args, rank, world, local_rank):
                                         "hbm_frac_at_gather_bound": round(j.bytes / (bound_ms * 1e-3) / 1e9 / peak, 4)})
                 if name in TRAFFIC_RATIO:
                     extra[name]["traffic"] = round(TRAFFIC_RATIO[name] * j.bytes)
+                if name in ("C2", "C3"):
+                    extra[name]["reference_kernel_ms"] = reference_kernel_ms(torch, j)
                 del j
                 torch.cuda.empty_cache()
             # the headline matrix with 64-bit indices, and with complex double values (bytes counted accordingly)
@@ -713,6 +745,8 @@ def run_gpu(args, rank, world, local_rank):
                 j = SpmmJob("C4", n, device, h)
                 extra[f"C4_n{n}"] = measure_job(torch, j, 30, 3, peak, flush_buf)
                 extra[f"C4_n{n}"]["work_buffer_bytes"] = j.panel_buffer_bytes
+                if n == 64:
+                    extra[f"C4_n{n}"]["reference_kernel_ms"] = reference_kernel_ms(torch, j, steps=2)
                 if f"C4_n{n}" in TRAFFIC_RATIO:
                     extra[f"C4_n{n}"]["traffic"] = round(TRAFFIC_RATIO[f"C4_n{n}"] * j.bytes)
                 del j

@@ -206,12 +206,19 @@ mcsparseStatus_t mcsparseB200PeerClose(void* mappedPtr);
  *   - Limit: the work area must hold the partition of (rows + nnz) merge items; larger
  *     matrices are refused with MCSPARSE_STATUS_INSUFFICIENT_RESOURCES and a message on stderr
  *     (about 8.5e8 items for fp64 values, 2.1e9 for fp32). Use mcsparseSpMV for those.
- *   - The first call on each device looks up the array's device address; make that first call
- *     outside any stream capture.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture. No call copies anything back to the host or waits for the
+ *     stream: the kernel family and tile size are the ones an earlier mcsparseSpMV / mcsparseSpMV_preprocess
+ *     call chose for this matrix, or the defaults if there was none (mcsparseSpMV's choice involves a small
+ *     probe kernel and a stream synchronisation, which this entry point must not do; results then agree with
+ *     mcsparseSpMV to rounding, not bit for bit).
  *   - All calls on a device share the one array and it keeps what the previous call left.
  *     Every entry a call reads is written earlier in the same call, so nothing needs clearing,
  *     but two calls that overlap on the GPU (different streams, or threads) would overwrite each
  *     other's partition: run them one after the other.
+ *   - A thread block that gives up its bounded wait reports through the handle (the next call returns
+ *     MCSPARSE_STATUS_EXECUTION_FAILED) and through the work area's status word, which
+ *     mcsparseB200SpMVGetStatus reads when its externalBuffer argument is NULL.
  * Arguments and status codes are those of mcsparseSpMV without the buffer.
  */
 #define MCSPARSE_B200_NOALLOC_SCRATCH_BYTES (16u << 20)

@@ -12,6 +12,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <string>
 
 #include "internal.h"
 
@@ -50,15 +52,45 @@ inline St from_cuda(cudaError_t e) {
     return EXEC_FAILED;
 }
 
-// Warnings go to stderr unless SPARSE_LOG_ENABLE=0, the switch the reference's logger reads
-// (mcsparse/src/utils/mcsp_logger.cpp:29-61).
-inline void log_error(const char* msg) {
-    static const bool enabled = [] {
-        const char* v = std::getenv("SPARSE_LOG_ENABLE");
-        return !(v && v[0] == '0');
+// The three switches of the reference's logger (mcsparse/src/utils/mcsp_logger.cpp:29-61):
+//   SPARSE_LOG_ENABLE=0   nothing is logged
+//   SPARSE_LOG_LEVEL=n    messages above level n are dropped (0 fatal, 1 error, 2 warning, 3 info, 4 debug; default 3)
+//   SPARSE_LOG_OUTPUT     "stdout", "file" (mcsparse.txt in the working directory, the reference's fixed name) or
+//                         "syslog" (the reference formats nothing for it either); unset: stderr here, where the
+//                         reference defaults to stdout, so that a caller's own standard output stays clean.
+inline void log_message(int level, const char* msg) {
+    struct Cfg {
+        bool enabled = true;
+        int level = 3;
+        int output = 0;  // 0 stderr, 1 stdout, 2 file, 3 syslog
+        std::FILE* file = nullptr;
+    };
+    static Cfg cfg = [] {
+        Cfg c;
+        if (const char* v = std::getenv("SPARSE_LOG_ENABLE")) c.enabled = std::strtol(v, nullptr, 10) != 0;
+        if (const char* v = std::getenv("SPARSE_LOG_LEVEL")) {
+            c.level = (int)std::strtol(v, nullptr, 10);
+            if (c.level > 4) c.level = 4;
+        }
+        if (const char* v = std::getenv("SPARSE_LOG_OUTPUT")) {
+            const std::string o(v);
+            c.output = o == "stdout" ? 1 : o == "file" ? 2 : o == "syslog" ? 3 : 0;
+        }
+        return c;
     }();
-    if (enabled) std::fprintf(stderr, "[mcsparse] %s\n", msg);
+    static std::mutex lock;
+    if (!cfg.enabled || level > cfg.level || cfg.output == 3) return;
+    static const char* const names[] = {"FATAL", "ERROR", "WARNING", "INFO", "DEBUG"};
+    std::lock_guard<std::mutex> g(lock);
+    std::FILE* out = cfg.output == 1 ? stdout : stderr;
+    if (cfg.output == 2) {
+        if (cfg.file == nullptr) cfg.file = std::fopen("mcsparse.txt", "w");
+        if (cfg.file != nullptr) out = cfg.file;
+    }
+    std::fprintf(out, "[%s] [mcsparse] %s\n", names[level < 0 ? 0 : (level > 4 ? 4 : level)], msg);
+    std::fflush(out);
 }
+inline void log_error(const char* msg) { log_message(1, msg); }
 
 inline bool value_type_known(macaDataType t) {
     switch (t) {

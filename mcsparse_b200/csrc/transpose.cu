@@ -358,6 +358,7 @@ cudaError_t coo_sort_structure(cudaStream_t s, int64_t key_range, int64_t nnz, i
 }
 
 __device__ int g_unsorted_flag;  // result word of indices_unsorted (one check at a time per process)
+static std::mutex g_unsorted_lock;  // one lock for every index type: the instantiations share the word above
 
 cudaError_t split_index_pairs(cudaStream_t s, int64_t nnz, const int32_t* pairs, int32_t* rows, int32_t* cols) {
     if (nnz == 0) return cudaSuccess;
@@ -368,8 +369,7 @@ cudaError_t split_index_pairs(cudaStream_t s, int64_t nnz, const int32_t* pairs,
 
 template <typename I>
 cudaError_t indices_unsorted(cudaStream_t s, int64_t count, const I* idx, int* host_flag) {
-    static std::mutex one_at_a_time;
-    std::lock_guard<std::mutex> g(one_at_a_time);
+    std::lock_guard<std::mutex> g(g_unsorted_lock);
     int* device_flag = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&device_flag), g_unsorted_flag);
     if (e == cudaSuccess) e = cudaMemsetAsync(device_flag, 0, sizeof(int), s);

@@ -172,3 +172,24 @@ def test_public_header_is_plain_c(tmp_path):
     src.write_text('#include "mcsparse.h"\nint main(void) { mcsparseHandle_t h = 0; (void)h; return 0; }\n')
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(root, "include"), "-I",
                     cuda_inc, str(src)], check=True)
+
+
+@pytest.mark.parametrize("env,where", [({}, "stderr"), ({"SPARSE_LOG_OUTPUT": "stdout"}, "stdout"),
+                                       ({"SPARSE_LOG_OUTPUT": "file"}, "file"), ({"SPARSE_LOG_ENABLE": "0"}, None),
+                                       ({"SPARSE_LOG_LEVEL": "0"}, None), ({"SPARSE_LOG_OUTPUT": "syslog"}, None)])
+def test_logger_switches(tmp_path, env, where):
+    """SPARSE_LOG_ENABLE / SPARSE_LOG_LEVEL / SPARSE_LOG_OUTPUT as the reference's logger reads them
+    (mcsparse/src/utils/mcsp_logger.cpp:29-61), on a create-time error (mcsparse/src/common/mcsp_helper.cpp:327)."""
+    import subprocess
+    import sys
+
+    code = ("import ctypes as C; from mcsparse_b200 import capi; d = C.c_void_p();"
+            "st = capi.lib.mcsparseCreateDnVec(C.byref(d), -1, C.c_void_p(0x1000), capi.MACA_R_32F); print('status', st)")
+    full = {k: v for k, v in os.environ.items() if not k.startswith("SPARSE_LOG")}
+    full.update(env, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", code], cwd=tmp_path, env=full, capture_output=True, text=True, timeout=120)
+    assert "status 3" in r.stdout, r.stderr
+    log_file = tmp_path / "mcsparse.txt"
+    seen = {"stderr": "Wrong input size" in r.stderr, "stdout": "Wrong input size" in r.stdout,
+            "file": log_file.exists() and "Wrong input size" in log_file.read_text()}
+    assert seen == {k: k == where for k in seen}

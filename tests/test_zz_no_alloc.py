@@ -5,8 +5,9 @@ cudaMalloc inside the call, or code that cannot afford the implicit synchronisat
 allocation) cannot provide the work buffer mcsparseSpMV needs, so this variant keeps the work
 partition in a fixed array inside the library. The test calls it through the C ABI twice in a
 row, on different matrices that share that array, and compares each result with mcsparseSpMV's
-on the same inputs; it also checks that torch's allocator is not touched and that a matrix too
-large for the fixed array is refused with the documented status. The file sorts last so that a
+on the same inputs; it also checks that the device's free memory (cudaMemGetInfo, which sees any
+allocation made inside the library) does not change and that a matrix too large for the fixed array
+is refused with the documented status. The file sorts last so that a
 run stopping at the first failure has already run every other test.
 """
 
@@ -51,11 +52,22 @@ def test_no_alloc_spmv_matches_spmv_on_two_calls_in_a_row(handle, device):
         cases.append((cfg, w, A, X, Ynew, y_ref, y_new, alpha, beta))
     torch.cuda.synchronize()
 
+    # one call first: the first call on a device looks up the address of the built-in work area
+    cfg, w, A, X, Ynew, y_ref, y_new, alpha, beta = cases[0]
+    capi.check(_no_alloc_spmv(handle, A, X, Ynew, cfg.dtype, alpha, beta), "mcsparseB200SpMVNoAlloc")
+    torch.cuda.synchronize()
+    y_new.copy_(w.y0)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(device)[0]  # cudaMemGetInfo: sees allocations torch's counters cannot
     before = torch.cuda.memory_stats(device)["allocation.all.allocated"]
     for cfg, w, A, X, Ynew, y_ref, y_new, alpha, beta in cases:  # two calls in a row, one shared work area
         capi.check(_no_alloc_spmv(handle, A, X, Ynew, cfg.dtype, alpha, beta), "mcsparseB200SpMVNoAlloc")
     torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(device)[0] == free_before
     assert torch.cuda.memory_stats(device)["allocation.all.allocated"] == before
+    status = C.c_int(-1)  # the status word of the built-in work area: NULL stands for it
+    capi.check(lib.mcsparseB200SpMVGetStatus(handle.h, cases[-1][2].d, None, C.byref(status)))
+    assert status.value == 0
 
     for cfg, w, A, X, Ynew, y_ref, y_new, alpha, beta in cases:
         ref, d = oracle.spmv(w.row_ptr, w.col, w.val, w.x, alpha, beta, w.y0)
