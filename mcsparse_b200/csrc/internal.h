@@ -39,6 +39,10 @@ struct mcsparseContext {
     int withhold_copies = 0;           // diagnostics: issue no bulk copies, so that every wait runs out
     int* fault_word_host = nullptr;
     int* fault_word_dev = nullptr;
+    // L2 residency of x (see XResidency in api.cpp): the device's largest persisting carve-out, read once, and
+    // whether this handle has already asked for it.
+    long long max_persisting_l2 = -1;
+    bool persisting_l2_requested = false;
 };
 
 struct mcsparseMatDescr {
