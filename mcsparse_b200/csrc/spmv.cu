@@ -576,7 +576,6 @@ __device__ void push_crew(const CrewCfg& crew, const PeerList<T>& peers, const i
 template <bool CREW>
 __device__ __forceinline__ void tile_count_off(const CrewCfg& crew, int t, int tid) {
     if constexpr (CREW) {
-        if (crew.tiles_per_chunk == 0) return;
         __syncthreads();  // every thread's stores to y are issued
         // A release without the acquire half: a full fence here would invalidate the SM's L1 at the end of every
         // tile and take the x lines of the other resident tiles with it.
@@ -1256,10 +1255,6 @@ cudaError_t spmv_tiled(cudaStream_t s, int64_t m, int64_t nnz, int base, const I
             crew.tiles_per_chunk = kCrewTilesPerChunk;
             crew.num_chunks = (int)((ws.num_tiles + kCrewTilesPerChunk - 1) / kCrewTilesPerChunk);
             crew.done = reinterpret_cast<int*>(base_ptr + ws.off_done);
-            if (const char* dbg = std::getenv("MCSPARSE_B200_CREW_DEBUG")) {  // tuning: 1 no count-off, no pushing; 2 no pushing
-                crew.num_chunks = 0;
-                if (dbg[0] == '1') crew.tiles_per_chunk = 0;
-            }
             cudaError_t e = cudaMemsetAsync(crew.done, 0, size_t(crew.num_chunks) * 4, s);
             if (e != cudaSuccess) return e;
             // (no fix-up kernel: the crew adds the carries of a chunk's rows before it copies them)
