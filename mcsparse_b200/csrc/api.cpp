@@ -124,7 +124,7 @@ int probe_tile_kind(mcsparseContext* h, const void* ptr, const void* idx, bool w
     // similar, moderate length are faster with lanes per row.
     int kind = counts[0] < 1024 ? kTileSmall : kTileLarge;
     if (counts[0] < 1024 && counts[1] >= 2) kind |= kTileWalk;
-    if (wide) kind |= kTileSmall;  // 64-bit indices: one tile size
+    if (wide && vsize == 4) kind |= kTileSmall;  // 64-bit indices with 4-byte values: one tile size
     // A matrix so small that the large tiles would not fill the GPU four times over also gets the small ones.
     const int64_t large = spmv_workspace(rows, nnz, vsize, kTileLarge).items_per_tile;
     if ((rows + nnz) / large < 4LL * 8 * (h->sm_count > 0 ? h->sm_count : 148)) kind |= kTileSmall;
@@ -148,7 +148,7 @@ int choose_tile_kind(mcsparseContext* h, mcsparseSpMatDescr* A, const void* ptr,
 int known_tile_kind(mcsparseSpMatDescr* A) {
     std::lock_guard<std::mutex> g(A->lock);
     if (A->probed_cols == A->cols && A->probed_nnz == A->nnz) return A->tile_kind;
-    return apply_tile_overrides(A->colIdxType == MCSPARSE_INDEX_64I ? kTileSmall : kTileLarge);
+    return apply_tile_overrides(A->colIdxType == MCSPARSE_INDEX_64I && value_size(A->valueType) == 4 ? kTileSmall : kTileLarge);
 }
 
 WaitCfg wait_cfg(const mcsparseContext* h) {

@@ -22,14 +22,16 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// Items per thread of the two tile sizes. With 64-bit column indices the staged columns take twice
-// the shared memory, so only the small tile is used.
+// Items per thread of the two tile sizes. With 64-bit column indices the staged columns take twice the shared
+// memory: 8-byte values keep both sizes (the large tile is then 33 KB), 4-byte values only the small one
+// (their large tile would need 49 KB, over the 48 KB of static shared memory).
 // The sizes go by the bytes of a value: 4 (float), 8 (double, complex float), 16 (complex double, one size).
 constexpr int tile_items(size_t value_size, bool small) {
     return value_size == 4   ? (small ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F32 : MCSPARSE_B200_SPMV_TILE_ITEMS_F32)
            : value_size == 8 ? (small ? MCSPARSE_B200_SPMV_SMALL_TILE_ITEMS_F64 : MCSPARSE_B200_SPMV_TILE_ITEMS_F64)
                              : MCSPARSE_B200_SPMV_TILE_ITEMS_C64;
 }
+constexpr bool wide_index_one_size(size_t value_size, size_t index_size) { return index_size == 8 && value_size == 4; }
 // Thread blocks per SM the tile kernels are compiled for: as many as their shared memory admits, at most 8
 // (256 threads x 8 = all the SM's threads). Without it the push variants, which keep the peer list live, take
 // 40 registers and lose a quarter of the resident blocks.
@@ -41,7 +43,7 @@ constexpr int tile_min_blocks(size_t value_size, size_t index_size, int threads,
 template <typename T, typename I>
 struct TileCfg {
     static constexpr int kSmall = tile_items(sizeof(T), true) / kThreads;
-    static constexpr int kLarge = sizeof(I) == 8 ? kSmall : tile_items(sizeof(T), false) / kThreads;
+    static constexpr int kLarge = wide_index_one_size(sizeof(T), sizeof(I)) ? kSmall : tile_items(sizeof(T), false) / kThreads;
 };
 
 // Structure probe: 1024 threads x 4 samples. count[0]: how many of 4096 evenly spaced pairs of neighbouring
@@ -1146,7 +1148,7 @@ static SpmvWorkspace spmv_layout(int64_t m, int64_t nnz, size_t value_size, int 
 
 SpmvWorkspace spmv_workspace(int64_t m, int64_t nnz, size_t value_size, int tile_kind, size_t index_size) {
     const int small = tile_items(value_size, true);
-    const int large = index_size == 8 ? small : tile_items(value_size, false);  // 64-bit indices: one tile size
+    const int large = wide_index_one_size(value_size, index_size) ? small : tile_items(value_size, false);
     SpmvWorkspace ws = spmv_layout(m, nnz, value_size, (tile_kind & kTileSmall) ? small : large);
     ws.walk = (tile_kind & kTileWalk) != 0;
     ws.bytes = spmv_layout(m, nnz, value_size, small).bytes;

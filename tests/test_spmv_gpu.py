@@ -119,6 +119,7 @@ def test_spmv_unaligned_arrays(handle, device, dtype, offset):
 def test_spmv_64bit_indices(handle, device, name, dtype, base, offset, monkeypatch):
     """MCSPARSE_INDEX_64I row offsets and column indices: same result, bit for bit, as the 32-bit
     run with the same (small) tile size, and the same work partition."""
+    monkeypatch.setenv("MCSPARSE_B200_SPMV_TILE", "small")  # (8-byte values would also have the large tile)
     lengths = ADVERSARIAL_LENGTHS[name]
     ncols = max(max(lengths), 1) + 17
     rp, col, val = csr_from_lengths(lengths, ncols, dtype, seed=13, base=base)
