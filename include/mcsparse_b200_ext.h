@@ -67,6 +67,17 @@ mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcspa
                                                 const int32_t** colInd, const void** values);
 
 /*
+ * A promise about the values of matA, for transposed products (op(A) = A^T / A^H on CSR, op(A) = A on CSC) that run
+ * from a structure recorded by mcsparseSpMV_preprocess: with keep != 0 the caller will announce every change of the
+ * value array through mcsparseSpMatSetValues or the SetPointers call of its format (passing the same pointer again
+ * is enough after an in-place edit). A product may then reuse the values it gathered into the external buffer the
+ * last time instead of gathering all nonzeros again (on the 27-point stencil the gather costs twice the product
+ * itself). Without the promise (the default) every product gathers, which is always right. The reference converts
+ * on every call (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:797-846); it has no such switch.
+ */
+mcsparseStatus_t mcsparseB200SpMatKeepConvertedValues(mcsparseSpMatDescr_t matA, int keep);
+
+/*
  * Device-side status of the SpMV calls that used externalBuffer since its last analysis (pass
  * NULL for the built-in work area of mcsparseB200SpMVNoAlloc): 0; bit 0 set if a thread block gave
  * up its bounded wait for the bulk copies of its tile and left its rows unwritten; bit 1 set if a

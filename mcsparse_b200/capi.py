@@ -140,6 +140,7 @@ PROTOTYPES = {
     "mcsparseB200PeerClose": (_i, [_vp]),
     "mcsparseB200SpMVGetStatus": (_i, [_vp, _vp, _vp, _pi]),
     "mcsparseB200SetDeviceWaitLimit": (_i, [_vp, _i64, _i]),
+    "mcsparseB200SpMatKeepConvertedValues": (_i, [_vp, _i]),
     "mcsparseB200GatherProbe": (_i, [_vp, _vp, _i64, _vp, _i, _vp, _i]),
     "mcsparseB200SpMVPartitionView": (_i, [_vp, _vp, _pi, _pi64, _pvp]),
     "mcsparseB200SpMVTransposedView": (_i, [_vp, _i, _vp, _pi64, _pvp, _pvp, _pvp]),

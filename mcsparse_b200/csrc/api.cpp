@@ -424,8 +424,26 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
         }
     }
     if (preprocess_only) return OK;
-    cudaError_t e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area, v.conjugate);
-    if (e != cudaSuccess) return from_cuda(e);
+    // The values are gathered through the permutation on every product (they may have been edited in place), unless
+    // the caller promised to announce changes (mcsparseB200SpMatKeepConvertedValues) and this buffer already holds
+    // the gathered values of this array.
+    bool gather = true;
+    {
+        std::lock_guard<std::mutex> g(A->lock);
+        gather = !(cached && A->keep_converted_values && A->trans_values_src == A->vals &&
+                   A->trans_values_conj == v.conjugate);
+        A->trans_values_src = nullptr;
+    }
+    cudaError_t e = cudaSuccess;
+    if (gather) {
+        e = transpose_values<T>(h->stream, nnz, static_cast<const T*>(A->vals), L.plan, L.area, v.conjugate);
+        if (e != cudaSuccess) return from_cuda(e);
+    }
+    if (cached) {  // (without a recorded conversion the buffer is rebuilt by the next call anyway)
+        std::lock_guard<std::mutex> g(A->lock);
+        A->trans_values_src = A->vals;
+        A->trans_values_conj = v.conjugate;
+    }
     e = spmv_tiled<T, int32_t>(h->stream, v.n, nnz, 0, t_ptr, t_idx, t_val, static_cast<const T*>(X->values),
                                static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws, L.work,
                                PeerList<T>(), wait_cfg(h));
@@ -493,7 +511,10 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
-        if (A->trans_buffer == buffer) A->trans_buffer = nullptr;  // the buffer changes hands: a later A^T product reconverts
+        if (A->trans_buffer == buffer) {  // the buffer changes hands: a later A^T product reconverts
+            A->trans_buffer = nullptr;
+            A->trans_values_src = nullptr;
+        }
         if (preprocess_only) {
             A->analysed_buffer = buffer;
             A->analysed_rows = view.ptr;

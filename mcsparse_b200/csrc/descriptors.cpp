@@ -306,6 +306,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     d->analysed_buffer = nullptr;
     d->analysed_rows = nullptr;
     d->trans_buffer = nullptr;
+    d->trans_values_src = nullptr;
     d->trans_probed_idx = nullptr;
     d->coo_checked_rows = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
@@ -426,6 +427,14 @@ mcsparseStatus_t mcsparseSpMatGetValues(mcsparseSpMatDescr_t d, void** values) {
 mcsparseStatus_t mcsparseSpMatSetValues(mcsparseSpMatDescr_t d, void* values) {
     if (d == nullptr) return pub(BAD_POINTER);
     d->vals = values;
+    d->trans_values_src = nullptr;  // the values changed (or may have): converted copies are stale
+    return MCSPARSE_STATUS_SUCCESS;
+}
+
+mcsparseStatus_t mcsparseB200SpMatKeepConvertedValues(mcsparseSpMatDescr_t d, int keep) {
+    if (d == nullptr) return pub(BAD_POINTER);
+    d->keep_converted_values = keep != 0;
+    d->trans_values_src = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
 }
 

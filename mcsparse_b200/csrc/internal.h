@@ -89,6 +89,12 @@ struct mcsparseSpMatDescr {
     const void* trans_probed_idx = nullptr;
     int64_t trans_probed_nnz = -1;
     int trans_tile_kind = 0;
+    // Set by mcsparseB200SpMatKeepConvertedValues: the caller promises to announce every change of the values
+    // (mcsparseSpMatSetValues / SetPointers), so a transposed product may reuse the values it gathered into the
+    // buffer last time (trans_values_src / _conj say which) instead of gathering them again.
+    bool keep_converted_values = false;
+    const void* trans_values_src = nullptr;
+    bool trans_values_conj = false;
     // COO inputs: whether the row indices were found out of order (checked once per array, remembered).
     const void* coo_checked_rows = nullptr;
     int64_t coo_checked_nnz = -1;

@@ -329,3 +329,40 @@ def test_spmv_coo_array_of_pairs(handle, device, name, dtype, op):
             ref, dd = oracle.spmv(t_ptr, t_idx, val[perm], x, alpha, beta, y0)
         assert_close(d_y.cpu().numpy(), ref, dd, TOL[np.dtype(dtype)], f"{name} pairs op {op} preprocess {pre}")
     lib.mcsparseDestroySpMat(d)
+
+
+def test_transposed_product_keeps_converted_values_on_promise(handle, device):
+    """mcsparseB200SpMatKeepConvertedValues: once the caller promises to announce value changes, a transposed
+    product reuses the values gathered last time; an in-place edit is then only seen after mcsparseSpMatSetValues."""
+    cfg = workloads.scaled("C5", 64)
+    w = workloads.generate(cfg, device)
+    A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
+    x = workloads.dense_values(cfg, device, w.rows, 77)
+    y = torch.zeros(w.cols, dtype=cfg.dtype, device=device)
+    X, Y = mc.DnVec(x), mc.DnVec(y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=T), dtype=torch.uint8, device=device)
+    mc.spmv_preprocess(handle, A, X, Y, buf, op=T)
+    capi.check(lib.mcsparseB200SpMatKeepConvertedValues(A.d, 1))
+    mc.spmv(handle, A, X, Y, buf, op=T)  # gathers (nothing gathered yet)
+    torch.cuda.synchronize()
+    first = y.clone()
+    mc.spmv(handle, A, X, Y, buf, op=T)  # reuses
+    torch.cuda.synchronize()
+    assert torch.equal(y, first)
+    w.val.mul_(3.0)  # in place, not announced: the product still runs on the gathered copy
+    mc.spmv(handle, A, X, Y, buf, op=T)
+    torch.cuda.synchronize()
+    assert torch.equal(y, first)
+    capi.check(lib.mcsparseSpMatSetValues(A.d, C.c_void_p(w.val.data_ptr())))  # announced: gathered again
+    mc.spmv(handle, A, X, Y, buf, op=T)
+    torch.cuda.synchronize()
+    rp, col = w.row_ptr.cpu().numpy(), w.col.cpu().numpy()
+    t_ptr, t_idx, perm = oracle.csr_transpose(rp, col, w.cols)
+    ref, d = oracle.spmv(t_ptr, t_idx, w.val.cpu().numpy()[perm], x.cpu().numpy(), 1.0, 0.0)
+    assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], "after the announced change")
+    capi.check(lib.mcsparseB200SpMatKeepConvertedValues(A.d, 0))  # promise withdrawn: every product gathers again
+    w.val.mul_(0.5)
+    mc.spmv(handle, A, X, Y, buf, op=T)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(t_ptr, t_idx, w.val.cpu().numpy()[perm], x.cpu().numpy(), 1.0, 0.0)
+    assert_close(y.cpu().numpy(), ref, d, TOL[cfg.dtype], "without the promise")
