@@ -121,7 +121,8 @@ def visible_device_index(local_rank):
 class SpmvJob:
     """One configuration on one rank: a row block of A resident in HBM, x replicated."""
 
-    def __init__(self, name, device, rank, world, handle, scale=1, index_bits=32, complex_values=False):
+    def __init__(self, name, device, rank, world, handle, scale=1, index_bits=32, complex_values=False,
+                 half_operands=False):
         import torch
 
         import mcsparse_b200 as mc
@@ -153,6 +154,10 @@ class SpmvJob:
             if w.y0 is not None:
                 w.y0 = torch.complex(w.y0, w.y0.flip(0)).to(cdt)
             self.vsize *= 2
+        self.compute_dtype = None
+        if half_operands:  # variant: the same matrix with A and x in fp16, sums and y in fp32 (N = 1 only)
+            w.val, w.x = w.val.to(torch.float16), w.x.to(torch.float16)
+            self.compute_dtype = torch.float32
         self.A = mc.CsrMatrix(w.rows, w.cols, w.row_ptr, w.col, w.val)
         if world > 1:
             from mcsparse_b200 import sharding
@@ -164,12 +169,12 @@ class SpmvJob:
             self.X, self.Y, self.buf = self.sharded.X, self.sharded.Y, self.sharded.buffer
         else:
             self.sharded = None
-            self.y_full = torch.zeros(cfg.rows, dtype=w.val.dtype, device=device)
+            self.y_full = torch.zeros(cfg.rows, dtype=self.compute_dtype or w.val.dtype, device=device)
             self.y = self.y_full[r0:r1]
             self.X, self.Y = mc.DnVec(w.x), mc.DnVec(self.y)
-            self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y), dtype=torch.uint8,
-                                   device=device)
-            mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf)
+            self.buf = torch.empty(mc.spmv_buffer_size(handle, self.A, self.X, self.Y, compute=self.compute_dtype),
+                                   dtype=torch.uint8, device=device)
+            mc.spmv_preprocess(handle, self.A, self.X, self.Y, self.buf, compute=self.compute_dtype)
         if cfg.beta != 0:
             self.y.copy_(w.y0)
         self.parts = [self.y_full[bounds[g]:bounds[g + 1]] for g in range(world)]
@@ -179,6 +184,9 @@ class SpmvJob:
         span = int((w.col.max() - w.col.min()).item()) + 1 if w.nnz else 0
         self.local_bytes = workloads.algorithmic_bytes(w.rows, min(w.cols, span), w.nnz, self.vsize, cfg.beta,
                                                        index_size=isize)
+        if half_operands:  # 2-byte values and x, 4-byte y
+            self.bytes = self.local_bytes = (w.nnz * (2 + isize) + (w.rows + 1) * isize + w.cols * 2
+                                             + w.rows * 4 * (2 if cfg.beta != 0 else 1))
         self.flops = 2 * self.total_nnz
         # tile kernel + carry fix-up; sharded: per chunk a tile launch and a fix-up (pipelined push), or one of each
         # (rows pushed by the tile kernel), and the kernel that orders the GPUs
@@ -188,7 +196,8 @@ class SpmvJob:
 
     def compute(self):
         """The local SpMV only (no assembly of y): what the roofline fraction is computed from."""
-        self.mc.spmv(self.h, self.A, self.X, self.Y, self.buf, alpha=self.cfg.alpha, beta=self.cfg.beta)
+        self.mc.spmv(self.h, self.A, self.X, self.Y, self.buf, alpha=self.cfg.alpha, beta=self.cfg.beta,
+                     compute=self.compute_dtype)
 
     def step(self):
         """One full step: at N > 1 the SpMV with the fused push of y to all GPUs, then the ordering collective."""
@@ -549,6 +558,18 @@ def run_gpu(args, rank, world, local_rank):
             print(json.dumps(r), flush=True)
         return
 
+    if args.half_operands:  # A and x in fp16, sums and y in fp32: single GPU, one compact line
+        if rank == 0:
+            j = SpmvJob(args.workload, device, 0, 1, h, args.scale, half_operands=True)
+            r = measure_job(torch, j, args.steps, args.warmup, peak, flush_buf)
+            r.update({"metric": METRIC, "value": r["gbs"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "higher_is_better": True, "dtype": "f16 operands, f32 sums",
+                      "data": "synthetic",
+                      "config": {"workload": workload_label(args.workload) + " with fp16 A and x, fp32 y"
+                                 + ("" if args.scale == 1 else f" / {args.scale}")}})
+            print(json.dumps(r), flush=True)
+        return
+
     job = SpmvJob(args.workload, device, rank, world, h, args.scale)
     flush = flush_buf if job.local_bytes < 4 * L2_BYTES else None
 
@@ -736,6 +757,12 @@ def run_gpu(args, rank, world, local_rank):
                 extra[key] = measure_job(torch, j, 30, 3, peak, flush_buf)
                 del j
                 torch.cuda.empty_cache()
+            # fp16 operands with fp32 sums and y (6 bytes per nonzero)
+            for name in ("C5", "C2", "C3"):
+                j = SpmvJob(name, device, 0, 1, h, half_operands=True)
+                extra[f"{name}_fp16_operands"] = measure_job(torch, j, 30, 3, peak, flush_buf)
+                del j
+                torch.cuda.empty_cache()
             for name in ("C2", "C5"):
                 j = TransposedSpmvJob(name, device, h)
                 extra[f"{name}_transposed"] = measure_job(torch, j, 30, 3, peak, flush_buf)
@@ -780,6 +807,8 @@ def main():
                     help="independent products kept in flight by the end-to-end (host buffer) measurement")
     ap.add_argument("--transposed", action="store_true",
                     help="time y = A^T x (conversion once, then value gather + SpMV per step) instead of y = A x")
+    ap.add_argument("--half-operands", action="store_true",
+                    help="the SpMV workload with A and x in fp16, sums and y in fp32 (N = 1)")
     ap.add_argument("--quick", action="store_true", help="tuning runs: skip the comparison timings")
     ap.add_argument("--headline-only", action="store_true", help="skip the per-configuration block at N=1")
     args = ap.parse_args()

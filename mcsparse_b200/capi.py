@@ -41,6 +41,7 @@ MCSPARSE_SPMV_ALG_DEFAULT = 0
 MCSPARSE_SPMM_ALG_DEFAULT = 0
 MCSPARSE_ALG_MERGE_PATH = 0
 MACA_R_32F, MACA_R_64F, MACA_R_16F, MACA_C_32F, MACA_C_64F, MACA_R_32I = 0, 1, 2, 4, 5, 10
+MACA_R_8I, MACA_R_16BF = 3, 14
 MAJOR_VERSION, MINOR_VERSION, PATCH_LEVEL = 0, 1, 2
 
 SPMV_TILE_ITEMS = {MACA_R_32F: (4096, 2048), MACA_R_64F: (2048, 1024),  # (large, small) tile per value type

@@ -23,6 +23,19 @@ bool real_matrix_complex_vectors(macaDataType a, macaDataType x, macaDataType y,
     return ((a == MACA_R_32F && compute == MACA_C_32F) || (a == MACA_R_64F && compute == MACA_C_64F)) &&
            x == compute && y == compute;
 }
+// Low-precision operands with wider sums (mcsp_spmv_gpu.cpp:848-860 sends every call whose compute, matrix and
+// output types are not all one type, and whose matrix is not fp32 / fp64, to mcspMixedPrecisionSpMVImpl, which
+// routes by the types of x and y, :498-561). A and x share a type; the scalars and the sums are fp32, or int32
+// for int8 -> int32. The half-precision complex pairs of that table are not built.
+MixedKind low_precision_kind(macaDataType a, macaDataType x, macaDataType y, macaDataType compute) {
+    if (a != x) return MixedKind::kNone;
+    if (compute == MACA_R_32I) return (x == MACA_R_8I && y == MACA_R_32I) ? MixedKind::kInt8ToInt32 : MixedKind::kNone;
+    if (compute != MACA_R_32F) return MixedKind::kNone;
+    if (x == MACA_R_16F) return y == MACA_R_32F ? MixedKind::kHalfToFloat : y == MACA_R_16F ? MixedKind::kHalfToHalf : MixedKind::kNone;
+    if (x == MACA_R_16BF) return y == MACA_R_32F ? MixedKind::kBf16ToFloat : y == MACA_R_16BF ? MixedKind::kBf16ToBf16 : MixedKind::kNone;
+    if (x == MACA_R_8I) return y == MACA_R_32F ? MixedKind::kInt8ToFloat : MixedKind::kNone;
+    return MixedKind::kNone;
+}
 size_t value_size(macaDataType t) { return t == MACA_C_64F ? 16 : (t == MACA_R_64F || t == MACA_C_32F) ? 8 : 4; }
 bool too_big(int64_t v) { return (v >> 31) != 0; }  // int32 indices: every extent must fit
 
@@ -78,6 +91,9 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     if (!n_op && !allow_transposed) return NOT_IMPL;
     // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
     if (A->format == MCSPARSE_FORMAT_CSC && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
+    // Low-precision operands: CSR, op(A) = A, 32-bit indices, through the generic entry points.
+    if (low_precision_kind(A->valueType, X->valueType, Y->valueType, computeType) != MixedKind::kNone)
+        return (allow_transposed && n_op && narrow && A->format == MCSPARSE_FORMAT_CSR) ? OK : NOT_IMPL;
     const bool mixed = real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType);
     if (!(computeType == A->valueType && computeType == Y->valueType && computeType == X->valueType) && !mixed)
         return NOT_IMPL;
@@ -481,6 +497,36 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
             default: return spmv_transposed_run<float>(h, A, view, X, Y, alpha, beta, buffer, preprocess_only);
         }
     }
+    if (const MixedKind low = low_precision_kind(A->valueType, X->valueType, Y->valueType, computeType);
+        low != MixedKind::kNone) {
+        // Same merge-path partition as the fp32 kernels' small tile, recorded by preprocess in the same way.
+        SpmvWorkspace ws = spmv_mixed_workspace(A->row_num, A->nnz);
+        void* buf = align_up_256(buffer);
+        // scattered columns and rows of very different lengths: every tile takes the merge walk
+        ws.walk = (choose_tile_kind(h, A, A->rows, A->cols, A->row_num, buf) & kTileWalk) != 0;
+        bool analyse = true;
+        {
+            std::lock_guard<std::mutex> g(A->lock);
+            if (A->trans_buffer == buffer) A->trans_buffer = nullptr, A->trans_values_src = nullptr;
+            if (preprocess_only) {
+                A->analysed_buffer = buffer;
+                A->analysed_rows = A->rows;
+                A->analysed_items_per_tile = ws.items_per_tile;
+            } else if (A->analysed_buffer == buffer && A->analysed_rows == A->rows &&
+                       A->analysed_items_per_tile == ws.items_per_tile) {
+                analyse = false;
+            }
+        }
+        const int32_t* rp = static_cast<const int32_t*>(A->rows);
+        if (analyse) {
+            const cudaError_t e = spmv_analysis(h->stream, A->row_num, A->nnz, A->mat_descr->base, rp, ws, buf);
+            if (e != cudaSuccess) return from_cuda(e);
+        }
+        if (preprocess_only) return OK;
+        return from_cuda(spmv_mixed(h->stream, low, A->row_num, A->mat_descr->base, rp, static_cast<const int32_t*>(A->cols),
+                                    A->vals, X->values, Y->values, scalar_arg<float>(h, alpha), scalar_arg<float>(h, beta),
+                                    scalar_arg<int>(h, alpha), scalar_arg<int>(h, beta), ws, buf));
+    }
     if (real_matrix_complex_vectors(A->valueType, X->valueType, Y->valueType, computeType)) {
         if (preprocess_only) return OK;  // nothing to record: the buffer only holds the intermediate product
         void* z = align_up_256(buffer);
@@ -860,6 +906,10 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
     if (st != OK) return pub(st);
     // Work partition + carries, plus slack to align the caller's pointer to 256 bytes; a COO matrix
     // also needs room for the row offsets derived from its row indices.
+    if (low_precision_kind(matA->valueType, vecX->valueType, vecY->valueType, computeType) != MixedKind::kNone) {
+        *bufferSize = spmv_mixed_workspace(matA->row_num, matA->nnz).bytes + 256;  // (+ alignment slack)
+        return MCSPARSE_STATUS_SUCCESS;
+    }
     if (real_matrix_complex_vectors(matA->valueType, vecX->valueType, vecY->valueType, computeType)) {
         *bufferSize = size_t(matA->row_num) * value_size(computeType) + 512;  // the intermediate A * x
         return MCSPARSE_STATUS_SUCCESS;

@@ -282,6 +282,17 @@ cudaError_t spmv_real_matrix_complex_vectors(cudaStream_t s, int64_t m, int base
                                              ScalarArg<Complex<F>> alpha, ScalarArg<Complex<F>> beta,
                                              Complex<F>* scratch);
 
+// Low-precision operands (A and x of one type) with fp32 or int32 sums: operand type -> type of y.
+enum class MixedKind { kNone, kHalfToFloat, kBf16ToFloat, kInt8ToFloat, kHalfToHalf, kBf16ToBf16, kInt8ToInt32 };
+
+// y = alpha * A * x + beta * y for a CSR matrix (32-bit indices) of one of the kinds above. alpha and beta are
+// floats, for kInt8ToInt32 32-bit integers (the other pair is not read). `buf` holds spmv_mixed_workspace(m, nnz)
+// with the partition written by spmv_analysis for that workspace.
+SpmvWorkspace spmv_mixed_workspace(int64_t m, int64_t nnz);
+cudaError_t spmv_mixed(cudaStream_t s, MixedKind kind, int64_t m, int base, const int32_t* row_ptr, const int32_t* col,
+                       const void* val, const void* x, void* y, ScalarArg<float> alpha_f, ScalarArg<float> beta_f,
+                       ScalarArg<int> alpha_i, ScalarArg<int> beta_i, const SpmvWorkspace& ws, void* buf);
+
 cudaError_t coo_row_offsets(cudaStream_t s, int64_t m, int64_t nnz, int base, const int32_t* coo_rows,
                             int32_t* offsets);
 

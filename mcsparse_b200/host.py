@@ -12,7 +12,10 @@ from . import capi
 from .capi import check, lib
 
 _DTYPE = {torch.float32: capi.MACA_R_32F, torch.float64: capi.MACA_R_64F,
-          torch.complex64: capi.MACA_C_32F, torch.complex128: capi.MACA_C_64F}
+          torch.complex64: capi.MACA_C_32F, torch.complex128: capi.MACA_C_64F,
+          # operands of the low-precision SpMV (sums in fp32 / int32)
+          torch.float16: capi.MACA_R_16F, torch.bfloat16: capi.MACA_R_16BF, torch.int8: capi.MACA_R_8I,
+          torch.int32: capi.MACA_R_32I}
 
 
 def _ptr(t):
@@ -31,6 +34,8 @@ def _scalar(value, dtype):
     if dtype in (torch.complex64, torch.complex128):
         z = complex(value)
         return ((C.c_float if dtype == torch.complex64 else C.c_double) * 2)(z.real, z.imag)
+    if dtype == torch.int32:
+        return C.c_int32(int(value))
     return (C.c_double if dtype == torch.float64 else C.c_float)(value)
 
 
@@ -151,28 +156,33 @@ def _scalars(handle, alpha, beta, dtype):
     return C.cast(C.byref(a), C.c_void_p), C.cast(C.byref(b), C.c_void_p), (a, b)
 
 
-def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
-    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+def spmv_buffer_size(handle, A, x, y, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE, compute=None):
+    compute = compute or A.dtype
+    pa, pb, keep = _scalars(handle, alpha, beta, compute)
     size = C.c_size_t()
     check(lib.mcsparseSpMV_bufferSize(handle.h, op, pa, A.d, x.d, pb, y.d,
-                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, C.byref(size)),
+                                      _DTYPE[compute], capi.MCSPARSE_SPMV_ALG_DEFAULT, C.byref(size)),
           "mcsparseSpMV_bufferSize")
     del keep
     return size.value
 
 
-def spmv_preprocess(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
-    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
+def spmv_preprocess(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE, compute=None):
+    compute = compute or A.dtype
+    pa, pb, keep = _scalars(handle, alpha, beta, compute)
     check(lib.mcsparseSpMV_preprocess(handle.h, op, pa, A.d, x.d, pb, y.d,
-                                      _DTYPE[A.dtype], capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)),
+                                      _DTYPE[compute], capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)),
           "mcsparseSpMV_preprocess")
     del keep
 
 
-def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE):
-    """y = alpha * op(A) @ x + beta * y through mcsparseSpMV (asynchronous on the handle's stream)."""
-    pa, pb, keep = _scalars(handle, alpha, beta, A.dtype)
-    check(lib.mcsparseSpMV(handle.h, op, pa, A.d, x.d, pb, y.d, _DTYPE[A.dtype],
+def spmv(handle, A, x, y, buffer, alpha=1.0, beta=0.0, op=capi.MCSPARSE_OPERATION_NON_TRANSPOSE, compute=None):
+    """y = alpha * op(A) @ x + beta * y through mcsparseSpMV (asynchronous on the handle's stream).
+    ``compute`` is the compute type where it differs from A's (fp16 / bf16 / int8 operands: torch.float32,
+    or torch.int32 for int8 -> int32)."""
+    compute = compute or A.dtype
+    pa, pb, keep = _scalars(handle, alpha, beta, compute)
+    check(lib.mcsparseSpMV(handle.h, op, pa, A.d, x.d, pb, y.d, _DTYPE[compute],
                            capi.MCSPARSE_SPMV_ALG_DEFAULT, _ptr(buffer)), "mcsparseSpMV")
     del keep
 
