@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) of one spmv_tile_kernel launch divided by its algorithmic bytes, from the ncu
 # captures summarised under profiles/ (taken at reduced scale and scaled by the units processed).
-TRAFFIC_RATIO = {"C5": 0.985, "C2": 0.99, "C3": 1.71, "C4_n64": 3.47}
+TRAFFIC_RATIO = {"C5": 0.985, "C5_fp16_operands": 1.003, "C2": 0.99, "C3": 1.71, "C4_n64": 3.47}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -761,6 +761,8 @@ def run_gpu(args, rank, world, local_rank):
             for name in ("C5", "C2", "C3"):
                 j = SpmvJob(name, device, 0, 1, h, half_operands=True)
                 extra[f"{name}_fp16_operands"] = measure_job(torch, j, 30, 3, peak, flush_buf)
+                if f"{name}_fp16_operands" in TRAFFIC_RATIO:
+                    extra[f"{name}_fp16_operands"]["traffic"] = round(TRAFFIC_RATIO[f"{name}_fp16_operands"] * j.bytes)
                 del j
                 torch.cuda.empty_cache()
             for name in ("C2", "C5"):
