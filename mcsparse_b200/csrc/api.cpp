@@ -89,8 +89,6 @@ St spmv_check(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     if (is_real_fp(computeType) && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return BAD_VALUE;
     // op(A) = A^T / A^H and CSC inputs run through a conversion into the buffer.
     if (!n_op && !allow_transposed) return NOT_IMPL;
-    // A^H of a CSC matrix would run the CSR kernels on conj(values): not built.
-    if (A->format == MCSPARSE_FORMAT_CSC && opA == MCSPARSE_OPERATION_CONJUGATE_TRANSPOSE) return NOT_IMPL;
     // Low-precision operands: CSR, op(A) = A, 32-bit indices, through the generic entry points.
     if (low_precision_kind(A->valueType, X->valueType, Y->valueType, computeType) != MixedKind::kNone)
         return (allow_transposed && n_op && narrow && A->format == MCSPARSE_FORMAT_CSR) ? OK : NOT_IMPL;
@@ -305,7 +303,7 @@ struct XResidency {
 template <typename T, typename I>
 St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X, mcsparseDnVecDescr* Y,
             const void* alpha, const void* beta, void* buffer, bool analyse, bool compute, int tile_kind,
-            const PushArgs& push = PushArgs()) {
+            const PushArgs& push = PushArgs(), bool scalars_on_host = false) {
     const SpmvWorkspace ws = spmv_workspace(v.m, A->nnz, sizeof(T), tile_kind, sizeof(I));
     void* buf = align_up_256(buffer);
     const int base = A->mat_descr->base;
@@ -336,11 +334,41 @@ St spmv_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcspars
                    (reinterpret_cast<uintptr_t>(push.y[0]) + size_t(push.row_offset) * sizeof(T))) & 15) == 0;
     const XResidency keep_x(h, X->values, size_t(X->size) * sizeof(T), tile_kind);
     for (int p = 0; p < push.count; ++p) peers.y[p] = static_cast<T*>(push.y[p]);
+    const ScalarArg<T> sa = scalars_on_host ? ScalarArg<T>{*static_cast<const T*>(alpha), nullptr} : scalar_arg<T>(h, alpha);
+    const ScalarArg<T> sb = scalars_on_host ? ScalarArg<T>{*static_cast<const T*>(beta), nullptr} : scalar_arg<T>(h, beta);
     cudaError_t e = spmv_tiled<T, I>(h->stream, v.m, A->nnz, base, rows, static_cast<const I*>(v.idx),
                                      static_cast<const T*>(A->vals), static_cast<const T*>(X->values),
-                                     static_cast<T*>(Y->values), scalar_arg<T>(h, alpha), scalar_arg<T>(h, beta), ws,
-                                     buf, peers, wait_cfg(h));
+                                     static_cast<T*>(Y->values), sa, sb, ws, buf, peers, wait_cfg(h));
     return from_cuda(e);
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// A^H x of a CSC matrix with complex values. The reference conjugates the values in place and runs its CSR kernel
+// on the CSC arrays (mcsp_spmv_gpu.cpp:734-770). Here the values stay untouched: conj(A^T) x = conj(A^T conj(x)),
+// the CSC arrays are the CSR arrays of A^T, and conj(x) (A.rows numbers) and the intermediate product (A.cols
+// numbers) live behind the work area; y = alpha * conj(z) + beta * y is the last, vector-sized pass.
+template <typename F, typename I>
+St spmv_csc_conjugate_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView& v, mcsparseDnVecDescr* X,
+                          mcsparseDnVecDescr* Y, const void* alpha, const void* beta, void* buffer, bool analyse,
+                          bool compute, int tile_kind) {
+    using T = Complex<F>;
+    const SpmvWorkspace ws = spmv_workspace(v.m, A->nnz, sizeof(T), tile_kind, sizeof(I));
+    char* const tail = static_cast<char*>(align_up_256(buffer)) + ws.bytes;
+    T* const xc = reinterpret_cast<T*>(tail);
+    T* const z = reinterpret_cast<T*>(tail + align256(size_t(v.n) * sizeof(T)));
+    if (compute) {
+        const cudaError_t e = complex_conj_copy<T>(h->stream, v.n, static_cast<const T*>(X->values), xc);
+        if (e != cudaSuccess) return from_cuda(e);
+    }
+    mcsparseDnVecDescr Xc = *X, Z = *Y;
+    Xc.values = xc;
+    Z.values = z;
+    const T one(F(1), F(0)), zero(F(0), F(0));
+    const St st = spmv_run<T, I>(h, A, v, &Xc, &Z, &one, &zero, buffer, analyse, compute, tile_kind, PushArgs(), true);
+    if (st != OK || !compute) return st;
+    return from_cuda(complex_conj_axpby<T>(h->stream, v.m, scalar_arg<T>(h, alpha), z, scalar_arg<T>(h, beta),
+                                           static_cast<T*>(Y->values)));
 }
 
 // COO as an array of (row, column) pairs: the pairs are split into two arrays behind the rest of the buffer
@@ -571,6 +599,13 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         }
     }
     const bool wide = index_size(A) == 8;
+    if (A->format == MCSPARSE_FORMAT_CSC && view.conjugate) {  // complex values only (view.conjugate says so)
+        if (computeType == MACA_C_32F)
+            return wide ? spmv_csc_conjugate_run<float, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small)
+                        : spmv_csc_conjugate_run<float, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small);
+        return wide ? spmv_csc_conjugate_run<double, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small)
+                    : spmv_csc_conjugate_run<double, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small);
+    }
     if (computeType == MACA_C_32F)
         return wide ? spmv_run<cfloat, int64_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push)
                     : spmv_run<cfloat, int32_t>(h, A, view, X, Y, alpha, beta, buffer, analyse, !preprocess_only, small, push);
@@ -926,6 +961,8 @@ mcsparseStatus_t mcsparseSpMV_bufferSize(mcsparseHandle_t handle, mcsparseOperat
         return MCSPARSE_STATUS_SUCCESS;
     }
     *bufferSize = spmv_workspace(view.m, matA->nnz, value_size(computeType), false, index_size(matA)).bytes + 256;
+    if (matA->format == MCSPARSE_FORMAT_CSC && view.conjugate)  // conj(x) and the intermediate product
+        *bufferSize += align256(size_t(view.n) * value_size(computeType)) + align256(size_t(view.m) * value_size(computeType));
     if (matA->format == MCSPARSE_FORMAT_COO) *bufferSize += ((size_t(matA->row_num) + 1) * 4 + 255) & ~size_t(255);
     return MCSPARSE_STATUS_SUCCESS;
 }

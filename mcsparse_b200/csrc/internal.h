@@ -282,6 +282,12 @@ cudaError_t spmv_real_matrix_complex_vectors(cudaStream_t s, int64_t m, int base
                                              ScalarArg<Complex<F>> alpha, ScalarArg<Complex<F>> beta,
                                              Complex<F>* scratch);
 
+// dst = conj(src); y = alpha * conj(z) + beta * y (complex vectors).
+template <typename T>
+cudaError_t complex_conj_copy(cudaStream_t s, int64_t n, const T* src, T* dst);
+template <typename T>
+cudaError_t complex_conj_axpby(cudaStream_t s, int64_t m, ScalarArg<T> alpha, const T* z, ScalarArg<T> beta, T* y);
+
 // Low-precision operands (A and x of one type) with fp32 or int32 sums: operand type -> type of y.
 enum class MixedKind { kNone, kHalfToFloat, kBf16ToFloat, kInt8ToFloat, kHalfToHalf, kBf16ToBf16, kInt8ToInt32 };
 

@@ -549,6 +549,42 @@ __global__ void complex_axpby_kernel(long long m, ScalarArg<T> alpha_arg, const 
     y[r] = v;
 }
 
+// dst = conj(src), and y = alpha * conj(z) + beta * y (y is not read when beta == 0): the two vector passes
+// around a product with conj(A), which is conj(A * conj(x)).
+template <typename T>
+__global__ void complex_conj_copy_kernel(long long n, const T* __restrict__ src, T* __restrict__ dst) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = conj_value(src[i]);
+}
+template <typename T>
+__global__ void complex_conj_axpby_kernel(long long m, ScalarArg<T> alpha_arg, const T* __restrict__ z,
+                                          ScalarArg<T> beta_arg, T* __restrict__ y) {
+    const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (r >= m) return;
+    const T alpha = alpha_arg.get(), beta = beta_arg.get();
+    T v = alpha * conj_value(ldcs(z + r));
+    if (beta != T(0)) v = mad(beta, y[r], v);
+    y[r] = v;
+}
+template <typename T>
+cudaError_t complex_conj_copy(cudaStream_t s, int64_t n, const T* src, T* dst) {
+    if (n == 0) return cudaSuccess;
+    complex_conj_copy_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(n, src, dst);
+    return cudaGetLastError();
+}
+template <typename T>
+cudaError_t complex_conj_axpby(cudaStream_t s, int64_t m, ScalarArg<T> alpha, const T* z, ScalarArg<T> beta, T* y) {
+    if (m == 0) return cudaSuccess;
+    complex_conj_axpby_kernel<T><<<(unsigned)((m + 255) / 256), 256, 0, s>>>(m, alpha, z, beta, y);
+    return cudaGetLastError();
+}
+template cudaError_t complex_conj_copy<cfloat>(cudaStream_t, int64_t, const cfloat*, cfloat*);
+template cudaError_t complex_conj_copy<cdouble>(cudaStream_t, int64_t, const cdouble*, cdouble*);
+template cudaError_t complex_conj_axpby<cfloat>(cudaStream_t, int64_t, ScalarArg<cfloat>, const cfloat*,
+                                                ScalarArg<cfloat>, cfloat*);
+template cudaError_t complex_conj_axpby<cdouble>(cudaStream_t, int64_t, ScalarArg<cdouble>, const cdouble*,
+                                                 ScalarArg<cdouble>, cdouble*);
+
 // Real matrix, complex vectors (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:633-658 instantiates its
 // CSR kernel with real values and complex x, y, alpha, beta). A complex vector is a two-column row-major real
 // matrix, so z = A * x is the real SpMM with n = 2 into `scratch` (m complex numbers), and the complex

@@ -224,7 +224,7 @@ def test_complex_with_64bit_indices(handle, device, dtype):
 
 
 def test_complex_refusals(handle, device):
-    """Complex values on the entry points that stay real-only, or as A^H of a CSC matrix."""
+    """Complex values on the entry points that stay real-only."""
     rp, col, val = csr_from_lengths([2, 3, 0, 1], 5, np.complex64)
     t = [up(a, device) for a in (rp, col, val)]
     A = mc.CsrMatrix(4, 5, *t)
@@ -238,14 +238,6 @@ def test_complex_refusals(handle, device):
     assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0, C.byref(size)) == 0
     assert lib.mcsparseSpMV_bufferSize(handle.h, N, pa, A64.d, X.d, pa, Y.d, c32, 0, C.byref(size)) == 0
     assert lib.mcsparseB200SpMVNoAlloc(handle.h, N, pa, A.d, X.d, pa, Y.d, c32, 0) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
-    csc = mc.CscMatrix.__new__(mc.CscMatrix)  # a CSC descriptor over the same arrays, only to query the status
-    d = C.c_void_p()
-    capi.check(lib.mcsparseCreateCsc(C.byref(d), 4, 5, 6, C.c_void_p(t[0].data_ptr()), C.c_void_p(t[1].data_ptr()),
-                                     C.c_void_p(t[2].data_ptr()), capi.MCSPARSE_INDEX_32I, capi.MCSPARSE_INDEX_32I, 0,
-                                     c32))
-    csc.d = d
-    assert lib.mcsparseSpMV_bufferSize(handle.h, H, pa, d, Y.d, pa, X.d, c32, 0,
-                                       C.byref(size)) == capi.MCSPARSE_STATUS_NOT_SUPPORTED
     # real values with op(A) = A^H stay an invalid combination, as in the reference
     rpr, colr, valr = csr_from_lengths([2, 3, 0, 1], 5, np.float32)
     Ar = mc.CsrMatrix(4, 5, *[up(a, device) for a in (rpr, colr, valr)])
@@ -253,3 +245,37 @@ def test_complex_refusals(handle, device):
     onef = C.c_float(1.0)
     assert lib.mcsparseSpMV_bufferSize(handle.h, H, C.byref(onef), Ar.d, Xr.d, C.byref(onef), Yr.d, capi.MACA_R_32F, 0,
                                        C.byref(size)) == capi.MCSPARSE_STATUS_INVALID_VALUE
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+@pytest.mark.parametrize("preprocess", [False, True])
+@pytest.mark.parametrize("name", ["lengths_1_to_33", "empty_start_mid_end", "long_then_short", "all_empty",
+                                  "tile_straddle", "many_short"])
+def test_complex_csc_conjugate_transpose(handle, device, name, dtype, preprocess):
+    """y = alpha * A^H x + beta * y for a CSC matrix: the CSC arrays are the CSR arrays of A^T, the values are
+    conjugated on the fly (the reference conjugates them in place first, mcsp_spmv_gpu.cpp:741-770)."""
+    lengths = ADVERSARIAL_LENGTHS[name]  # lengths of A's columns
+    n, m = len(lengths), max(max(lengths), 1) + 9  # A is m x n
+    base = 1
+    cp, ri, val = csr_from_lengths(lengths, m, dtype, seed=17, base=base)
+    rng = np.random.default_rng(19)
+    x, y0 = cplx(rng, m, dtype), cplx(rng, n, dtype)
+    d_val = up(val, device)
+    A = mc.CscMatrix(m, n, up(cp, device), up(ri, device), d_val, base=base)
+    d_y = up(y0.copy(), device)
+    X, Y = mc.DnVec(up(x, device)), mc.DnVec(d_y)
+    buf = torch.empty(mc.spmv_buffer_size(handle, A, X, Y, op=H), dtype=torch.uint8, device=device)
+    alpha, beta = 0.75 - 1.5j, -0.5 + 0.25j
+    if preprocess:
+        mc.spmv_preprocess(handle, A, X, Y, buf, op=H)
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=beta, op=H)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(cp, ri, val, x, alpha, beta, y0, base=base, conj=True)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], name)
+    assert np.array_equal(d_val.cpu().numpy(), val)  # the values stay as they were
+    # beta = 0 does not read y
+    d_y.fill_(float("nan"))
+    mc.spmv(handle, A, X, Y, buf, alpha=alpha, beta=0.0, op=H)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmv(cp, ri, val, x, alpha, 0.0, None, base=base, conj=True)
+    assert_close(d_y.cpu().numpy(), ref, d, TOL[np.dtype(dtype)], name + " beta 0")
