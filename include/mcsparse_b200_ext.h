@@ -74,6 +74,8 @@ mcsparseStatus_t mcsparseB200SpMVTransposedView(mcsparseSpMatDescr_t matA, mcspa
  * last time instead of gathering all nonzeros again (on the 27-point stencil the gather costs twice the product
  * itself). Without the promise (the default) every product gathers, which is always right. The reference converts
  * on every call (mcsparse/src/kernels/level2/spmv/mcsp_spmv_gpu.cpp:797-846); it has no such switch.
+ * The same promise lets mcsparseSpMM, running from the panels recorded by mcsparseSpMM_preprocess, skip the pass that
+ * regroups the values panel by panel when the buffer holds them from the last call (single matrices, not batches).
  */
 mcsparseStatus_t mcsparseB200SpMatKeepConvertedValues(mcsparseSpMatDescr_t matA, int keep);
 

@@ -1140,6 +1140,7 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
     const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
     std::lock_guard<std::mutex> g(matA->lock);
     matA->spmm_buffer = nullptr;
+    matA->spmm_values_src = nullptr;
     if (plan.num_panels <= 1) return MCSPARSE_STATUS_SUCCESS;
     DeviceGuard guard(handle->device);
     const cudaError_t e =
@@ -1172,7 +1173,7 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
         return pub(BAD_POINTER);
     if (!descr_general(matA->mat_descr)) return pub(NOT_IMPL);
     DeviceGuard guard(handle->device);
-    const SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
+    SpmmPlan plan = spmm_plan_for(opB, matA, matB, matC, computeType);
     const SpmmPlan* use_plan = nullptr;
     void* plan_buffer = nullptr;
     {
@@ -1182,6 +1183,12 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
             plan.num_panels > 1) {
             use_plan = &plan;
             plan_buffer = align_up_256(externalBuffer);
+            // The values are regrouped on every call, unless the caller promised to announce their changes and
+            // the buffer holds these values from the last call (a single-matrix product; batches always regroup).
+            plan.values_current = matA->keep_converted_values && matA->spmm_values_src == matA->vals && matA->batchCount <= 1;
+            matA->spmm_values_src = (matA->keep_converted_values && matA->batchCount <= 1) ? matA->vals : nullptr;
+        } else if (matA->spmm_buffer == externalBuffer) {
+            matA->spmm_values_src = nullptr;
         }
     }
     // A COO or CSC input is converted behind the (panel) plan's part of the buffer.

@@ -307,6 +307,7 @@ mcsparseStatus_t mcsparseCsrSetPointers(mcsparseSpMatDescr_t d, void* csrRowOffs
     d->analysed_rows = nullptr;
     d->trans_buffer = nullptr;
     d->trans_values_src = nullptr;
+    d->spmm_values_src = nullptr;
     d->trans_probed_idx = nullptr;
     d->coo_checked_rows = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
@@ -428,6 +429,7 @@ mcsparseStatus_t mcsparseSpMatSetValues(mcsparseSpMatDescr_t d, void* values) {
     if (d == nullptr) return pub(BAD_POINTER);
     d->vals = values;
     d->trans_values_src = nullptr;  // the values changed (or may have): converted copies are stale
+    d->spmm_values_src = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
 }
 
@@ -435,6 +437,7 @@ mcsparseStatus_t mcsparseB200SpMatKeepConvertedValues(mcsparseSpMatDescr_t d, in
     if (d == nullptr) return pub(BAD_POINTER);
     d->keep_converted_values = keep != 0;
     d->trans_values_src = nullptr;
+    d->spmm_values_src = nullptr;
     return MCSPARSE_STATUS_SUCCESS;
 }
 

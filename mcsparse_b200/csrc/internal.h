@@ -95,6 +95,7 @@ struct mcsparseSpMatDescr {
     bool keep_converted_values = false;
     const void* trans_values_src = nullptr;
     bool trans_values_conj = false;
+    const void* spmm_values_src = nullptr;  // the same for the values regrouped panel by panel by mcsparseSpMM
     // COO inputs: whether the row indices were found out of order (checked once per array, remembered).
     const void* coo_checked_rows = nullptr;
     int64_t coo_checked_nnz = -1;
@@ -258,8 +259,10 @@ struct SpmmPlan {
     int num_panels = 1;
     int panel_cols = 0;  // rows of B (columns of A) per panel
     int lanes = 0;       // lanes per row of the panel kernel: the slab is lanes x 16 bytes wide
-    size_t off_pos = 0, off_ccol = 0, off_cval = 0, off_scan = 0;
+    size_t off_pos = 0, off_ccol = 0, off_cval = 0, off_dst = 0, off_scan = 0;
     size_t bytes = 128;
+    int64_t nnz = 0;              // nonzeros of the matrix the plan was made for
+    bool values_current = false;  // the buffer already holds these values regrouped (the caller vouches for it)
 };
 long long scan_scratch_elems(long long count);
 cudaError_t exclusive_scan_u32(cudaStream_t s, unsigned* data, long long count, unsigned* sums);

@@ -157,14 +157,16 @@ __global__ void __launch_bounds__(kThreads)
         }
         const int cnt = max(0, min(G, j1 - j));
         const int maxcnt = __reduce_max_sync(0xffffffffu, cnt);
-#pragma unroll 4
-        for (int q = 0; q < maxcnt; ++q) {
-            const int cq = __shfl_sync(0xffffffffu, cj, q, G);
-            const T vq = shfl_idx(0xffffffffu, vj, q, G);
-            if (q < cnt && col_ok) {
-                const V b = *reinterpret_cast<const V*>(Bc + (long long)cq * ldb);
-                fma_vec(acc, vq, b);
+        // chunks of four B rows requested together, predicated; no remainder loop (its loads would go one by one)
+        for (int q0 = 0; q0 < maxcnt; q0 += 4) {
+            V b[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int cq = __shfl_sync(0xffffffffu, cj, (q0 + u) & (G - 1), G);
+                b[u] = (q0 + u < cnt && col_ok) ? *reinterpret_cast<const V*>(Bc + (long long)cq * ldb) : zero_vec<V>();
             }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) fma_vec(acc, shfl_idx(0xffffffffu, vj, (q0 + u) & (G - 1), G), b[u]);
         }
     }
     if (row_ok && col_ok) {
@@ -203,6 +205,7 @@ __global__ void __launch_bounds__(kThreads)
 // B rows are loaded with default caching (they are the L2-resident operand); A, the bounds and C
 // are streamed (evict-first).
 // ---------------------------------------------------------------------------------------
+constexpr int kPanelChunk = 4;  // B rows a lane requests together (divides every lane-group width)
 template <typename T, int G, bool FIRST>
 __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
     spmm_panel_kernel(int m, int n, const int* __restrict__ pos, const int* __restrict__ ccol,
@@ -251,19 +254,25 @@ __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
             }
             const int cnt = max(0, min(2 * G, hi0 - j));
             const int maxcnt = __reduce_max_sync(0xffffffffu, cnt);
+            // Chunks of CH nonzeros: the chunk's B rows are requested together (predicated per lane group), then
+            // multiplied. No remainder loop: it would fetch its B rows one after the other, an L2 round trip each
+            // (1.105 -> 1.004 ms at 64 columns). Chunks of 8, or requesting the next chunk before multiplying this
+            // one, were slower (1.04 / 1.06 ms): more predicated-off work, spills at 64 registers.
+            constexpr int CH = kPanelChunk < G ? kPanelChunk : G;
+            auto chunk = [&](int creg, T vreg, int q0, int before) {
+                V b[CH];
+#pragma unroll
+                for (int u = 0; u < CH; ++u) {
+                    const int cq = __shfl_sync(0xffffffffu, creg, q0 + u, G);
+                    b[u] = (before + q0 + u < cnt && col_ok) ? *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32)
+                                                             : zero_vec<V>();
+                }
+#pragma unroll
+                for (int u = 0; u < CH; ++u) fma_vec(acc, shfl_idx(0xffffffffu, vreg, q0 + u, G), b[u]);
+            };
             const int first_half = min(maxcnt, G);
-#pragma unroll 4
-            for (int q = 0; q < first_half; ++q) {
-                const int cq = __shfl_sync(0xffffffffu, ca0, q, G);
-                const T vq = shfl_idx(0xffffffffu, va0, q, G);
-                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32));
-            }
-#pragma unroll 4
-            for (int q = G; q < maxcnt; ++q) {
-                const int cq = __shfl_sync(0xffffffffu, cb0, q - G, G);
-                const T vq = shfl_idx(0xffffffffu, vb0, q - G, G);
-                if (q < cnt && col_ok) fma_vec(acc, vq, *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32));
-            }
+            for (int q0 = 0; q0 < first_half; q0 += CH) chunk(ca0, va0, q0, 0);
+            for (int q0 = G; q0 < maxcnt; q0 += CH) chunk(cb0, vb0, q0 - G, G);
         }
         if (write_c) {
             if (FIRST)
@@ -317,21 +326,52 @@ __global__ void spmm_piece_len_kernel(long long m, int num_panels, const int* __
     if (i == count) piece_len[i] = 0u;
 }
 
-// Regroups one array of A (column indices made 0-based, or values) panel by panel: eight lanes copy the piece
-// of one (panel, row) from its place inside the row to piece_pos[p * m + r].
+// Regroups one array of A (column indices made 0-based, or values; without a source: for every entry of A the
+// position it is regrouped to) panel by panel: eight lanes copy the piece of one (panel, row) from its place inside the row to
+// piece_pos[p * m + r].
 template <typename S, typename D>
 __global__ void __launch_bounds__(256)
-    spmm_regroup_kernel(long long pieces, const int* __restrict__ panel_ptr, long long m,
+    spmm_regroup_kernel(long long pieces, const int* __restrict__ panel_ptr, long long m, int num_panels,
                         const int* __restrict__ piece_pos, const S* __restrict__ src, D* __restrict__ dst, int sub) {
-    const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;
+    // Lane groups are numbered row by row (the pieces of one row are neighbours in a warp), so that a warp reads a
+    // contiguous stretch of the source and every sector of it once; piece (panel p, row r) has index p * m + r.
+    const long long g = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3;
     const int lane = threadIdx.x & 7;
-    if (i >= pieces) return;
+    if (g >= pieces) return;
+    const long long r = g / num_panels;
+    const long long i = (g - r * num_panels) * m + r;
     const int from = panel_ptr[i], len = panel_ptr[i + m] - from, to = piece_pos[i];
     for (int e = lane; e < len; e += 8) {
-        if constexpr (std::is_integral<D>::value)
-            dst[to + e] = (D)src[from + e] - (D)sub;
-        else
+        if constexpr (std::is_integral<D>::value) {
+            if (src == nullptr)
+                dst[from + e] = (D)(to + e);  // where the entry goes (indexed by where it comes from)
+            else
+                dst[to + e] = (D)src[from + e] - (D)sub;
+        } else {
             dst[to + e] = src[from + e];
+        }
+    }
+}
+
+// cval[dst[j]] = val[j]: the per-call regrouping of the values through the destinations recorded by the preprocess
+// call. In source order on purpose: val and dst are read once, fully coalesced (four consecutive j per thread, 128-bit
+// loads where the value type allows), and the stores of a piece (a run of consecutive destinations) meet those of the
+// same piece of the neighbouring rows in L2 before the lines are written back. In destination order every 40-byte
+// piece re-read its 64-byte bursts of val: 534 MB of reads instead of 2 x 134.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    spmm_scatter_values_kernel(long long nnz, const T* __restrict__ val, const int* __restrict__ dst, T* __restrict__ cval) {
+    const long long k = 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x);
+    if (k + 3 < nnz && (reinterpret_cast<uintptr_t>(val) & 15) == 0) {
+        const int4 p = __ldcs(reinterpret_cast<const int4*>(dst + k));
+        alignas(16) T v[4];
+        const uint4* from = reinterpret_cast<const uint4*>(val + k);
+        uint4* to = reinterpret_cast<uint4*>(v);
+#pragma unroll
+        for (int i = 0; i < (int)(4 * sizeof(T) / 16); ++i) to[i] = __ldcs(from + i);
+        cval[p.x] = v[0], cval[p.y] = v[1], cval[p.z] = v[2], cval[p.w] = v[3];
+    } else {
+        for (long long i = k; i < nnz && i < k + 4; ++i) cval[dst[i]] = val[i];
     }
 }
 
@@ -396,14 +436,17 @@ cudaError_t launch_panels(cudaStream_t s, int64_t m, int64_t n, const T* val, co
             blocks_per_sm = std::max(1, std::min(blocks_per_sm, std::atoi(v)));
     }
     char* base_ptr = static_cast<char*>(buf);
-    const int* panel_ptr = reinterpret_cast<const int*>(base_ptr);
     const int* pos = reinterpret_cast<const int*>(base_ptr + plan.off_pos);
     const int* ccol = reinterpret_cast<const int*>(base_ptr + plan.off_ccol);
     T* cval = reinterpret_cast<T*>(base_ptr + plan.off_cval);
-    const long long pieces = (long long)plan.num_panels * m;
-    spmm_regroup_kernel<T, T><<<(unsigned)((pieces * 8 + 255) / 256), 256, 0, s>>>(pieces, panel_ptr, m, pos, val, cval, 0);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    cudaError_t e = cudaSuccess;
+    const long long nnz = plan.nnz;
+    if (!plan.values_current && nnz > 0) {
+        const int* dst = reinterpret_cast<const int*>(base_ptr + plan.off_dst);
+        spmm_scatter_values_kernel<T><<<(unsigned)((nnz + 1023) / 1024), 256, 0, s>>>(nnz, val, dst, cval);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
     const long long groups_per_block = kThreads / G;
     const long long want = (m + groups_per_block - 1) / groups_per_block;
     const unsigned grid = (unsigned)std::max<long long>(1, std::min<long long>(want, (long long)sm_count * blocks_per_sm));
@@ -478,7 +521,9 @@ SpmmPlan spmm_plan(int64_t m, int64_t k, int64_t n, int64_t nnz, size_t value_si
         plan.off_pos = up(size_t(plan.num_panels + 1) * size_t(m) * 4);
         plan.off_ccol = plan.off_pos + up((pieces + 1) * 4);
         plan.off_cval = plan.off_ccol + up(size_t(nnz) * 4);
-        plan.off_scan = plan.off_cval + up(size_t(nnz) * value_size);
+        plan.nnz = nnz;
+        plan.off_dst = plan.off_cval + up(size_t(nnz) * value_size);
+        plan.off_scan = plan.off_dst + up(size_t(nnz) * 4);
         plan.bytes = 256 + plan.off_scan + up(size_t(scan_scratch_elems((long long)pieces + 1)) * 4);
     }
     return plan;
@@ -502,7 +547,13 @@ cudaError_t spmm_preprocess(cudaStream_t s, int64_t m, int64_t nnz, int base, co
     if (e == cudaSuccess) e = exclusive_scan_u32(s, pos, pieces + 1, scratch);
     if (e != cudaSuccess) return e;
     spmm_regroup_kernel<I, int><<<(unsigned)((pieces * 8 + 255) / 256), 256, 0, s>>>(
-        pieces, panel_ptr, m, reinterpret_cast<const int*>(pos), col, ccol, base);
+        pieces, panel_ptr, m, plan.num_panels, reinterpret_cast<const int*>(pos), col, ccol, base);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    // where every entry of A is regrouped to: the values follow through these positions on every product
+    spmm_regroup_kernel<int, int><<<(unsigned)((pieces * 8 + 255) / 256), 256, 0, s>>>(
+        pieces, panel_ptr, m, plan.num_panels, reinterpret_cast<const int*>(pos), nullptr,
+        reinterpret_cast<int*>(base_ptr + plan.off_dst), 0);
     return cudaGetLastError();
 }
 

@@ -162,7 +162,13 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks)
                 sum += times(widen<C, V>(s_val[k + 2 * G]), widen<C, V>(x2));
                 sum += times(widen<C, V>(s_val[k + 3 * G]), widen<C, V>(x3));
             }
-            for (; k < e; k += G) sum += times(widen<C, V>(s_val[k]), widen<C, V>(xb[s_col[k]]));
+            if (k < e) {  // up to three left: gathered together as well
+                const int k1 = min(k + G, e - 1), k2 = min(k + 2 * G, e - 1);
+                const V x0 = xb[s_col[k]], x1 = xb[s_col[k1]], x2 = xb[s_col[k2]];
+                sum += times(widen<C, V>(s_val[k]), widen<C, V>(x0));
+                if (k + G < e) sum += times(widen<C, V>(s_val[k + G]), widen<C, V>(x1));
+                if (k + 2 * G < e) sum += times(widen<C, V>(s_val[k + 2 * G]), widen<C, V>(x2));
+            }
             for (int d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
             if (glane == 0 && i <= nrows) {
                 if (i == nrows) {

@@ -249,6 +249,40 @@ def test_spmm_column_panels(handle, device, dtype, beta, shuffle_rows, lanes, mo
     assert_close(t[4].cpu().numpy().reshape(m, n), ref, d, TOL[np.dtype(dtype)], "single pass")
 
 
+def test_spmm_panels_keep_regrouped_values_on_promise(handle, device, monkeypatch):
+    """With mcsparseB200SpMatKeepConvertedValues the panelled product reuses the values it regrouped last time:
+    an in-place edit is seen only after it was announced (mcsparseSpMatSetValues); without the promise at once."""
+    monkeypatch.setenv("MCSPARSE_B200_SPMM_PANEL_MB", "1")
+    rng = np.random.default_rng(8)
+    m, k, n = 2000, 9000, 64
+    rp, col, val = csr_from_lengths(rng.integers(10, 30, size=m).tolist(), k, np.float32, seed=4)
+    B = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B.ravel())]
+    Cd = torch.zeros(m * n, dtype=torch.float32, device=device)
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2])
+    Bm, Cm = mc.DnMat(t[3], k, n, n), mc.DnMat(Cd, m, n, n)
+    buf = torch.empty(mc.spmm_buffer_size(handle, A, Bm, Cm), dtype=torch.uint8, device=device)
+    mc.spmm_preprocess(handle, A, Bm, Cm, buf)
+    ref, d = oracle.spmm(rp, col, val, B, n, ROW, n, 1.0, 0.0)
+    ref2, d2 = oracle.spmm(rp, col, 2 * val, B, n, ROW, n, 1.0, 0.0)
+
+    def product():
+        mc.spmm(handle, A, Bm, Cm, buf)
+        torch.cuda.synchronize()
+        return Cd.cpu().numpy().reshape(m, n)
+
+    capi.check(lib.mcsparseB200SpMatKeepConvertedValues(A.d, 1))
+    assert_close(product(), ref, d, 1e-5, "first product regroups")
+    assert_close(product(), ref, d, 1e-5, "second product reuses")
+    t[2].mul_(2)  # edited in place, not announced: the product may still use the old values
+    assert_close(product(), ref, d, 1e-5, "unannounced edit")
+    capi.check(lib.mcsparseSpMatSetValues(A.d, C.c_void_p(t[2].data_ptr())))
+    assert_close(product(), ref2, d2, 1e-5, "announced edit")
+    capi.check(lib.mcsparseB200SpMatKeepConvertedValues(A.d, 0))
+    t[2].div_(2)
+    assert_close(product(), ref, d, 1e-5, "without the promise every product regroups")
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("shared_a", [False, True])
 def test_spmm_strided_batch(handle, device, dtype, shared_a):
