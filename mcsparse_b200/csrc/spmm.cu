@@ -205,7 +205,17 @@ __global__ void __launch_bounds__(kThreads)
 // B rows are loaded with default caching (they are the L2-resident operand); A, the bounds and C
 // are streamed (evict-first).
 // ---------------------------------------------------------------------------------------
-constexpr int kPanelChunk = 4;  // B rows a lane requests together (divides every lane-group width)
+constexpr int kPanelRound = 8;  // B rows a lane group has in flight in one round (divides every lane-group width above 4)
+// 16 bytes global -> shared, asynchronously (L2 only: the B rows are the L2-resident operand), and the wait for
+// all of this thread's copies.
+__device__ __forceinline__ void copy16_async(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void copies_wait() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 template <typename T, int G, bool FIRST>
 __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
     spmm_panel_kernel(int m, int n, const int* __restrict__ pos, const int* __restrict__ ccol,
@@ -220,6 +230,8 @@ __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
     const bool col_ok = c0 < n;
     const T* const Bc = B + c0;
     const unsigned ldb32 = (unsigned)ldb;  // the launcher checks that every element offset into B fits 32 bits
+    __shared__ __align__(16) V s_rows[kThreads / G][kPanelRound < G ? kPanelRound : G][G];
+    V* const mine = &s_rows[threadIdx.x / G][0][lane];  // row u of the round: mine[u * G]
     const T alpha = alpha_arg.get(), beta = beta_arg.get();
 
     // bounds of the group's rows i, i + 1, i + 2; the first 2 G elements of the pieces of rows i, i + 1
@@ -254,25 +266,30 @@ __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
             }
             const int cnt = max(0, min(2 * G, hi0 - j));
             const int maxcnt = __reduce_max_sync(0xffffffffu, cnt);
-            // Chunks of CH nonzeros: the chunk's B rows are requested together (predicated per lane group), then
-            // multiplied. No remainder loop: it would fetch its B rows one after the other, an L2 round trip each
-            // (1.105 -> 1.004 ms at 64 columns). Chunks of 8, or requesting the next chunk before multiplying this
-            // one, were slower (1.04 / 1.06 ms): more predicated-off work, spills at 64 registers.
-            constexpr int CH = kPanelChunk < G ? kPanelChunk : G;
-            auto chunk = [&](int creg, T vreg, int q0, int before) {
-                V b[CH];
+            // Rounds of R nonzeros: the lanes copy their 16 bytes of each of the round's B rows into shared memory
+            // asynchronously (cp.async: no destination registers are held while the rows are in flight, so a round
+            // can be twice as deep as a register-staged one), wait once, and multiply from shared memory; every lane
+            // reads back only what it copied itself. No remainder loop (it would fetch its B rows one after the
+            // other, an L2 round trip each): rows past a group's piece are predicated off.
+            // Measured at 64 columns: register-staged chunks of 4 with a remainder loop 1.105 ms, without 1.004 ms,
+            // chunks of 8 1.04 ms; these rounds of 8 0.955 ms; one round of 16 (three blocks per SM) 0.98 ms.
+            constexpr int R = kPanelRound < G ? kPanelRound : G;
+            auto round = [&](int creg, T vreg, int q0, int before) {
 #pragma unroll
-                for (int u = 0; u < CH; ++u) {
+                for (int u = 0; u < R; ++u) {
                     const int cq = __shfl_sync(0xffffffffu, creg, q0 + u, G);
-                    b[u] = (before + q0 + u < cnt && col_ok) ? *reinterpret_cast<const V*>(Bc + (unsigned)cq * ldb32)
-                                                             : zero_vec<V>();
+                    if (before + q0 + u < cnt && col_ok) copy16_async(mine + u * G, Bc + (unsigned)cq * ldb32);
                 }
+                copies_wait();
 #pragma unroll
-                for (int u = 0; u < CH; ++u) fma_vec(acc, shfl_idx(0xffffffffu, vreg, q0 + u, G), b[u]);
+                for (int u = 0; u < R; ++u) {
+                    const T vq = shfl_idx(0xffffffffu, vreg, q0 + u, G);
+                    if (before + q0 + u < cnt && col_ok) fma_vec(acc, vq, mine[u * G]);
+                }
             };
             const int first_half = min(maxcnt, G);
-            for (int q0 = 0; q0 < first_half; q0 += CH) chunk(ca0, va0, q0, 0);
-            for (int q0 = G; q0 < maxcnt; q0 += CH) chunk(cb0, vb0, q0 - G, G);
+            for (int q0 = 0; q0 < first_half; q0 += R) round(ca0, va0, q0, 0);
+            for (int q0 = G; q0 < maxcnt; q0 += R) round(cb0, vb0, q0 - G, G);
         }
         if (write_c) {
             if (FIRST)
