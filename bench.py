@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) of one spmv_tile_kernel launch divided by its algorithmic bytes, from the ncu
 # captures summarised under profiles/ (taken at reduced scale and scaled by the units processed).
-TRAFFIC_RATIO = {"C5": 0.985, "C5_fp16_operands": 1.003, "C2": 0.99, "C3": 1.71, "C4_n64": 3.47}
+TRAFFIC_RATIO = {"C5": 0.985, "C5_fp16_operands": 1.003, "C2": 0.99, "C3": 1.71, "C4_n64": 3.18}
 FALLBACK_HBM_GBS = 6650.0
 
 

@@ -711,12 +711,16 @@ __global__ void __launch_bounds__(THREADS, (PUSH || CREW) ? tile_min_blocks(size
                 sum = mad(valv[k + 2 * G], x2, sum);
                 sum = mad(valv[k + 3 * G], x3, sum);
             }
-            if (k < e) {  // up to three left: gathered together as well (one after the other, each would wait for the last)
-                const int k1 = min(k + G, e - 1), k2 = min(k + 2 * G, e - 1);
-                const T x0 = ldg(xb + colv[k]), x1 = ldg(xb + colv[k1]), x2 = ldg(xb + colv[k2]);
-                sum = mad(valv[k], x0, sum);
-                if (k + G < e) sum = mad(valv[k + G], x1, sum);
-                if (k + 2 * G < e) sum = mad(valv[k + 2 * G], x2, sum);
+            if constexpr (sizeof(T) <= 8 && IPT <= 8) {
+                if (k < e) {  // up to three left: gathered together as well (one after the other, each would wait for the last)
+                    const int k1 = min(k + G, e - 1), k2 = min(k + 2 * G, e - 1);
+                    const T x0 = ldg(xb + colv[k]), x1 = ldg(xb + colv[k1]), x2 = ldg(xb + colv[k2]);
+                    sum = mad(valv[k], x0, sum);
+                    if (k + G < e) sum = mad(valv[k + G], x1, sum);
+                    if (k + 2 * G < e) sum = mad(valv[k + 2 * G], x2, sum);
+                }
+            } else {  // (complex double and the 16-item tiles would pay for it with a resident block less per SM)
+                for (; k < e; k += G) sum = mad(valv[k], ldg(xb + colv[k]), sum);
             }
             for (int d = G >> 1; d > 0; d >>= 1) sum += shfl_xor(sum, d);
             if (glane == 0 && i <= nrows) {
