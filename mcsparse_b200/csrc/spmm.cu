@@ -275,16 +275,29 @@ __global__ void __launch_bounds__(kThreads, MCSP_PANEL_MIN_BLOCKS)
             // chunks of 8 1.04 ms; these rounds of 8 0.955 ms; one round of 16 (three blocks per SM) 0.98 ms.
             constexpr int R = kPanelRound < G ? kPanelRound : G;
             auto round = [&](int creg, T vreg, int q0, int before) {
+                // slots are issued in groups of four, only as many groups as the longest piece of the warp needs
+                // (a predicated-off slot still costs its issue slots)
+                const int need = maxcnt - before - q0;  // warp-uniform
 #pragma unroll
-                for (int u = 0; u < R; ++u) {
-                    const int cq = __shfl_sync(0xffffffffu, creg, q0 + u, G);
-                    if (before + q0 + u < cnt && col_ok) copy16_async(mine + u * G, Bc + (unsigned)cq * ldb32);
+                for (int u0 = 0; u0 < R; u0 += 4) {
+                    if (u0 < need) {
+#pragma unroll
+                        for (int u = u0; u < u0 + 4; ++u) {
+                            const int cq = __shfl_sync(0xffffffffu, creg, q0 + u, G);
+                            if (before + q0 + u < cnt && col_ok) copy16_async(mine + u * G, Bc + (unsigned)cq * ldb32);
+                        }
+                    }
                 }
                 copies_wait();
 #pragma unroll
-                for (int u = 0; u < R; ++u) {
-                    const T vq = shfl_idx(0xffffffffu, vreg, q0 + u, G);
-                    if (before + q0 + u < cnt && col_ok) fma_vec(acc, vq, mine[u * G]);
+                for (int u0 = 0; u0 < R; u0 += 4) {
+                    if (u0 < need) {
+#pragma unroll
+                        for (int u = u0; u < u0 + 4; ++u) {
+                            const T vq = shfl_idx(0xffffffffu, vreg, q0 + u, G);
+                            if (before + q0 + u < cnt && col_ok) fma_vec(acc, vq, mine[u * G]);
+                        }
+                    }
                 }
             };
             const int first_half = min(maxcnt, G);
