@@ -10,6 +10,7 @@ Only torch.distributed and the C ABI are used; there is no arithmetic here.
 """
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -172,7 +173,15 @@ class ShardedSpmv:
         self.buffer = torch.empty(host.spmv_buffer_size(handle, A_local, self.X, self.Y), dtype=torch.uint8,
                                   device=x.device)
         host.spmv_preprocess(handle, A_local, self.X, self.Y, self.buffer)
-        ptrs = [] if self.mode == "multicast" else [self.y.peer_ptrs[g] for g in sorted(self.y.peer_ptrs)]
+        # Destinations in rank order; MCSPARSE_B200_PEER_ORDER=rotated lists them as rank + 1, rank + 2, ... modulo the
+        # group, so that at any moment the ranks aim at different GPUs instead of all starting with GPU 0.
+        if self.mode == "multicast":
+            ptrs = []
+        else:
+            order = sorted(self.y.peer_ptrs)
+            if os.environ.get("MCSPARSE_B200_PEER_ORDER", "ascending") == "rotated":
+                order = sorted(order, key=lambda g: (g - self.rank) % self.world)
+            ptrs = [self.y.peer_ptrs[g] for g in order]
         self.n_peers = len(ptrs)
         self.peer_array = (C.c_void_p * max(self.n_peers, 1))(*ptrs)
         self.token = torch.zeros(1, dtype=torch.int32, device=x.device)
