@@ -145,8 +145,6 @@ class MulticastVector:
 
 def push_mode(world):
     """How ShardedSpmv assembles y: MCSPARSE_B200_PUSH_MODE=peer|multicast, default peer stores."""
-    import os
-
     mode = os.environ.get("MCSPARSE_B200_PUSH_MODE", "peer")
     return mode if mode in ("peer", "multicast") and world > 1 else "peer"
 
@@ -185,8 +183,6 @@ class ShardedSpmv:
         self.n_peers = len(ptrs)
         self.peer_array = (C.c_void_p * max(self.n_peers, 1))(*ptrs)
         self.token = torch.zeros(1, dtype=torch.int32, device=x.device)
-        import os
-
         # After the push the GPUs are ordered by per-peer arrival flags written and awaited on the device
         # (mcsparseB200PeerSignalWait); MCSPARSE_B200_PUSH_SYNC=collective uses a 4-byte all-reduce instead,
         # as the multicast variant always does (its vector comes from another allocator).
