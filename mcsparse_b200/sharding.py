@@ -149,6 +149,14 @@ def push_mode(world):
     return mode if mode in ("peer", "multicast") and world > 1 else "peer"
 
 
+def destination_order(rank, world, mode=None):
+    """The other ranks of the group in the order a rank lists them as push destinations: rank order, or with
+    MCSPARSE_B200_PEER_ORDER=rotated (or mode="rotated") rank + 1, rank + 2, ... modulo the group."""
+    mode = mode or os.environ.get("MCSPARSE_B200_PEER_ORDER", "ascending")
+    others = [g for g in range(world) if g != rank]
+    return sorted(others, key=lambda g: (g - rank) % world) if mode == "rotated" else others
+
+
 class ShardedSpmv:
     """y = alpha * A @ x + beta * y for a row-sharded A with the full y left on every GPU.
 
@@ -173,13 +181,7 @@ class ShardedSpmv:
         host.spmv_preprocess(handle, A_local, self.X, self.Y, self.buffer)
         # Destinations in rank order; MCSPARSE_B200_PEER_ORDER=rotated lists them as rank + 1, rank + 2, ... modulo the
         # group, so that at any moment the ranks aim at different GPUs instead of all starting with GPU 0.
-        if self.mode == "multicast":
-            ptrs = []
-        else:
-            order = sorted(self.y.peer_ptrs)
-            if os.environ.get("MCSPARSE_B200_PEER_ORDER", "ascending") == "rotated":
-                order = sorted(order, key=lambda g: (g - self.rank) % self.world)
-            ptrs = [self.y.peer_ptrs[g] for g in order]
+        ptrs = [] if self.mode == "multicast" else [self.y.peer_ptrs[g] for g in destination_order(self.rank, self.world)]
         self.n_peers = len(ptrs)
         self.peer_array = (C.c_void_p * max(self.n_peers, 1))(*ptrs)
         self.token = torch.zeros(1, dtype=torch.int32, device=x.device)

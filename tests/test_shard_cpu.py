@@ -66,3 +66,19 @@ def test_shard_bounds_edge_cases():
     b, nnz = sharding.shard_bounds(torch.zeros(7, dtype=torch.int64), 2)
     assert nnz == 0 and b == [0, 0, 7]
     assert b == oracle.shard_row_bounds(np.zeros(8, np.int32), 0, 2).tolist()
+
+
+def test_destination_order(monkeypatch):
+    """Push destinations of a rank: every other rank once; rank order by default, rotated on request."""
+    from mcsparse_b200 import sharding
+
+    monkeypatch.delenv("MCSPARSE_B200_PEER_ORDER", raising=False)
+    assert sharding.destination_order(2, 4) == [0, 1, 3]
+    assert sharding.destination_order(0, 1) == []
+    monkeypatch.setenv("MCSPARSE_B200_PEER_ORDER", "rotated")
+    assert sharding.destination_order(2, 4) == [3, 0, 1]
+    assert sharding.destination_order(7, 8) == [0, 1, 2, 3, 4, 5, 6]
+    for world in (2, 3, 8):
+        for rank in range(world):
+            for mode in ("ascending", "rotated"):
+                assert sorted(sharding.destination_order(rank, world, mode)) == [g for g in range(world) if g != rank]
