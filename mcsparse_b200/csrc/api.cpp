@@ -444,6 +444,7 @@ St spmv_transposed_run(mcsparseContext* h, mcsparseSpMatDescr* A, const CsrView&
             std::lock_guard<std::mutex> g(A->lock);
             if (A->analysed_buffer == buffer) A->analysed_buffer = nullptr;
             if (A->push_buffer == buffer) A->push_buffer = nullptr;
+            if (A->spmm_buffer == buffer) A->spmm_buffer = nullptr, A->spmm_values_src = nullptr;
         }
         cudaError_t e = convert_structure(h->stream, A, v, L.plan, L.area);
         if (e != cudaSuccess) return from_cuda(e);
@@ -536,6 +537,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
         {
             std::lock_guard<std::mutex> g(A->lock);
             if (A->trans_buffer == buffer) A->trans_buffer = nullptr, A->trans_values_src = nullptr;
+            if (A->spmm_buffer == buffer) A->spmm_buffer = nullptr, A->spmm_values_src = nullptr;  // (the panels too)
             if (preprocess_only) {
                 A->analysed_buffer = buffer;
                 A->analysed_rows = A->rows;
@@ -585,6 +587,7 @@ St spmv_entry(mcsparseHandle_t h, mcsparseOperation_t opA, const void* alpha, mc
     bool analyse = true;
     {
         std::lock_guard<std::mutex> g(A->lock);
+        if (A->spmm_buffer == buffer) A->spmm_buffer = nullptr, A->spmm_values_src = nullptr;  // SpMM panels recorded here are gone
         if (A->trans_buffer == buffer) {  // the buffer changes hands: a later A^T product reconverts
             A->trans_buffer = nullptr;
             A->trans_values_src = nullptr;

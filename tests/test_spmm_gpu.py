@@ -283,6 +283,33 @@ def test_spmm_panels_keep_regrouped_values_on_promise(handle, device, monkeypatc
     assert_close(product(), ref, d, 1e-5, "without the promise every product regroups")
 
 
+def test_spmm_panels_forgotten_when_the_buffer_is_given_to_spmv(handle, device, monkeypatch):
+    """A buffer that holds recorded panels and is then handed to mcsparseSpMV for the same matrix no longer holds
+    them: the next mcsparseSpMM with that buffer must not read them (it takes the single-pass kernel)."""
+    monkeypatch.setenv("MCSPARSE_B200_SPMM_PANEL_MB", "1")
+    rng = np.random.default_rng(21)
+    m, k, n = 1500, 9000, 64
+    rp, col, val = csr_from_lengths(rng.integers(10, 30, size=m).tolist(), k, np.float32, seed=5)
+    B = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    t = [torch.from_numpy(a).to(device) for a in (rp, col, val, B.ravel())]
+    Cd = torch.zeros(m * n, dtype=torch.float32, device=device)
+    A = mc.CsrMatrix(m, k, t[0], t[1], t[2])
+    Bm, Cm = mc.DnMat(t[3], k, n, n), mc.DnMat(Cd, m, n, n)
+    buf = torch.empty(mc.spmm_buffer_size(handle, A, Bm, Cm), dtype=torch.uint8, device=device)
+    mc.spmm_preprocess(handle, A, Bm, Cm, buf)
+    x = torch.from_numpy(rng.uniform(-1, 1, k).astype(np.float32)).to(device)
+    y = torch.zeros(m, dtype=torch.float32, device=device)
+    X, Y = mc.DnVec(x), mc.DnVec(y)
+    assert mc.spmv_buffer_size(handle, A, X, Y) <= buf.numel()
+    mc.spmv(handle, A, X, Y, buf)  # writes its partition over the start of the panel data
+    mc.spmm(handle, A, Bm, Cm, buf)
+    torch.cuda.synchronize()
+    ref, d = oracle.spmm(rp, col, val, B, n, ROW, n, 1.0, 0.0)
+    assert_close(Cd.cpu().numpy().reshape(m, n), ref, d, 1e-5, "SpMM after SpMV in the same buffer")
+    refv, dv = oracle.spmv(rp, col, val, x.cpu().numpy(), 1.0, 0.0, None)
+    assert_close(y.cpu().numpy(), refv, dv, 1e-5, "the SpMV itself")
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("shared_a", [False, True])
 def test_spmm_strided_batch(handle, device, dtype, shared_a):
