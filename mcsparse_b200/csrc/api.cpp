@@ -1145,6 +1145,10 @@ mcsparseStatus_t mcsparseSpMM_preprocess(mcsparseHandle_t handle, mcsparseOperat
     matA->spmm_buffer = nullptr;
     matA->spmm_values_src = nullptr;
     if (plan.num_panels <= 1) return MCSPARSE_STATUS_SUCCESS;
+    // the buffer is about to hold the panels: what mcsparseSpMV recorded in it for this matrix is gone
+    if (matA->analysed_buffer == externalBuffer) matA->analysed_buffer = nullptr;
+    if (matA->push_buffer == externalBuffer) matA->push_buffer = nullptr;
+    if (matA->trans_buffer == externalBuffer) matA->trans_buffer = nullptr, matA->trans_values_src = nullptr;
     DeviceGuard guard(handle->device);
     const cudaError_t e =
         matA->rowIdxType == MCSPARSE_INDEX_64I
@@ -1192,6 +1196,11 @@ mcsparseStatus_t mcsparseSpMM(mcsparseHandle_t handle, mcsparseOperation_t opA, 
             matA->spmm_values_src = (matA->keep_converted_values && matA->batchCount <= 1) ? matA->vals : nullptr;
         } else if (matA->spmm_buffer == externalBuffer) {
             matA->spmm_values_src = nullptr;
+        }
+        if (matA->format != MCSPARSE_FORMAT_CSR) {  // the conversion writes the buffer: SpMV records in it are gone
+            if (matA->analysed_buffer == externalBuffer) matA->analysed_buffer = nullptr;
+            if (matA->push_buffer == externalBuffer) matA->push_buffer = nullptr;
+            if (matA->trans_buffer == externalBuffer) matA->trans_buffer = nullptr, matA->trans_values_src = nullptr;
         }
     }
     // A COO or CSC input is converted behind the (panel) plan's part of the buffer.

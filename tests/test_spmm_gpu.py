@@ -308,6 +308,13 @@ def test_spmm_panels_forgotten_when_the_buffer_is_given_to_spmv(handle, device, 
     assert_close(Cd.cpu().numpy().reshape(m, n), ref, d, 1e-5, "SpMM after SpMV in the same buffer")
     refv, dv = oracle.spmv(rp, col, val, x.cpu().numpy(), 1.0, 0.0, None)
     assert_close(y.cpu().numpy(), refv, dv, 1e-5, "the SpMV itself")
+    # and the other way round: a partition recorded by mcsparseSpMV_preprocess is forgotten when the buffer takes panels
+    mc.spmv_preprocess(handle, A, X, Y, buf)
+    mc.spmm_preprocess(handle, A, Bm, Cm, buf)
+    y.fill_(float("nan"))
+    mc.spmv(handle, A, X, Y, buf)
+    torch.cuda.synchronize()
+    assert_close(y.cpu().numpy(), refv, dv, 1e-5, "SpMV after SpMM_preprocess in the same buffer")
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
