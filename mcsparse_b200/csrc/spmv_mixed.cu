@@ -8,15 +8,15 @@
 // type, the row sum is kept in the compute type, y[r] = beta * compute(y[r]) + alpha * sum is converted to
 // y's type (round to nearest even) once.
 //
-// The matrix moves 4 + 2 (or 4 + 1) bytes per nonzero, so what matters is bytes in flight and work balance,
-// as for the fp32 / fp64 kernels; the kernel uses the same merge-path partition (2048 merge items per
-// tile, 256 threads) and the same two in-tile paths (lanes per row for short rows, the merge walk for long
-// ones). Differences: the tile's column indices and values are loaded lane-consecutively into registers
-// (sixteen independent loads per thread before the first use; the narrow values would make poor bulk
-// copies: a tile's slice is 2 to 4 KB), sums and products are in the compute type, and a row that
-// continues from an earlier tile is not added into y
-// piecewise (y may be a 16-bit type, and the result is to be rounded once): the tile leaves the row's
-// local part in head_val[t] and a second kernel adds the carries of the tiles before it and writes y.
+// The matrix moves 4 + 2 (or 4 + 1) bytes per nonzero, so what matters is bytes in flight and work balance, as for
+// the fp32 / fp64 kernels; the kernel uses the same merge-path partition (2048 merge items per tile, 256 threads)
+// and the same two in-tile paths (lanes per row for short rows, the merge walk for long ones). Differences:
+//   - the tile's column indices and values are loaded lane-consecutively into registers (sixteen independent loads
+//     per thread before the first use) instead of by bulk copies;
+//   - sums and products are in the compute type;
+//   - a row that continues from an earlier tile is not added into y piecewise (y may be a 16-bit type, and the
+//     result is to be rounded once): the tile leaves the row's local part in head_val[t] and a second kernel adds the
+//     carries of the tiles before it and writes y.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
